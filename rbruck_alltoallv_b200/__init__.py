@@ -1,0 +1,19 @@
+"""rbruck_alltoallv_b200: a Blackwell-native non-uniform all-to-all (alltoallv) library.
+
+Host-only parts (plan compiler, CPU executor, distributions, oracle) import without a GPU; the CUDA
+library is loaded on first use of a GPU entry point.
+"""
+from .parallel.plan import ALGOS, Plan, PlanError, host_alltoallv  # noqa: F401
+
+__version__ = "0.1.0"
+
+
+def __getattr__(name):
+    # GPU-facing API is imported lazily so that ``import rbruck_alltoallv_b200`` works on CPU boxes.
+    if name in ("Communicator", "init", "get_default_comm"):
+        from .parallel import comm as _c
+        return getattr(_c, name)
+    if name in ("alltoallv", "alltoall", "nccl_alltoallv"):
+        from .ops import alltoallv as _a
+        return getattr(_a, name)
+    raise AttributeError(name)

@@ -1,0 +1,123 @@
+"""Plan compiler + CPU executor against the direct-copy oracle (no GPU)."""
+import numpy as np
+import pytest
+
+from rbruck_alltoallv_b200 import Plan, host_alltoallv
+from rbruck_alltoallv_b200.parallel.plan import ALGOS, HIERARCHICAL
+from rbruck_alltoallv_b200.utils import distributions as dist
+from rbruck_alltoallv_b200.utils import oracle
+
+
+def run(plan, P, ts, seed, packed=True, hi=9):
+    counts = dist.uniform(P, hi, seed)
+    counts[counts < 2] = 0  # zero-length blocks
+    prob = oracle.make_problem(counts, ts, seed, packed=packed)
+    send = oracle.fill_send(prob, seed)
+    recv = oracle.empty_recv(prob)
+    rc = host_alltoallv(plan, send, recv, prob.counts, prob.sdispls, prob.rdispls, ts)
+    assert rc == 0, f"executor rc {rc}"
+    assert oracle.first_mismatch(recv, oracle.expected_recv(prob, send)) is None
+
+
+FLAT = ["linear", "spreadout", "scattered", "pairwise", "xor", "rbruck", "rbruck_om", "tuna", "tuna2"]
+
+
+@pytest.mark.parametrize("algo", FLAT)
+@pytest.mark.parametrize("P", [1, 2, 3, 4, 5, 6, 7, 8, 12, 16, 27])
+def test_flat_all_radices(algo, P):
+    if algo == "xor" and P & (P - 1):
+        assert Plan(algo, P).err == -1
+        return
+    radices = range(2, P + 2) if "bruck" in algo or "tuna" in algo else [2]
+    for r in radices:
+        for b in ([0, 1, 2, 3] if algo in ("tuna", "tuna2", "scattered") else [0]):
+            plan = Plan(algo, P, r=r, b=b).check()
+            run(plan, P, ts=4, seed=P * 100 + r, packed=(r % 2 == 0))
+
+
+@pytest.mark.parametrize("algo", sorted(HIERARCHICAL))
+@pytest.mark.parametrize("P,n", [(4, 2), (8, 4), (8, 2), (6, 3), (6, 2), (12, 4), (16, 4), (27, 9), (9, 3)])
+def test_hierarchical(algo, P, n):
+    for r in range(2, n + 2):
+        for b in [0, 1, 2, 5]:
+            plan = Plan(algo, P, n=n, r=r, r2=r, b=b, b2=b).check()
+            run(plan, P, ts=8, seed=P + 31 * r + b, packed=(b % 2 == 0))
+
+
+def test_type_sizes_and_unaligned():
+    for ts in (1, 2, 4, 8, 16):
+        run(Plan("tuna2", 8, r=2, b=1).check(), 8, ts, seed=ts, packed=False, hi=33)
+
+
+def test_round_counts_match_reference_formula():
+    # K = w (r - 1) - d  (src/tuna.cpp:28-31)
+    for P in range(2, 40):
+        for r in range(2, P):
+            st = Plan("tuna", P, r=r).check().stats
+            w, v = 0, P - 1
+            while v:
+                w += 1
+                v //= r
+            nlpow = r ** (w - 1)
+            d = (nlpow * r - P) // nlpow
+            assert st.w == w and st.K == w * (r - 1) - d, (P, r, st)
+
+
+def test_known_table():
+    # rounds / staging cells / forwarded blocks per rank for P = 8
+    for r, K, hops_per_rank in [(2, 3, 12), (3, 4, 10), (4, 4, 10), (7, 7, 7)]:
+        p = Plan("rbruck_om", 8, r=r).check()
+        assert p.stats.K == K
+        assert p.stats.hops == 8 * hops_per_rank
+        assert p.ncells == hops_per_rank - 7
+
+
+def test_argument_rules():
+    assert Plan("rbruck", 8, r=1).err == -1
+    assert Plan("rbruck_om", 8, r=0).err == -1
+    assert Plan("rbruck", 8, r=100).check().spec["r"] == 8
+    assert Plan("tuna", 8, r=1).check().spec["r"] == 2
+    assert Plan("tuna2", 8, r=100, b=-3).check().spec == dict(algo="tuna2", P=8, n=0, r=7, r2=0, b=8, b2=0)
+    assert Plan("tuna2", 2, r=5).check().spec["r"] == 2       # the reference would loop forever here
+    assert Plan("tuna", 1, r=5).check().stats.hops == 0
+    assert Plan("scattered", 8, b=0).check().spec["b"] == 8
+    assert Plan("xor", 6).err == -1
+    assert Plan("ttpl_bt", 8, n=4, r=1).err == -1
+    assert Plan("ttpl_bt", 8, n=4, r=9).check().spec["r"] == 4
+    assert Plan("ttpl_bt", 8, n=3, r=2).err == -1
+    assert Plan("uniform_spreadout_twolayer", 8, n=8, r=2).err == -2
+    assert Plan("twolayer_linear", 8, n=8).err == -2
+    assert Plan("twolayer_linear_s2", 8, n=4, b=0, b2=0).check().spec["b2"] == 8
+    assert Plan("uniform_isplit_rbruck", 8, n=2, r=2, r2=0).check().spec["r2"] == 4
+
+
+def test_cells_are_single_assignment_and_ordered():
+    # every staging cell of every rank is written once, read once, and written before it is read
+    for algo, kw in [("rbruck", dict(r=2)), ("tuna2", dict(r=3, b=2)), ("ttpl", dict(n=4, r=2)),
+                     ("ttpl_bt_s1", dict(n=2, r=2, b=3)), ("uniform_isplit_rbruck", dict(n=2, r=2, r2=2))]:
+        p = Plan(algo, 16, **kw).check()
+        ops = p.ops()
+        written, read = {}, {}
+        for i, o in enumerate(ops):
+            if o["src_cell"] >= 0:
+                k = (int(o["src"]), int(o["src_cell"]))
+                assert k not in read
+                read[k] = i
+            if o["dst_cell"] >= 0:
+                k = (int(o["dst"]), int(o["dst_cell"]))
+                assert k not in written
+                written[k] = i
+        assert set(read) <= set(written)
+        for k, i in read.items():
+            assert ops[written[k]]["key"] < ops[i]["key"]
+        assert np.all(np.diff(ops["key"].astype(np.int64)) >= 0)
+
+
+def test_every_pair_delivered_once():
+    for algo in ALGOS:
+        P, n = 8, 4
+        p = Plan(algo, P, n=n, r=2, r2=2, b=2, b2=2).check()
+        ops = p.ops()
+        final = ops[ops["dst_cell"] < 0]
+        pairs = sorted((int(o["origin"]), int(o["dest"])) for o in final)
+        assert pairs == [(s, d) for s in range(P) for d in range(P)], algo
