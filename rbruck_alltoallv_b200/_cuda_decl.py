@@ -1,0 +1,44 @@
+"""ctypes signatures of the CUDA library's C API (``csrc/include/rbv/rbruckv.h``)."""
+import ctypes as C
+
+c_int_p = C.POINTER(C.c_int)
+c_ll_p = C.POINTER(C.c_longlong)
+
+
+class Status(C.Structure):
+    _fields_ = [("code", C.c_int), ("site", C.c_int), ("detail0", C.c_int), ("detail1", C.c_int),
+                ("trace", C.c_ulonglong * 8)]
+
+
+STATUS_NAMES = {0: "ok", 1: "timeout", 2: "bad_argument", 3: "staging_capacity", 4: "truncate", 5: "aborted"}
+SITE_NAMES = {0: "-", 1: "metadata", 2: "staging_cell", 3: "final_arrival"}
+
+
+def declare_cuda(lib):
+    lib.rbv_last_error.restype = C.c_char_p
+    lib.rbv_ctx_create.restype = C.c_void_p
+    lib.rbv_ctx_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_size_t]
+    lib.rbv_ctx_destroy.argtypes = [C.c_void_p]
+    lib.rbv_ctx_ipc_handle.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_ctx_connect.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_ctx_set_stream.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_ctx_set_timeout_ms.argtypes = [C.c_void_p, C.c_double]
+    lib.rbv_ctx_set_launch.argtypes = [C.c_void_p, C.c_int, C.c_size_t]
+    lib.rbv_ctx_sync.argtypes = [C.c_void_p]
+    lib.rbv_ctx_set_absent_rank.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_status.argtypes = [C.c_void_p, C.POINTER(Status)]
+    lib.rbv_ctx_reset.argtypes = [C.c_void_p]
+    lib.rbv_ctx_info.argtypes = [C.c_void_p, c_ll_p]
+    lib.rbv_ctx_heap.restype = C.c_void_p
+    lib.rbv_ctx_heap.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_symm_alloc.restype = C.c_void_p
+    lib.rbv_symm_alloc.argtypes = [C.c_void_p, C.c_size_t]
+    lib.rbv_symm_free.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_comm.restype = C.c_void_p
+    lib.rbv_comm.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_comm_rank.argtypes = [C.c_void_p]
+    lib.rbv_comm_size.argtypes = [C.c_void_p]
+    lib.rbv_alltoallv.argtypes = [C.c_void_p] + [C.c_int] * 7 + [
+        C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+        C.c_int, C.c_longlong, C.c_uint, C.c_int, C.c_size_t, C.c_void_p]
+    lib.rbv_update_timers.argtypes = [C.c_void_p]

@@ -1,0 +1,347 @@
+// Context implementation: heap layout, CUDA IPC peer mapping, symmetric allocator, plan cache and
+// the launch path of the alltoallv kernel.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+
+#include "rbv/context.h"
+
+namespace rbv {
+
+namespace {
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+#define RBV_CUDA_THROW(expr)                                                              \
+  do {                                                                                    \
+    cudaError_t e__ = (expr);                                                             \
+    if (e__ != cudaSuccess) {                                                             \
+      char buf__[512];                                                                    \
+      std::snprintf(buf__, sizeof buf__, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+      throw std::runtime_error(buf__);                                                    \
+    }                                                                                     \
+  } while (0)
+}  // namespace
+
+Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size_t arena_bytes)
+    : P_(P), L_(nproc > 0 ? P / nproc : 0), nproc_(nproc), proc_(proc), device_(device) {
+  if (P < 1 || P > kMaxRanks) throw std::runtime_error("rank count must be in 1..64");
+  if (nproc < 1 || nproc > kMaxProcs || P % nproc != 0) throw std::runtime_error("process count must divide the rank count (max 16)");
+  if (proc < 0 || proc >= nproc) throw std::runtime_error("process index out of range");
+  RBV_CUDA_THROW(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  RBV_CUDA_THROW(cudaGetDeviceProperties(&prop, device));
+  sm_count_ = prop.multiProcessorCount;
+  int per_sm = 1;
+  RBV_CUDA_THROW(a2av_configure(P, &per_sm));
+  per_sm = std::max(1, std::min(per_sm, 2));
+  max_ctas_ = sm_count_ * per_sm;
+
+  lay_.ctrl_off = 0;
+  lay_.flags_off = align_up(sizeof(CtrlBlock), 256);
+  lay_.meta_off = lay_.flags_off + align_up(sizeof(unsigned) * 2ull * L_ * kMaxCellsPerRank, 256);
+  lay_.meta_bytes = meta_table_bytes(P);
+  lay_.stage_off = align_up(lay_.meta_off + 2 * lay_.meta_bytes, 4096);
+  lay_.arena_bytes = align_up(arena_bytes, 4096);
+  lay_.user_off = lay_.stage_off + 2ull * L_ * lay_.arena_bytes;
+  lay_.total_bytes = lay_.user_off + align_up(user_bytes, 4096);
+
+  RBV_CUDA_THROW(cudaMalloc(&heap_, lay_.total_bytes));
+  RBV_CUDA_THROW(cudaMemset(heap_, 0, lay_.stage_off));
+  peer_[proc] = heap_;
+  opened_[proc] = false;
+  free_[lay_.user_off] = lay_.total_bytes - lay_.user_off;
+
+  RBV_CUDA_THROW(cudaHostAlloc(&host_status_, sizeof(StatusBlock), cudaHostAllocMapped));
+  std::memset(host_status_, 0, sizeof(StatusBlock));
+  RBV_CUDA_THROW(cudaHostGetDevicePointer(&host_status_dev_, host_status_, 0));
+  RBV_CUDA_THROW(cudaDeviceSynchronize());
+}
+
+Context::~Context() {
+  cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  for (auto& kv : plans_) {
+    if (kv.second->d_ops) cudaFree(kv.second->d_ops);
+    if (kv.second->d_done) cudaFree(kv.second->d_done);
+  }
+  for (int q = 0; q < nproc_; q++)
+    if (opened_[q] && peer_[q]) cudaIpcCloseMemHandle(peer_[q]);
+  for (int i = 0; i < kRing; i++) {
+    if (ring_host_[i]) cudaFreeHost(ring_host_[i]);
+    if (ring_dev_[i]) cudaFree(ring_dev_[i]);
+    if (ring_ev_[i]) cudaEventDestroy(ring_ev_[i]);
+  }
+  if (host_status_) cudaFreeHost(host_status_);
+  if (heap_) cudaFree(heap_);
+}
+
+cudaError_t Context::ipc_handle(void* out64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, heap_);
+  if (e == cudaSuccess) std::memcpy(out64, &h, 64);
+  return e;
+}
+
+cudaError_t Context::connect(const void* handles) {
+  cudaError_t e = cudaSetDevice(device_);
+  if (e != cudaSuccess) return e;
+  for (int q = 0; q < nproc_; q++) {
+    if (q == proc_) continue;
+    if (opened_[q]) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, static_cast<const char*>(handles) + 64 * q, 64);
+    void* p = nullptr;
+    e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return e;
+    peer_[q] = static_cast<char*>(p);
+    opened_[q] = true;
+  }
+  return cudaSuccess;
+}
+
+void* Context::symm_alloc(size_t bytes) {
+  bytes = align_up(std::max<size_t>(bytes, 1), 256);
+  for (auto it = free_.begin(); it != free_.end(); ++it) {
+    if (it->second >= bytes) {
+      size_t off = it->first, rest = it->second - bytes;
+      free_.erase(it);
+      if (rest) free_[off + bytes] = rest;
+      used_[off] = bytes;
+      return heap_ + off;
+    }
+  }
+  return nullptr;
+}
+
+int Context::symm_free(void* p) {
+  size_t off = static_cast<char*>(p) - heap_;
+  auto it = used_.find(off);
+  if (it == used_.end()) return -1;
+  size_t bytes = it->second;
+  used_.erase(it);
+  auto ins = free_.emplace(off, bytes).first;
+  auto next = std::next(ins);
+  if (next != free_.end() && ins->first + ins->second == next->first) {
+    ins->second += next->second;
+    free_.erase(next);
+  }
+  if (ins != free_.begin()) {
+    auto prev = std::prev(ins);
+    if (prev->first + prev->second == ins->first) {
+      prev->second += ins->second;
+      free_.erase(ins);
+    }
+  }
+  return 0;
+}
+
+bool Context::in_heap(const void* p, size_t bytes) const {
+  const char* c = static_cast<const char*>(p);
+  return c >= heap_ + lay_.user_off && c + bytes <= heap_ + lay_.total_bytes;
+}
+
+const DevPlan* Context::plan_for(const AlgoSpec& s) {
+  auto key = std::make_tuple(s.algo, s.P, s.n, s.r, s.r2, s.b, s.b2);
+  auto it = plans_.find(key);
+  if (it != plans_.end()) return it->second.get();
+  auto dp = std::make_unique<DevPlan>();
+  dp->plan = build_plan(s);
+  if (!dp->plan.err) {
+    if (dp->plan.ncells > kMaxCellsPerRank) {
+      dp->plan.err = -3;
+      dp->plan.errmsg = "plan needs more staging cells than the communicator provides";
+    } else {
+      std::vector<int> mine(L_);
+      for (int i = 0; i < L_; i++) mine[i] = proc_ * L_ + i;
+      std::vector<Op> ops = ops_for_ranks(dp->plan, mine);
+      dp->nops = (int)ops.size();
+      if (dp->nops) {
+        RBV_CUDA_THROW(cudaMalloc(&dp->d_ops, ops.size() * sizeof(Op)));
+        RBV_CUDA_THROW(cudaMemcpy(dp->d_ops, ops.data(), ops.size() * sizeof(Op), cudaMemcpyHostToDevice));
+        RBV_CUDA_THROW(cudaMalloc(&dp->d_done, ops.size() * sizeof(unsigned)));
+        RBV_CUDA_THROW(cudaMemset(dp->d_done, 0, ops.size() * sizeof(unsigned)));
+      }
+    }
+  }
+  const DevPlan* out = dp.get();
+  plans_[key] = std::move(dp);
+  return out;
+}
+
+int Context::alltoallv(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const CallOptions& opt,
+                       cudaStream_t stream) {
+  AlgoSpec spec = spec_in;
+  spec.P = P_;
+  const DevPlan* dp = plan_for(spec);
+  if (dp->plan.err) { last_error_ = dp->plan.errmsg; return dp->plan.err; }
+  if (ts < 1) { last_error_ = "type size must be positive"; return RBV_ERR_BAD_ARG; }
+  const bool inplace = (opt.flags & CALL_INPLACE) != 0;
+  if (inplace && ca.counts_on_device) { last_error_ = "in-place calls need host-side counts"; return RBV_ERR_BAD_ARG; }
+  if (!ca.sendcounts || !ca.sdispls || !ca.rdispls || !ca.recvbufs || (!inplace && !ca.sendbufs)) {
+    last_error_ = "null argument"; return RBV_ERR_BAD_ARG;
+  }
+
+  KernelArgs ka;
+  std::memset(&ka, 0, sizeof ka);
+  ka.P = P_; ka.L = L_; ka.nproc = nproc_; ka.proc = proc_;
+  ka.type_size = ts;
+  ka.seq = seq_;
+  ka.flags = opt.flags & CALL_INPLACE;
+  ka.nops = dp->nops;
+  ka.absent_rank = absent_rank_;
+  ka.ncells = dp->plan.ncells;
+  ka.ops = dp->d_ops;
+  ka.op_done = dp->d_done;
+  ka.timeout_ns = timeout_ns_;
+  ka.lay = lay_;
+  for (int q = 0; q < nproc_; q++) {
+    if (!peer_[q]) { last_error_ = "peer heaps are not connected"; return RBV_ERR_BAD_ARG; }
+    ka.heap[q] = peer_[q];
+  }
+  ka.host_status = host_status_dev_;
+  for (int lr = 0; lr < L_; lr++) {
+    if (!in_heap(ca.recvbufs[lr], 1)) {
+      last_error_ = "recvbuf must be allocated from the symmetric heap";
+      return RBV_ERR_BAD_ARG;
+    }
+    ka.recvoff[lr] = static_cast<char*>(ca.recvbufs[lr]) - heap_;
+    ka.sendbuf[lr] = inplace ? nullptr : static_cast<const char*>(ca.sendbufs[lr]);
+  }
+
+  // --- counts / displacements ---
+  const size_t n = (size_t)L_ * P_;
+  long long send_bytes = ca.bytes_hint;
+  if (!ca.counts_on_device) {
+    send_bytes = 0;
+    for (size_t i = 0; i < n; i++) {
+      if (ca.sendcounts[i] < 0 || ca.sdispls[i] < 0 || ca.rdispls[i] < 0 || (ca.recvcounts && ca.recvcounts[i] < 0)) {
+        last_error_ = "negative count or displacement"; return RBV_ERR_BAD_ARG;
+      }
+      send_bytes += (long long)ca.sendcounts[i] * ts;
+    }
+    if (inplace) {
+      size_t total = 0;
+      for (int lr = 0; lr < L_; lr++) {
+        size_t ext = 0;
+        for (int d = 0; d < P_; d++)
+          ext = std::max(ext, (size_t)(ca.sdispls[(size_t)lr * P_ + d] + ca.sendcounts[(size_t)lr * P_ + d]) * ts);
+        ka.sendcopy_bytes[lr] = ext;
+        total += align_up(ext, 256);
+      }
+      if (total > sendcopy_bytes_) {
+        if (sendcopy_) symm_free(sendcopy_);
+        sendcopy_ = symm_alloc(total);
+        sendcopy_bytes_ = sendcopy_ ? total : 0;
+        if (!sendcopy_) { last_error_ = "symmetric heap exhausted (in-place copy)"; return RBV_ERR_CAPACITY; }
+      }
+      size_t off = static_cast<char*>(sendcopy_) - heap_;
+      for (int lr = 0; lr < L_; lr++) {
+        ka.sendcopy_off[lr] = off;
+        off += align_up(ka.sendcopy_bytes[lr], 256);
+      }
+    }
+    if (n <= (size_t)kInlineMeta) {
+      ka.flags |= CALL_META_INLINE;
+      for (size_t i = 0; i < n; i++) {
+        ka.inl.sendcounts[i] = ca.sendcounts[i];
+        ka.inl.recvcounts[i] = ca.recvcounts ? ca.recvcounts[i] : -1;
+        ka.inl.sdispls[i] = ca.sdispls[i];
+        ka.inl.rdispls[i] = ca.rdispls[i];
+      }
+    } else {
+      const size_t need = n * (4 + 4 + 8 + 8);
+      if (need > ring_bytes_) {
+        for (int i = 0; i < kRing; i++) {
+          if (ring_ev_[i]) cudaEventSynchronize(ring_ev_[i]);
+          if (ring_host_[i]) cudaFreeHost(ring_host_[i]);
+          if (ring_dev_[i]) cudaFree(ring_dev_[i]);
+          RBV_CUDA_THROW(cudaHostAlloc(&ring_host_[i], need, cudaHostAllocDefault));
+          RBV_CUDA_THROW(cudaMalloc(&ring_dev_[i], need));
+          if (!ring_ev_[i]) RBV_CUDA_THROW(cudaEventCreateWithFlags(&ring_ev_[i], cudaEventDisableTiming));
+        }
+        ring_bytes_ = need;
+      }
+      const int slot = ring_next_;
+      ring_next_ = (ring_next_ + 1) % kRing;
+      RBV_CUDA_THROW(cudaEventSynchronize(ring_ev_[slot]));
+      char* h = ring_host_[slot];
+      long long* h_sd = reinterpret_cast<long long*>(h);
+      long long* h_rd = h_sd + n;
+      int* h_sc = reinterpret_cast<int*>(h_rd + n);
+      int* h_rc = h_sc + n;
+      for (size_t i = 0; i < n; i++) {
+        h_sd[i] = ca.sdispls[i]; h_rd[i] = ca.rdispls[i];
+        h_sc[i] = ca.sendcounts[i]; h_rc[i] = ca.recvcounts ? ca.recvcounts[i] : -1;
+      }
+      RBV_CUDA_THROW(cudaMemcpyAsync(ring_dev_[slot], h, need, cudaMemcpyHostToDevice, stream));
+      RBV_CUDA_THROW(cudaEventRecord(ring_ev_[slot], stream));
+      long long* d_sd = reinterpret_cast<long long*>(ring_dev_[slot]);
+      int* d_sc = reinterpret_cast<int*>(d_sd + 2 * n);
+      ka.sdispls = d_sd;
+      ka.rdispls = d_sd + n;
+      ka.sendcounts = d_sc;
+      ka.recvcounts = d_sc + n;
+    }
+  } else {
+    ka.sendcounts = ca.sendcounts; ka.recvcounts = ca.recvcounts;
+    ka.sdispls = ca.sdispls; ka.rdispls = ca.rdispls;
+  }
+
+  // --- launch shape ---
+  // Bytes this process moves, counting forwarded hops (a relay moves other ranks' blocks of
+  // about the same size).
+  double hop_factor = dp->nops > 0 ? (double)dp->nops / (double)((size_t)L_ * P_) : 1.0;
+  double work = send_bytes >= 0 ? (double)send_bytes * std::max(1.0, hop_factor) : -1.0;
+  unsigned long long chunk = opt.chunk_bytes;
+  int grid = opt.grid;
+  if (!chunk) {
+    if (work < 0) chunk = 64 << 10;
+    else {
+      // aim at ~4 chunks per CTA at full grid, within [16 KB, 512 KB]
+      double c = work / (4.0 * max_ctas_);
+      chunk = (unsigned long long)std::min(512.0 * 1024, std::max(16.0 * 1024, c));
+      chunk = align_up(chunk, 4096);
+    }
+  }
+  chunk = align_up(chunk, 16);
+  if (grid <= 0) {
+    if (work < 0) grid = max_ctas_;
+    else {
+      double chunks = work / (double)chunk + dp->nops;
+      grid = (int)std::min<double>(max_ctas_, std::max<double>(1.0, chunks));
+    }
+  }
+  grid = std::max(1, std::min(grid, max_ctas_));
+  ka.chunk_bytes = chunk;
+
+  cudaError_t e = a2av_launch(ka, grid, stream);
+  if (e != cudaSuccess) {
+    last_error_ = std::string("kernel launch failed: ") + cudaGetErrorString(e);
+    return RBV_ERR_BAD_ARG;
+  }
+  seq_++;
+  return 0;
+}
+
+StatusBlock Context::status(cudaStream_t stream) {
+  cudaStreamSynchronize(stream);
+  return *host_status_;
+}
+
+cudaError_t Context::reset() {
+  cudaError_t e = cudaSetDevice(device_);
+  if (e != cudaSuccess) return e;
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return e;
+  e = cudaMemset(heap_, 0, lay_.stage_off);
+  if (e != cudaSuccess) return e;
+  for (auto& kv : plans_)
+    if (kv.second->d_done) cudaMemset(kv.second->d_done, 0, kv.second->nops * sizeof(unsigned));
+  seq_ = 0;
+  std::memset(host_status_, 0, sizeof(StatusBlock));
+  return cudaDeviceSynchronize();
+}
+
+}  // namespace rbv

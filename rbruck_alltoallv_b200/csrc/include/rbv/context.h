@@ -1,0 +1,119 @@
+// Host runtime: one Context per process (one GPU).  It owns the symmetric heap, the peer mappings
+// obtained through CUDA IPC, the device copies of compiled plans and the call sequence number.
+// It stands in for what the MPI runtime and MPI_Comm_split provide in the reference
+// (groups are index arithmetic on ranks; no sub-communicator is ever created).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "rbv/device_types.h"
+#include "rbv/plan.h"
+
+namespace rbv {
+
+struct DevPlan {
+  Plan plan;               // host copy (all ranks)
+  Op* d_ops = nullptr;     // ops of this process's ranks
+  unsigned* d_done = nullptr;
+  int nops = 0;
+};
+
+struct CallOptions {
+  int grid = 0;                       // CTAs; 0 = choose
+  unsigned long long chunk_bytes = 0; // 0 = choose
+  unsigned flags = 0;                 // CALL_INPLACE
+};
+
+// Arguments of one collective call for all L local ranks.  Count arrays are [L][P].
+struct CallArgs {
+  const void* const* sendbufs = nullptr;   // [L] device pointers (ignored for in-place calls)
+  void* const* recvbufs = nullptr;         // [L] device pointers inside the symmetric heap
+  const int* sendcounts = nullptr;
+  const int* recvcounts = nullptr;         // may be null
+  const long long* sdispls = nullptr;
+  const long long* rdispls = nullptr;
+  bool counts_on_device = false;           // the four arrays are device memory
+  long long bytes_hint = -1;               // total bytes sent by this process, if known (device counts)
+};
+
+class Context {
+ public:
+  Context(int P, int nproc, int proc, int device, size_t user_bytes, size_t arena_bytes);
+  ~Context();
+  Context(const Context&) = delete;
+
+  int P() const { return P_; }
+  int L() const { return L_; }
+  int nproc() const { return nproc_; }
+  int proc() const { return proc_; }
+  int device() const { return device_; }
+  unsigned seq() const { return seq_; }
+  const HeapLayout& layout() const { return lay_; }
+  char* heap() const { return heap_; }
+  char* peer_heap(int q) const { return peer_[q]; }
+  int max_ctas() const { return max_ctas_; }
+  int sm_count() const { return sm_count_; }
+
+  cudaError_t ipc_handle(void* out64);
+  cudaError_t connect(const void* handles);  // nproc x 64 bytes, in process order
+
+  void* symm_alloc(size_t bytes);
+  int symm_free(void* p);
+  bool in_heap(const void* p, size_t bytes) const;
+
+  // Launches the collective on `stream`.  Returns 0, the plan's error code (< 0), or a positive
+  // Status for argument errors detected on the host.  Device-side errors are reported by status().
+  int alltoallv(const AlgoSpec& spec, int type_size, const CallArgs& args, const CallOptions& opt,
+                cudaStream_t stream);
+
+  // Status of the most recent call; synchronises `stream` first.
+  StatusBlock status(cudaStream_t stream);
+  // Clears all synchronisation state.  Every process must call it between the same two calls,
+  // with a host barrier before and after.
+  cudaError_t reset();
+  void set_timeout_ns(unsigned long long ns) { timeout_ns_ = ns; }
+  // Fault injection for tests: the given local rank skips its metadata row in the next calls (-1: off).
+  void set_absent_rank(int lr) { absent_rank_ = lr; }
+  const std::string& last_error() const { return last_error_; }
+  const DevPlan* plan_for(const AlgoSpec& spec);
+
+ private:
+  int P_, L_, nproc_, proc_, device_;
+  HeapLayout lay_{};
+  char* heap_ = nullptr;
+  char* peer_[kMaxProcs] = {};
+  bool opened_[kMaxProcs] = {};
+  unsigned seq_ = 0;
+  int absent_rank_ = -1;
+  unsigned long long timeout_ns_ = 2000000000ull;
+  int max_ctas_ = 1, sm_count_ = 1;
+  StatusBlock* host_status_ = nullptr;
+  StatusBlock* host_status_dev_ = nullptr;
+  std::string last_error_;
+  std::map<std::tuple<int, int, int, int, int, int, int>, std::unique_ptr<DevPlan>> plans_;
+  // free list of the user region: offset -> size
+  std::map<size_t, size_t> free_;
+  std::map<size_t, size_t> used_;
+  // staging ring for host-side count arrays that do not fit in the kernel parameters
+  static constexpr int kRing = 4;
+  char* ring_host_[kRing] = {};
+  char* ring_dev_[kRing] = {};
+  cudaEvent_t ring_ev_[kRing] = {};
+  size_t ring_bytes_ = 0;
+  int ring_next_ = 0;
+  // private copies for in-place calls
+  void* sendcopy_ = nullptr;
+  size_t sendcopy_bytes_ = 0;
+};
+
+// implemented in kernels/a2av_kernel.cu
+size_t a2av_smem_bytes(int P);
+cudaError_t a2av_configure(int P, int* max_ctas_per_sm);
+cudaError_t a2av_launch(const KernelArgs& args, int grid, cudaStream_t stream);
+
+}  // namespace rbv

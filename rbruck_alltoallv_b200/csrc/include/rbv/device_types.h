@@ -1,0 +1,130 @@
+// Structures shared by the host runtime and the device kernels.
+//
+// Execution model.  A *context* is one process driving one GPU.  It hosts L consecutive logical
+// ranks of a P-rank communicator (L = P / nproc).  L = 1 is the production layout (one rank per
+// GPU); L = P runs a whole communicator inside one kernel on one GPU, which is how the multi-rank
+// logic is exercised where only one GPU is available and how a fixed P-rank problem is spread
+// over fewer GPUs.  The kernels never distinguish the two: a rank's memory is reached through
+// `heap[proc_of(rank)]`, which is either this GPU's heap or a peer mapping over NVLink.
+//
+// Every context owns one "symmetric heap" with the same internal layout on all processes:
+//
+//   [ CtrlBlock | cell flags | metadata tables x2 | staging arenas (L ranks x 2 parities) | user ]
+//
+// Cross-rank synchronisation uses monotonic counters and sequence-stamped flags only, so nothing
+// has to be reset between calls:
+//   * meta_arrivals[parity]      += 1 per published metadata row      (target: calls_on_parity * P)
+//   * recv_arrivals[local rank]  += 1 per block landed in recvbuf      (target: (seq + 1) * P)
+//   * cell_flag[parity][lr][c]    = seq + 1 when staging cell c holds this call's block
+// Staging arenas, cell flags and metadata tables alternate by call parity: a peer can run at most
+// one call ahead (it cannot finish call c+1 without data this rank sends in call c+1), so two
+// copies suffice.
+#pragma once
+#include <cstdint>
+
+#include "rbv/plan.h"
+
+namespace rbv {
+
+constexpr int kMaxRanks = 64;         // logical ranks per communicator
+constexpr int kMaxProcs = 16;         // processes (GPUs) per communicator
+constexpr int kMaxCellsPerRank = 2048;
+constexpr int kInlineMeta = 64;       // L * P up to this many count/displacement entries travel as kernel parameters
+constexpr int kThreads = 512;
+
+enum Status : int {
+  RBV_OK = 0,
+  RBV_ERR_TIMEOUT = 1,    // a bounded wait ran out (peer absent or late)
+  RBV_ERR_BAD_ARG = 2,
+  RBV_ERR_CAPACITY = 3,   // staging arena too small for ncells * max block
+  RBV_ERR_TRUNCATE = 4,   // a block is larger than the receiver's recvcount
+  RBV_ERR_ABORTED = 5,    // another rank reported an error and asked everyone to stop
+};
+
+enum WaitSite : int { WAIT_META = 1, WAIT_CELL = 2, WAIT_RECV = 3 };
+
+struct StatusBlock {
+  int code;        // Status of the first error of the most recent call, 0 if none
+  int site;        // WaitSite for time-outs
+  int detail0;     // op index / local rank / cell, depending on site
+  int detail1;     // peer rank or expected count
+  unsigned long long trace[8];  // %globaltimer stamps of CTA 0: 0 start, 1 metadata published,
+                                // 2 metadata complete, 3 own ops issued, 4 all blocks received
+};
+
+// Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.
+struct CtrlBlock {
+  unsigned long long meta_arrivals[2];
+  unsigned long long recv_arrivals[kMaxRanks];
+  unsigned int abort_flag;       // set locally on error, and by peers that want everyone to stop
+  unsigned int pad0;
+  unsigned int exit_count;       // CTAs that finished the current call (the last one publishes the status)
+  unsigned int pad1;
+  StatusBlock status;
+};
+
+// Byte offsets of the regions of a heap; identical on every process of a communicator.
+struct HeapLayout {
+  unsigned long long ctrl_off;      // CtrlBlock
+  unsigned long long flags_off;     // uint32 cell_flag[2][L][kMaxCellsPerRank]
+  unsigned long long meta_off;      // 2 x MetaTable(P)
+  unsigned long long meta_bytes;    // size of one parity copy
+  unsigned long long stage_off;     // staging arenas: [L][2] x arena_bytes
+  unsigned long long arena_bytes;   // per rank per parity
+  unsigned long long user_off;      // user allocations
+  unsigned long long total_bytes;
+};
+
+// One parity copy of the metadata tables (sizes depend on P):
+//   int32  counts[P][P]   row s written by rank s: what s sends to each d
+//   int32  caps  [P][P]   row d written by rank d: recvcounts of d per source, -1 = unchecked
+//   int64  rdispl[P][P]   row d written by rank d, in elements
+//   uint64 recvoff[P]     offset of rank d's recvbuf inside its process's heap
+__host__ __device__ inline unsigned long long meta_counts_off(int P) { (void)P; return 0; }
+__host__ __device__ inline unsigned long long meta_caps_off(int P) { return 4ull * P * P; }
+__host__ __device__ inline unsigned long long meta_rdispl_off(int P) { return 8ull * P * P; }
+__host__ __device__ inline unsigned long long meta_recvoff_off(int P) { return 16ull * P * P; }
+__host__ __device__ inline unsigned long long meta_table_bytes(int P) {
+  return (16ull * P * P + 8ull * P + 255) & ~255ull;
+}
+
+enum CallFlags : unsigned {
+  CALL_INPLACE = 1u,      // send data is taken from recvbuf (copied to a private region first)
+  CALL_META_INLINE = 2u,  // counts/displacements are in KernelArgs::inl, not behind the pointers
+};
+
+struct InlineMeta {
+  int sendcounts[kInlineMeta];
+  int recvcounts[kInlineMeta];
+  long long sdispls[kInlineMeta];
+  long long rdispls[kInlineMeta];
+};
+
+struct KernelArgs {
+  int P, L, nproc, proc;
+  int type_size;
+  unsigned seq;            // 0-based call number on this communicator
+  unsigned flags;
+  int nops;                // ops executed by this process
+  int absent_rank;         // fault injection for tests: this local rank never publishes its metadata (-1: none)
+  int ncells;
+  const Op* ops;           // device copy of the process's op list
+  unsigned* op_done;       // [nops] completion counters of multi-chunk ops (zero between calls)
+  unsigned long long chunk_bytes;
+  unsigned long long timeout_ns;
+  HeapLayout lay;
+  char* heap[kMaxProcs];   // heap base of every process as mapped in this process
+  const char* sendbuf[kMaxRanks];         // per local rank (any device memory of this GPU)
+  unsigned long long recvoff[kMaxRanks];  // per local rank: recvbuf offset in this process's heap
+  unsigned long long sendcopy_off[kMaxRanks];  // CALL_INPLACE: private copy location (heap offset)
+  unsigned long long sendcopy_bytes[kMaxRanks];
+  // device arrays [L][P]; recvcounts may be null (no truncation check)
+  const int* sendcounts;
+  const int* recvcounts;
+  const long long* sdispls;
+  const long long* rdispls;
+  StatusBlock* host_status;  // pinned, mapped: a copy of the final status
+  InlineMeta inl;
+};
+
+}  // namespace rbv

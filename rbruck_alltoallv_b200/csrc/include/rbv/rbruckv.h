@@ -1,0 +1,150 @@
+/* Public C API.
+ *
+ * The collective entry points keep the names, argument order and return conventions of the
+ * reference's src/rbruckv.h:20-96 (including the `exclisive_or_alltoallv` spelling).  Two types
+ * change: MPI_Datatype becomes rbv_datatype (the element size in bytes, which is all the reference
+ * ever reads from a datatype) and MPI_Comm becomes rbv_comm_t.  Buffers are device pointers;
+ * receive buffers come from rbv_symm_alloc(), count / displacement arrays are host arrays in
+ * elements, exactly as with MPI_Alltoallv.
+ *
+ * Process model: one process per GPU creates one rbv_ctx_t; the context hosts L = nranks / nproc
+ * logical ranks and hands out one rbv_comm_t per local rank.  A collective is called once per
+ * local rank, like an SPMD program would; the kernel is launched when the last local rank of the
+ * process has made its call (L = 1: immediately).  Calls are asynchronous on the context's stream.
+ *
+ * Return codes: 0 success; -1 invalid radix / rank count (as the reference); -2 invalid group size
+ * (the reference calls MPI_Abort there); > 0 an rbv_status detected on the host.  Errors detected
+ * on the device (time-out, truncation, staging capacity) are read with rbv_ctx_status().
+ */
+#ifndef RBV_RBRUCKV_H_
+#define RBV_RBRUCKV_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+#include <vector>
+extern "C" {
+#endif
+
+typedef struct rbv_ctx_s* rbv_ctx_t;
+typedef struct rbv_comm_s* rbv_comm_t;
+typedef int rbv_datatype; /* element size in bytes */
+
+#define RBV_CHAR 1
+#define RBV_BF16 2
+#define RBV_INT 4
+#define RBV_FLOAT 4
+#define RBV_LONG_LONG 8
+#define RBV_UNSIGNED_LONG_LONG 8
+#define RBV_DOUBLE 8
+#define RBV_COMPLEX64 8
+
+typedef struct rbv_status_s {
+  int code;    /* 0 ok, 1 time-out, 2 bad argument, 3 staging capacity, 4 truncation, 5 aborted by a peer */
+  int site;    /* for time-outs: 1 metadata, 2 staging cell, 3 final arrival */
+  int detail0;
+  int detail1;
+  unsigned long long trace[8]; /* device clock (ns): start, metadata published, metadata complete,
+                                  own transfers issued, all blocks received */
+} rbv_status;
+
+/* ---- context / communicator ---- */
+rbv_ctx_t rbv_ctx_create(int nranks, int nproc, int proc, int device, size_t user_bytes, size_t arena_bytes);
+void rbv_ctx_destroy(rbv_ctx_t ctx);
+const char* rbv_last_error(void);
+int rbv_ctx_ipc_handle(rbv_ctx_t ctx, void* out64);
+int rbv_ctx_connect(rbv_ctx_t ctx, const void* handles);
+void rbv_ctx_set_stream(rbv_ctx_t ctx, void* cuda_stream);
+void rbv_ctx_set_timeout_ms(rbv_ctx_t ctx, double ms);
+void rbv_ctx_set_launch(rbv_ctx_t ctx, int grid, size_t chunk_bytes); /* 0 = automatic */
+void rbv_ctx_set_absent_rank(rbv_ctx_t ctx, int local_rank); /* test hook: rank skips the metadata phase; -1 off */
+int rbv_ctx_sync(rbv_ctx_t ctx);
+int rbv_ctx_status(rbv_ctx_t ctx, rbv_status* out); /* synchronises the stream */
+int rbv_ctx_reset(rbv_ctx_t ctx);
+int rbv_ctx_info(rbv_ctx_t ctx, long long* out8); /* P, L, nproc, proc, device, seq, max_ctas, sm_count */
+void* rbv_ctx_heap(rbv_ctx_t ctx, int proc);
+void* rbv_symm_alloc(rbv_ctx_t ctx, size_t bytes);
+int rbv_symm_free(rbv_ctx_t ctx, void* ptr);
+rbv_comm_t rbv_comm(rbv_ctx_t ctx, int local_rank);
+int rbv_comm_rank(rbv_comm_t comm);
+int rbv_comm_size(rbv_comm_t comm);
+
+/* Generic entry: all local ranks at once.  Arrays are [L] pointers and [L][P] counts
+ * (64-bit displacements); `counts_on_device` != 0 means the four count arrays are device memory.
+ * algo is an rbv::Algo value. */
+int rbv_alltoallv(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
+                  const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
+                  const int* recvcounts, const long long* sdispls, const long long* rdispls,
+                  int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes,
+                  void* cuda_stream);
+
+/* Phase timers of the most recent call, filled by rbv_update_timers() (which synchronises).
+ * Names as in the reference (src/rbruckv.h:13-18); phases that no longer exist as separate steps
+ * (pack, unpack, organise) stay 0. */
+extern double init_time, findMax_time, rotateIndex_time, alcCopy_time, getBlock_time, prepData_time,
+    excgMeta_time, excgData_time, replace_time, orgData_time, prepSP_time, SP_time;
+extern double intra_time;
+extern double* iteration_time;
+int rbv_update_timers(rbv_ctx_t ctx);
+
+/* ---- helpers (src/utils.cpp) ---- */
+int myPow(int x, unsigned int p);
+int check_errors(int* recvcounts, long long* recv_buffer, int rank, int nprocs); /* host buffer */
+
+/* ---- collectives, one call per local rank ---- */
+int twophase_rbruck_alltoallv(int r, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                              char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int twophase_rbruck_alltoallv_om(int r, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                                 char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int tuna_algorithm(int r, int b, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                   char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int tuna2_algorithm(int r, int b, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                    char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int uniform_spreadout_twolayer(int n, int r, char* sendbuf, int sendcount, rbv_datatype sendtype, char* recvbuf,
+                               int recvcount, rbv_datatype recvtype, rbv_comm_t comm);
+void uniform_inverse_isplit_r_bruck(int n, int r1, int r2, char* sendbuf, int sendcount, rbv_datatype sendtype,
+                                    char* recvbuf, int recvcount, rbv_datatype recvtype, rbv_comm_t comm);
+int TTPL_rbruck_alltoallv(int n, int r, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                          char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int TTPL_BT_alltoallv(int n, int r, int bblock, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                      char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int TTPL_BT_alltoallv_s1(int n, int r, int bblock, char* sendbuf, int* sendcounts, int* sdispls,
+                         rbv_datatype sendtype, char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype,
+                         rbv_comm_t comm);
+int TTPL_BT_alltoallv_s2(int n, int r, int bblock, char* sendbuf, int* sendcounts, int* sdispls,
+                         rbv_datatype sendtype, char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype,
+                         rbv_comm_t comm);
+int MPICH_intra_scattered(int bblock, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                          char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int ompi_alltoallv_intra_basic_linear(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                                      char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype,
+                                      rbv_comm_t comm);
+int ompi_alltoallv_intra_pairwise(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                                  int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int exclisive_or_alltoallv(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                           int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int exclusive_or_alltoallv(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                           int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int twolayer_communicator_linear(int n, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                                 char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int twolayer_communicator_linear_s2(int n, int bblock1, int bblock2, char* sendbuf, int* sendcounts, int* sdispls,
+                                    rbv_datatype sendtype, char* recvbuf, int* recvcounts, int* rdispls,
+                                    rbv_datatype recvtype, rbv_comm_t comm);
+int twolayer_communicator_linear_s3(int n, int bblock1, int bblock2, char* sendbuf, int* sendcounts, int* sdispls,
+                                    rbv_datatype sendtype, char* recvbuf, int* recvcounts, int* rdispls,
+                                    rbv_datatype recvtype, rbv_comm_t comm);
+int twolayer_communicator_linear_s4(int n, int bblock1, int bblock2, char* sendbuf, int* sendcounts, int* sdispls,
+                                    rbv_datatype sendtype, char* recvbuf, int* recvcounts, int* rdispls,
+                                    rbv_datatype recvtype, rbv_comm_t comm);
+/* Declared but never defined in the reference (src/rbruckv.h:80-81); here: the automatic choice. */
+int ML_benchmark(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf, int* recvcounts,
+                 int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+void spreadout_alltoallv(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                         int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+
+#ifdef __cplusplus
+} /* extern "C" */
+std::vector<int> convert10tob(int w, int N, int b);
+#endif
+
+#endif /* RBV_RBRUCKV_H_ */

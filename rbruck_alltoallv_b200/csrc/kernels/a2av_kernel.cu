@@ -1,0 +1,358 @@
+// The alltoallv kernel: one persistent cooperative launch per call and per process that performs
+//   (1) the metadata phase  -- every rank stores its sendcounts / recvcounts / rdispls row and its
+//       receive-buffer offset into every process's metadata table and bumps an arrival counter
+//       (this replaces the host-side MPI_Alltoall of counts in the reference's drivers, the
+//       MPI_Allreduce(MAX) and the per-round metadata MPI_Sendrecv, e.g. src/tuna2.cpp:45,160),
+//   (2) the data phase      -- an interpreter of the plan's op list: each op copies one block from
+//       the executing rank's send buffer or staging cell straight into the destination rank's
+//       receive buffer or staging cell (a peer mapping over NVLink when the destination lives on
+//       another GPU); rotation, pack, unpack and final placement are folded into the addressing,
+//   (3) completion          -- waits until all P blocks of every local rank have landed.
+//
+// Work distribution: ops are cut into chunks of `chunk_bytes`; chunk c of the process-wide
+// sequence is handled by CTA c mod gridDim.  CTAs walk their chunks in plan order, so a wait on a
+// staging cell only ever depends on chunks of an earlier plan key, which rules out cycles as long
+// as all CTAs are resident (cooperative launch).
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+
+#include "kernels/primitives.cuh"
+#include "rbv/device_types.h"
+
+namespace cg = cooperative_groups;
+
+namespace rbv {
+
+namespace {
+
+constexpr int kOpTile = 1024;
+
+struct Smem {
+  // dynamic layout: int counts[P*P]; int caps[P*P]; long long rdispl[P*P]; ull recvoff[P];
+  // then unsigned prefix[kOpTile + 1]
+  int* counts;
+  int* caps;
+  long long* rdispl;
+  unsigned long long* recvoff;
+  unsigned* prefix;
+};
+
+__device__ __forceinline__ CtrlBlock* ctrl_of(const KernelArgs& a, int proc) {
+  return reinterpret_cast<CtrlBlock*>(a.heap[proc] + a.lay.ctrl_off);
+}
+__device__ __forceinline__ unsigned* cell_flag_of(const KernelArgs& a, int proc, int parity, int lr, int cell) {
+  return reinterpret_cast<unsigned*>(a.heap[proc] + a.lay.flags_off) +
+         ((size_t)(parity * a.L + lr) * kMaxCellsPerRank + cell);
+}
+__device__ __forceinline__ char* meta_of(const KernelArgs& a, int proc, int parity) {
+  return a.heap[proc] + a.lay.meta_off + (size_t)parity * a.lay.meta_bytes;
+}
+__device__ __forceinline__ char* stage_of(const KernelArgs& a, int proc, int parity, int lr) {
+  return a.heap[proc] + a.lay.stage_off + (size_t)(lr * 2 + parity) * a.lay.arena_bytes;
+}
+
+__device__ void report_error(const KernelArgs& a, int code, int site, int d0, int d1) {
+  CtrlBlock* c = ctrl_of(a, a.proc);
+  if (atomicCAS(&c->status.code, 0, code) == 0) {
+    c->status.site = site;
+    c->status.detail0 = d0;
+    c->status.detail1 = d1;
+  }
+  __threadfence();
+  dev::st_relaxed_sys(&c->abort_flag, 1u);
+  // ask the other processes to stop waiting as well
+  for (int q = 0; q < a.nproc; q++)
+    if (q != a.proc) dev::st_relaxed_sys(&ctrl_of(a, q)->abort_flag, 1u);
+}
+
+__device__ __forceinline__ const int* in_sendcounts(const KernelArgs& a) {
+  return (a.flags & CALL_META_INLINE) ? a.inl.sendcounts : a.sendcounts;
+}
+__device__ __forceinline__ const int* in_recvcounts(const KernelArgs& a) {
+  return (a.flags & CALL_META_INLINE) ? a.inl.recvcounts : a.recvcounts;
+}
+__device__ __forceinline__ const long long* in_sdispls(const KernelArgs& a) {
+  return (a.flags & CALL_META_INLINE) ? a.inl.sdispls : a.sdispls;
+}
+__device__ __forceinline__ const long long* in_rdispls(const KernelArgs& a) {
+  return (a.flags & CALL_META_INLINE) ? a.inl.rdispls : a.rdispls;
+}
+
+// Metadata rows of local rank lr go to process q: one warp per (lr, q) pair.
+__device__ void publish_metadata(const KernelArgs& a) {
+  const int P = a.P, parity = a.seq & 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const bool have_rc = (a.flags & CALL_META_INLINE) ? true : (a.recvcounts != nullptr);
+  for (int pair = warp; pair < a.L * a.nproc; pair += nwarps) {
+    const int lr = pair / a.nproc, q = pair % a.nproc;
+    if (lr == a.absent_rank) continue;  // host-injected fault: the rank "never joins"
+    const int me = a.proc * a.L + lr;
+    char* mt = meta_of(a, q, parity);
+    int* counts = reinterpret_cast<int*>(mt + meta_counts_off(P)) + (size_t)me * P;
+    int* caps = reinterpret_cast<int*>(mt + meta_caps_off(P)) + (size_t)me * P;
+    long long* rd = reinterpret_cast<long long*>(mt + meta_rdispl_off(P)) + (size_t)me * P;
+    unsigned long long* ro = reinterpret_cast<unsigned long long*>(mt + meta_recvoff_off(P)) + me;
+    const int* sc = in_sendcounts(a) + (size_t)lr * P;
+    const int* rc = in_recvcounts(a);
+    const long long* rdi = in_rdispls(a) + (size_t)lr * P;
+    for (int i = lane; i < P; i += 32) {
+      counts[i] = sc[i];
+      caps[i] = (have_rc && rc) ? rc[(size_t)lr * P + i] : -1;
+      rd[i] = rdi[i];
+    }
+    if (lane == 0) *ro = a.recvoff[lr];
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_system();
+      dev::red_release_sys_add(&ctrl_of(a, q)->meta_arrivals[parity], 1ull);
+    }
+  }
+}
+
+__device__ __forceinline__ size_t op_bytes(const Op& o, const Smem& sm, int P, int ts) {
+  return (size_t)sm.counts[(size_t)o.origin * P + o.dest] * (size_t)ts;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant__ KernelArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int s_flag;
+  __shared__ unsigned s_total;
+  const int P = a.P, L = a.L, ts = a.type_size;
+  const int parity = a.seq & 1;
+  const int tid = threadIdx.x;
+  CtrlBlock* my = ctrl_of(a, a.proc);
+  dev::WaitCfg wc{&my->abort_flag, a.timeout_ns};
+
+  Smem sm;
+  {
+    unsigned char* p = smem_raw;
+    sm.rdispl = reinterpret_cast<long long*>(p); p += 8ull * P * P;
+    sm.recvoff = reinterpret_cast<unsigned long long*>(p); p += 8ull * P;
+    sm.counts = reinterpret_cast<int*>(p); p += 4ull * P * P;
+    sm.caps = reinterpret_cast<int*>(p); p += 4ull * P * P;
+    sm.prefix = reinterpret_cast<unsigned*>(p);
+  }
+
+  if (blockIdx.x == 0 && tid == 0) my->status.trace[0] = dev::globaltimer();
+
+  // ---- in-place calls: move the send data out of recvbuf before anyone may write into it ----
+  if (a.flags & CALL_INPLACE) {
+    for (int lr = 0; lr < L; lr++) {
+      const size_t n = a.sendcopy_bytes[lr];
+      const size_t per = ((n + gridDim.x - 1) / gridDim.x + 15) & ~(size_t)15;
+      const size_t lo = (size_t)blockIdx.x * per;
+      if (lo < n) {
+        const size_t len = (lo + per <= n) ? per : n - lo;
+        dev::cta_copy(a.heap[a.proc] + a.sendcopy_off[lr] + lo, a.heap[a.proc] + a.recvoff[lr] + lo, len);
+      }
+    }
+    __threadfence();
+    cg::this_grid().sync();
+  }
+
+  // ---- (1) metadata phase ----
+  if (blockIdx.x == 0) {
+    publish_metadata(a);
+    if (tid == 0) my->status.trace[1] = dev::globaltimer();
+  }
+  if (tid == 0) {
+    const unsigned long long target = ((unsigned long long)(a.seq >> 1) + 1ull) * (unsigned long long)P;
+    int r = dev::wait_ge(&my->meta_arrivals[parity], target, wc);
+    if (r == dev::WAIT_TIMEOUT) report_error(a, RBV_ERR_TIMEOUT, WAIT_META, (int)my->meta_arrivals[parity], (int)target);
+    s_flag = r;
+  }
+  __syncthreads();
+  bool alive = (s_flag == dev::WAIT_OK);
+  __syncthreads();
+
+  size_t stride = 0;
+  if (alive) {
+    const char* mt = meta_of(a, a.proc, parity);
+    const int* gc = reinterpret_cast<const int*>(mt + meta_counts_off(P));
+    const int* gk = reinterpret_cast<const int*>(mt + meta_caps_off(P));
+    const long long* gr = reinterpret_cast<const long long*>(mt + meta_rdispl_off(P));
+    const unsigned long long* go = reinterpret_cast<const unsigned long long*>(mt + meta_recvoff_off(P));
+    int mx = 0;
+    for (int i = tid; i < P * P; i += blockDim.x) {
+      int c = __ldcg(gc + i);
+      sm.counts[i] = c;
+      sm.caps[i] = __ldcg(gk + i);
+      sm.rdispl[i] = __ldcg(gr + i);
+      mx = max(mx, c);
+    }
+    for (int i = tid; i < P; i += blockDim.x) sm.recvoff[i] = __ldcg(go + i);
+    // global max block -> staging cell stride (the reference's max_send_count allreduce)
+    mx = __reduce_max_sync(0xffffffffu, mx);
+    if (tid == 0) s_flag = 0;
+    __syncthreads();
+    if ((tid & 31) == 0) atomicMax(&s_flag, mx);
+    __syncthreads();
+    stride = (((size_t)s_flag * ts) + 15) & ~(size_t)15;
+    __syncthreads();
+    if (a.ncells > 0 && stride * (size_t)a.ncells > a.lay.arena_bytes) {
+      if (blockIdx.x == 0 && tid == 0)
+        report_error(a, RBV_ERR_CAPACITY, 0, a.ncells, (int)(stride >> 10));
+      alive = false;
+    }
+    if (blockIdx.x == 0 && tid == 0) my->status.trace[2] = dev::globaltimer();
+  }
+
+  // ---- (2) data phase ----
+  unsigned base = 0;  // chunks before the current tile
+  for (int t0 = 0; t0 < a.nops; t0 += kOpTile) {
+    const int tn = min(kOpTile, a.nops - t0);
+    // chunks per op of this tile, then an exclusive scan (tile sizes are small: serial per warp 0)
+    for (int i = tid; i < tn; i += blockDim.x) {
+      const Op o = a.ops[t0 + i];
+      size_t b = alive ? op_bytes(o, sm, P, ts) : 0;
+      unsigned nch = (unsigned)((b + a.chunk_bytes - 1) / a.chunk_bytes);
+      sm.prefix[i + 1] = nch ? nch : 1u;   // empty blocks still signal their arrival
+    }
+    __syncthreads();
+    if (tid < 32) {
+      unsigned carry = 0;
+      if (tid == 0) sm.prefix[0] = 0;
+      for (int i0 = 0; i0 < tn; i0 += 32) {
+        int i = i0 + tid;
+        unsigned v = (i < tn) ? sm.prefix[i + 1] : 0u;
+        unsigned s = v;
+        #pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          unsigned n = __shfl_up_sync(0xffffffffu, s, d);
+          if (tid >= d) s += n;
+        }
+        if (i < tn) sm.prefix[i + 1] = s + carry;
+        carry += __shfl_sync(0xffffffffu, s, 31);
+      }
+      if (tid == 0) s_total = carry;
+    }
+    __syncthreads();
+    const unsigned total = s_total;
+
+    // first chunk of this tile owned by this CTA
+    unsigned c = (blockIdx.x + gridDim.x - (base % gridDim.x)) % gridDim.x;
+    int oi = 0;
+    for (; c < total; c += gridDim.x) {
+      while (sm.prefix[oi + 1] <= c) oi++;   // ops are visited in order: monotone search
+      const Op o = a.ops[t0 + oi];
+      const unsigned k = c - sm.prefix[oi];
+      const unsigned nch = sm.prefix[oi + 1] - sm.prefix[oi];
+      const int lsrc = o.src - a.proc * L;
+      const int dproc = o.dst / L, ldst = o.dst - dproc * L;
+      bool ok = alive;
+      size_t bytes = ok ? op_bytes(o, sm, P, ts) : 0;
+
+      // truncation check for blocks that go to a receive buffer
+      if (ok && o.dst_cell < 0) {
+        const int cap = sm.caps[(size_t)o.dst * P + o.origin];
+        if (cap >= 0 && sm.counts[(size_t)o.origin * P + o.dest] > cap) {
+          if (tid == 0 && k == 0) report_error(a, RBV_ERR_TRUNCATE, 0, o.origin, o.dest);
+          bytes = 0;
+        }
+      }
+      // wait for the source cell
+      if (ok && o.src_cell >= 0) {
+        if (tid == 0) {
+          int r = dev::wait_ge(cell_flag_of(a, a.proc, parity, lsrc, o.src_cell), a.seq + 1u, wc);
+          if (r == dev::WAIT_TIMEOUT) report_error(a, RBV_ERR_TIMEOUT, WAIT_CELL, t0 + oi, o.src_cell);
+          s_flag = r;
+        }
+        __syncthreads();
+        if (s_flag != dev::WAIT_OK) { ok = false; alive = false; }
+        __syncthreads();
+      }
+      if (ok && bytes) {
+        const size_t off = (size_t)k * a.chunk_bytes;
+        const size_t len = (off + a.chunk_bytes <= bytes) ? (size_t)a.chunk_bytes : bytes - off;
+        const char* src;
+        if (o.src_cell < 0) {
+          const char* sb = (a.flags & CALL_INPLACE) ? (a.heap[a.proc] + a.sendcopy_off[lsrc]) : a.sendbuf[lsrc];
+          src = sb + (size_t)in_sdispls(a)[(size_t)lsrc * P + o.dest] * ts;
+        } else {
+          src = stage_of(a, a.proc, parity, lsrc) + (size_t)o.src_cell * stride;
+        }
+        char* dst;
+        if (o.dst_cell < 0)
+          dst = a.heap[dproc] + sm.recvoff[o.dst] + (size_t)sm.rdispl[(size_t)o.dst * P + o.origin] * ts;
+        else
+          dst = stage_of(a, dproc, parity, ldst) + (size_t)o.dst_cell * stride;
+        dev::cta_copy(dst + off, src + off, len);
+      }
+      __syncthreads();
+      // completion: the CTA that finishes the last chunk of the op signals the destination
+      if (tid == 0) {
+        bool last = true;
+        if (nch > 1) {
+          __threadfence_system();
+          unsigned old = atomicAdd(&a.op_done[t0 + oi], 1u);
+          last = (old == nch - 1);
+          if (last) a.op_done[t0 + oi] = 0;
+        }
+        if (last) {
+          __threadfence_system();
+          if (o.dst_cell < 0)
+            dev::red_release_sys_add(&ctrl_of(a, dproc)->recv_arrivals[ldst], 1ull);
+          else if (ok)
+            dev::st_release_sys(cell_flag_of(a, dproc, parity, ldst, o.dst_cell), a.seq + 1u);
+        }
+      }
+    }
+    base += total;
+    __syncthreads();
+  }
+
+  // ---- (3) completion ----
+  if (blockIdx.x == 0) {
+    if (tid == 0) my->status.trace[3] = dev::globaltimer();
+    if (tid < L) {
+      const unsigned long long target = ((unsigned long long)a.seq + 1ull) * (unsigned long long)P;
+      int r = dev::wait_ge(&my->recv_arrivals[tid], target, wc);
+      if (r == dev::WAIT_TIMEOUT)
+        report_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, tid, (int)(target - my->recv_arrivals[tid]));
+    }
+    __syncthreads();
+    if (tid == 0) my->status.trace[4] = dev::globaltimer();
+  }
+  // The last CTA to leave publishes the status of this call and clears it for the next one.
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
+      my->exit_count = 0;
+      if (my->status.code == 0 && dev::ld_relaxed_sys(&my->abort_flag)) my->status.code = RBV_ERR_ABORTED;
+      __threadfence();
+      if (a.host_status) {
+        *a.host_status = my->status;
+        __threadfence_system();
+      }
+      my->status.code = 0;
+    }
+  }
+}
+
+size_t a2av_smem_bytes(int P) {
+  return 8ull * P * P + 8ull * P + 4ull * P * P * 2 + 4ull * (kOpTile + 1) + 16;
+}
+
+cudaError_t a2av_configure(int P, int* max_ctas_per_sm) {
+  size_t smem = a2av_smem_bytes(P);
+  // The attribute belongs to the kernel, not to a context: size it for the largest communicator so
+  // that contexts with different rank counts can coexist in one process.
+  cudaError_t e = cudaFuncSetAttribute(a2av_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)a2av_smem_bytes(kMaxRanks));
+  if (e != cudaSuccess) return e;
+  int nb = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, a2av_kernel, kThreads, smem);
+  if (max_ctas_per_sm) *max_ctas_per_sm = nb;
+  return e;
+}
+
+cudaError_t a2av_launch(const KernelArgs& args, int grid, cudaStream_t stream) {
+  void* params[] = {(void*)&args};
+  return cudaLaunchCooperativeKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params,
+                                     a2av_smem_bytes(args.P), stream);
+}
+
+}  // namespace rbv

@@ -1,0 +1,153 @@
+// Device primitives: system-scope signal / bounded wait, CTA-wide byte copy for arbitrary alignment.
+//
+// Every wait is bounded by a %globaltimer deadline and also leaves when the context's abort flag
+// is raised; it never traps.  On expiry the caller records a status and the kernel runs to its
+// normal end, so the CUDA context stays usable.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace rbv {
+namespace dev {
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_relaxed_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Result of a bounded wait.
+enum WaitResult : int { WAIT_OK = 0, WAIT_TIMEOUT = 1, WAIT_ABORTED = 2 };
+
+struct WaitCfg {
+  const unsigned* abort_flag;        // local
+  unsigned long long timeout_ns;
+};
+
+template <typename T>
+__device__ __forceinline__ WaitResult wait_ge(const T* p, T target, const WaitCfg& cfg) {
+  if (ld_acquire_sys(p) >= target) return WAIT_OK;
+  unsigned long long t0 = globaltimer();
+  unsigned it = 0;
+  for (;;) {
+    if (ld_acquire_sys(p) >= target) return WAIT_OK;
+    if ((++it & 31u) == 0) {
+      if (ld_relaxed_sys(cfg.abort_flag)) return WAIT_ABORTED;
+      if (globaltimer() - t0 > cfg.timeout_ns) return WAIT_TIMEOUT;
+      __nanosleep(32);
+    }
+  }
+}
+
+// ---- CTA-wide copy ---------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_cg_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_v4(uint4* p, const uint4& v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ unsigned char ld_cg_u8(const unsigned char* p) {
+  unsigned v;
+  asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return (unsigned char)v;
+}
+
+template <int WO>
+__device__ __forceinline__ uint4 shift_words(const uint4& a, const uint4& b, unsigned bits) {
+  // the 16 bytes that start WO words + bits/8 bytes into the 32-byte pair (a, b)
+  const unsigned w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  uint4 o;
+  o.x = __funnelshift_r(w[WO + 0], w[WO + 1], bits);
+  o.y = __funnelshift_r(w[WO + 1], w[WO + 2], bits);
+  o.z = __funnelshift_r(w[WO + 2], w[WO + 3], bits);
+  o.w = __funnelshift_r(w[WO + 3], w[WO + 4], bits);
+  return o;
+}
+
+template <int WO>
+__device__ __forceinline__ void copy_shifted(uint4* d, const uint4* s, size_t nvec, unsigned bits,
+                                             unsigned tid, unsigned nt) {
+  size_t i = tid;
+  for (; i + nt < nvec; i += 2 * (size_t)nt) {
+    uint4 a0 = ld_cg_v4(s + i), b0 = ld_cg_v4(s + i + 1);
+    uint4 a1 = ld_cg_v4(s + i + nt), b1 = ld_cg_v4(s + i + nt + 1);
+    st_v4(d + i, shift_words<WO>(a0, b0, bits));
+    st_v4(d + i + nt, shift_words<WO>(a1, b1, bits));
+  }
+  for (; i < nvec; i += nt) {
+    uint4 a = ld_cg_v4(s + i), b = ld_cg_v4(s + i + 1);
+    st_v4(d + i, shift_words<WO>(a, b, bits));
+  }
+}
+
+// Copies n bytes with all threads of the CTA.  dst and src may have any alignment, relative to
+// each other too: stores are 16-byte aligned vectors, loads are aligned vectors re-assembled with
+// funnel shifts when the two phases differ.  Loads bypass L1 (the source may have been written by
+// another GPU).  The caller synchronises.
+__device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t n) {
+  const unsigned tid = threadIdx.x, nt = blockDim.x;
+  if (n == 0) return;
+  size_t head = (16 - ((uintptr_t)dst & 15)) & 15;
+  if (head > n) head = n;
+  if (tid < head) dst[tid] = (char)ld_cg_u8((const unsigned char*)src + tid);
+  dst += head; src += head; n -= head;
+  const size_t nvec = n >> 4;
+  if (nvec) {
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    const unsigned sh = (unsigned)((uintptr_t)src & 15);
+    if (sh == 0) {
+      const uint4* s = reinterpret_cast<const uint4*>(src);
+      size_t i = tid;
+      for (; i + 3 * (size_t)nt < nvec; i += 4 * (size_t)nt) {
+        uint4 v0 = ld_cg_v4(s + i), v1 = ld_cg_v4(s + i + nt);
+        uint4 v2 = ld_cg_v4(s + i + 2 * nt), v3 = ld_cg_v4(s + i + 3 * nt);
+        st_v4(d + i, v0); st_v4(d + i + nt, v1);
+        st_v4(d + i + 2 * nt, v2); st_v4(d + i + 3 * nt, v3);
+      }
+      for (; i < nvec; i += nt) st_v4(d + i, ld_cg_v4(s + i));
+    } else {
+      const uint4* s = reinterpret_cast<const uint4*>(src - sh);
+      const unsigned bits = (sh & 3u) * 8u;
+      switch (sh >> 2) {
+        case 0: copy_shifted<0>(d, s, nvec, bits, tid, nt); break;
+        case 1: copy_shifted<1>(d, s, nvec, bits, tid, nt); break;
+        case 2: copy_shifted<2>(d, s, nvec, bits, tid, nt); break;
+        default: copy_shifted<3>(d, s, nvec, bits, tid, nt); break;
+      }
+    }
+  }
+  const size_t done = nvec << 4, tail = n - done;
+  if (tid < tail) dst[done + tid] = (char)ld_cg_u8((const unsigned char*)src + done + tid);
+}
+
+}  // namespace dev
+}  // namespace rbv

@@ -1,0 +1,252 @@
+"""Communicator: the Python face of the native context (``csrc/comm/comm.cu``).
+
+One process drives one GPU.  Under ``torchrun`` (``torch.distributed`` initialised) the communicator
+spans all processes and maps every peer's symmetric heap through CUDA IPC; the handles travel over a
+gloo side group, so NCCL is not needed for bootstrap.  Without ``torch.distributed`` the communicator
+lives in one process and hosts all ``nranks`` logical ranks on one GPU.
+
+It replaces what ``MPI_Init`` / ``MPI_Comm`` / ``MPI_Comm_split`` are to the reference: ranks, groups and
+the transport (peer stores over NVLink instead of MPI point-to-point).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import _native
+from .._cuda_decl import SITE_NAMES, STATUS_NAMES, Status
+from .plan import ALGO_ID, Plan
+
+_default_comm: Optional["Communicator"] = None
+
+
+class CommError(RuntimeError):
+    pass
+
+
+class _Block:
+    """Owner of one symmetric-heap allocation, exposed to torch through the CUDA array interface."""
+
+    def __init__(self, comm: "Communicator", nbytes: int):
+        self._comm = comm
+        self.nbytes = int(nbytes)
+        self.ptr = comm._lib.rbv_symm_alloc(comm._ctx, max(self.nbytes, 1))
+        if not self.ptr:
+            raise MemoryError(f"symmetric heap exhausted while allocating {nbytes} bytes "
+                              f"(heap_bytes={comm.heap_bytes})")
+        self.__cuda_array_interface__ = {"shape": (max(self.nbytes, 1),), "typestr": "|u1",
+                                         "data": (self.ptr, False), "version": 3, "strides": None}
+
+    def __del__(self):
+        comm = getattr(self, "_comm", None)
+        if comm is not None and getattr(comm, "_ctx", None) and getattr(self, "ptr", None):
+            comm._lib.rbv_symm_free(comm._ctx, C.c_void_p(self.ptr))
+            self.ptr = None
+
+
+class Communicator:
+    def __init__(self, nranks: Optional[int] = None, device: Optional[int] = None,
+                 heap_bytes: int = 1 << 30, arena_bytes: int = 32 << 20, timeout_ms: float = 2000.0):
+        import torch.distributed as dist
+
+        self._lib = _native.cuda_lib()
+        self._dist = dist if dist.is_available() and dist.is_initialized() else None
+        if self._dist is not None:
+            self.nproc = dist.get_world_size()
+            self.proc = dist.get_rank()
+        else:
+            self.nproc, self.proc = 1, 0
+        if device is None:
+            device = int(os.environ.get("LOCAL_RANK", "0")) if self._dist is not None else torch.cuda.current_device()
+        self.device = int(device)
+        torch.cuda.set_device(self.device)
+        self.P = int(nranks) if nranks else self.nproc
+        if self.P % self.nproc:
+            raise ValueError(f"nranks={self.P} is not a multiple of the process count {self.nproc}")
+        self.L = self.P // self.nproc
+        self.heap_bytes = int(heap_bytes)
+        self.arena_bytes = int(arena_bytes)
+        torch.zeros(1, device=f"cuda:{self.device}")  # make sure the primary context exists
+        self._ctx = C.c_void_p(self._lib.rbv_ctx_create(self.P, self.nproc, self.proc, self.device,
+                                                        self.heap_bytes, self.arena_bytes))
+        if not self._ctx:
+            raise CommError("context creation failed: " + self._lib.rbv_last_error().decode())
+        self._lib.rbv_ctx_set_timeout_ms(self._ctx, float(timeout_ms))
+        self._side = None
+        if self.nproc > 1:
+            self._side = dist.new_group(backend="gloo")
+            mine = (C.c_char * 64)()
+            rc = self._lib.rbv_ctx_ipc_handle(self._ctx, mine)
+            if rc:
+                raise CommError("cudaIpcGetMemHandle failed: " + self._lib.rbv_last_error().decode())
+            handles = [None] * self.nproc
+            dist.all_gather_object(handles, bytes(mine.raw), group=self._side)
+            blob = b"".join(handles)
+            rc = self._lib.rbv_ctx_connect(self._ctx, blob)
+            if rc:
+                raise CommError("cudaIpcOpenMemHandle failed: " + self._lib.rbv_last_error().decode())
+            dist.barrier(group=self._side)
+        info = (C.c_longlong * 8)()
+        self._lib.rbv_ctx_info(self._ctx, info)
+        self.max_ctas = int(info[6])
+        self.sm_count = int(info[7])
+
+    # ---- life cycle -------------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_ctx", None):
+            torch.cuda.synchronize(self.device)
+            if self._side is not None:
+                self._dist.barrier(group=self._side)
+            self._lib.rbv_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_ctx", None) and self.nproc == 1:
+                self.close()
+        except Exception:
+            pass
+
+    def host_barrier(self):
+        if self._side is not None:
+            self._dist.barrier(group=self._side)
+
+    @property
+    def local_ranks(self):
+        return list(range(self.proc * self.L, (self.proc + 1) * self.L))
+
+    # ---- memory -------------------------------------------------------------------------------
+    def symm_empty(self, shape, dtype=torch.uint8) -> torch.Tensor:
+        """A tensor inside the symmetric heap.  Every process must make the same sequence of
+        allocations only if it wants equal offsets; the kernels do not require that."""
+        if isinstance(shape, int):
+            shape = (shape,)
+        numel = int(np.prod(shape)) if len(shape) else 1
+        itemsize = torch.empty(0, dtype=dtype).element_size()
+        blk = _Block(self, numel * itemsize)
+        t = torch.as_tensor(blk, device=f"cuda:{self.device}")
+        t = t[: numel * itemsize].view(dtype).view(*shape) if numel else t[:0].view(dtype).view(*shape)
+        return t
+
+    def symm_zeros(self, shape, dtype=torch.uint8) -> torch.Tensor:
+        t = self.symm_empty(shape, dtype)
+        t.zero_()
+        return t
+
+    # ---- collectives --------------------------------------------------------------------------
+    def alltoallv(self, send: Sequence[torch.Tensor] | torch.Tensor, recv: Sequence[torch.Tensor] | torch.Tensor,
+                  sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, algo: str = "spreadout",
+                  n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0, type_size: Optional[int] = None,
+                  inplace: bool = False, grid: int = 0, chunk_bytes: int = 0, bytes_hint: int = -1,
+                  stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Non-uniform all-to-all of the L local ranks (asynchronous on the current stream).
+
+        ``send`` / ``recv`` are one tensor per local rank (a bare tensor when L == 1); ``recv`` must come
+        from :meth:`symm_empty`.  Counts and displacements are in elements, shaped ``[L, P]`` (``[P]`` when
+        L == 1): numpy / lists (host) or int32 / int64 CUDA tensors (device-resident, e.g. produced by a
+        router kernel).  ``sdispls`` / ``rdispls`` default to the packed layout when counts are on the host.
+        ``recvcounts`` is optional: when given, a block larger than its slot is refused (status
+        ``truncate``) instead of overrunning the buffer.
+        """
+        L, P = self.L, self.P
+        send_l = [send] if isinstance(send, torch.Tensor) else (list(send) if send is not None else [None] * L)
+        recv_l = [recv] if isinstance(recv, torch.Tensor) else list(recv)
+        if len(send_l) != L or len(recv_l) != L:
+            raise ValueError(f"expected {L} send and receive tensors")
+        ref = recv_l[0]
+        ts = int(type_size) if type_size else ref.element_size()
+        on_dev = isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda
+        keep = []
+        if on_dev:
+            def dev(a, dt):
+                if a is None:
+                    return None
+                a = a.to(dt).contiguous().view(L, P)
+                keep.append(a)
+                return a
+            sc, rc = dev(sendcounts, torch.int32), dev(recvcounts, torch.int32)
+            sd, rd = dev(sdispls, torch.int64), dev(rdispls, torch.int64)
+            if sd is None or rd is None:
+                raise ValueError("device-resident counts need explicit displacements")
+            p_sc, p_rc = sc.data_ptr(), (rc.data_ptr() if rc is not None else None)
+            p_sd, p_rd = sd.data_ptr(), rd.data_ptr()
+        else:
+            sc = np.ascontiguousarray(np.asarray(sendcounts, dtype=np.int32).reshape(L, P))
+            rc = None if recvcounts is None else np.ascontiguousarray(np.asarray(recvcounts, dtype=np.int32).reshape(L, P))
+            if sdispls is None:
+                sd = np.zeros((L, P), dtype=np.int64)
+                sd[:, 1:] = np.cumsum(sc[:, :-1], axis=1)
+            else:
+                sd = np.ascontiguousarray(np.asarray(sdispls, dtype=np.int64).reshape(L, P))
+            if rdispls is None:
+                if rc is None:
+                    raise ValueError("rdispls or recvcounts is required")
+                rd = np.zeros((L, P), dtype=np.int64)
+                rd[:, 1:] = np.cumsum(rc[:, :-1], axis=1)
+            else:
+                rd = np.ascontiguousarray(np.asarray(rdispls, dtype=np.int64).reshape(L, P))
+            keep += [sc, rc, sd, rd]
+            p_sc, p_rc = sc.ctypes.data, (rc.ctypes.data if rc is not None else None)
+            p_sd, p_rd = sd.ctypes.data, rd.ctypes.data
+        sp = (C.c_void_p * L)(*[(t.data_ptr() if t is not None else None) for t in send_l])
+        rp = (C.c_void_p * L)(*[t.data_ptr() for t in recv_l])
+        st = stream or torch.cuda.current_stream(self.device)
+        algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
+        rcode = self._lib.rbv_alltoallv(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
+                                        1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
+                                        int(chunk_bytes), C.c_void_p(st.cuda_stream))
+        if rcode:
+            raise CommError(f"alltoallv({algo}) failed with code {rcode}: {self._lib.rbv_last_error().decode()}")
+
+    # ---- status -------------------------------------------------------------------------------
+    def status(self) -> dict:
+        """Synchronises the current stream and returns the device-side status of the last call."""
+        st = Status()
+        self._lib.rbv_ctx_set_stream(self._ctx, C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self._lib.rbv_ctx_status(self._ctx, C.byref(st))
+        tr = [int(x) for x in st.trace]
+        return {"code": st.code, "name": STATUS_NAMES.get(st.code, "?"), "site": SITE_NAMES.get(st.site, "?"),
+                "detail": (st.detail0, st.detail1), "trace_ns": tr,
+                "phases_us": {"publish": (tr[1] - tr[0]) / 1e3, "metadata": (tr[2] - tr[1]) / 1e3,
+                              "issue": (tr[3] - tr[2]) / 1e3, "drain": (tr[4] - tr[3]) / 1e3}}
+
+    def check(self) -> None:
+        s = self.status()
+        if s["code"]:
+            raise CommError(f"device status {s['name']} at {s['site']} detail={s['detail']}")
+
+    def reset(self) -> None:
+        """Clears flags and counters after an error.  Collective: every process must call it."""
+        torch.cuda.synchronize(self.device)
+        self.host_barrier()
+        self._lib.rbv_ctx_reset(self._ctx)
+        self.host_barrier()
+
+    def set_timeout_ms(self, ms: float) -> None:
+        self._lib.rbv_ctx_set_timeout_ms(self._ctx, float(ms))
+
+    def inject_absent_rank(self, local_rank: int) -> None:
+        """Test hook: the given local rank skips the metadata phase of the following calls (-1 switches it off).
+        The other ranks then run into their bounded wait and report a time-out."""
+        self._lib.rbv_ctx_set_absent_rank(self._ctx, int(local_rank))
+
+    def plan(self, algo: str, **kw) -> Plan:
+        return Plan(algo, self.P, lib=self._lib, **kw)
+
+
+def init(nranks: Optional[int] = None, **kw) -> Communicator:
+    """Creates (or returns) the process-wide default communicator."""
+    global _default_comm
+    if _default_comm is None or (nranks and _default_comm.P != nranks):
+        _default_comm = Communicator(nranks, **kw)
+    return _default_comm
+
+
+def get_default_comm() -> Communicator:
+    if _default_comm is None:
+        raise CommError("call rbruck_alltoallv_b200.init() first")
+    return _default_comm

@@ -1,0 +1,174 @@
+"""GPU tests of the alltoallv kernel: all logical ranks of a communicator on one device."""
+import numpy as np
+import pytest
+import torch
+
+from rbruck_alltoallv_b200.utils import distributions as dist
+from rbruck_alltoallv_b200.utils import oracle
+
+pytestmark = pytest.mark.gpu
+
+_comms = {}
+
+
+def get_comm(P):
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    if P not in _comms:
+        _comms[P] = Communicator(nranks=P, heap_bytes=256 << 20, arena_bytes=4 << 20)
+    return _comms[P]
+
+
+def run_case(P, algo, ts, counts, packed=True, seed=0, with_recvcounts=True, device_counts=False, **kw):
+    comm = get_comm(P)
+    prob = oracle.make_problem(counts, ts, seed, packed=packed)
+    send_h = oracle.fill_send(prob, seed)
+    want = oracle.expected_recv(prob, send_h)
+    send = [torch.from_numpy(b).cuda() for b in send_h]
+    recv = [comm.symm_empty(len(w), torch.uint8) for w in want]
+    for t in recv:
+        t.fill_(oracle.CANARY)
+    rc = prob.recvcounts if with_recvcounts else None
+    sc, sd, rd = prob.counts, prob.sdispls, prob.rdispls
+    if device_counts:
+        sc = torch.from_numpy(sc.astype(np.int32)).cuda()
+        sd = torch.from_numpy(sd).cuda()
+        rd = torch.from_numpy(rd).cuda()
+        rc = torch.from_numpy(rc.astype(np.int32)).cuda() if rc is not None else None
+    comm.alltoallv(send, recv, sc, sd, rc, rd, algo=algo, type_size=ts, **kw)
+    comm.check()
+    got = [t.cpu().numpy() for t in recv]
+    bad = oracle.first_mismatch(got, want)
+    assert bad is None, f"{algo} P={P} {kw}: first mismatch at rank/offset {bad}"
+
+
+ALL = [("linear", {}), ("spreadout", {}), ("scattered", dict(b=3)), ("pairwise", {}), ("xor", {}),
+       ("rbruck", dict(r=2)), ("rbruck", dict(r=3)), ("rbruck_om", dict(r=2)), ("tuna", dict(r=2, b=1)),
+       ("tuna2", dict(r=2, b=2)), ("tuna2", dict(r=4, b=1)), ("tuna2", dict(r=8, b=0)),
+       ("ttpl", dict(n=4, r=2)), ("ttpl", dict(n=2, r=2)), ("ttpl_bt", dict(n=4, r=2, b=1)),
+       ("ttpl_bt_s1", dict(n=4, r=2, b=3)), ("ttpl_bt_s1", dict(n=2, r=2)), ("ttpl_bt_s2", dict(n=4, r=3, b=2)),
+       ("uniform_spreadout_twolayer", dict(n=4, r=2)), ("uniform_isplit_rbruck", dict(n=2, r=2, r2=2)),
+       ("twolayer_linear", dict(n=4)), ("twolayer_linear_s2", dict(n=4, b=2, b2=3)),
+       ("twolayer_linear_s3", dict(n=2, b=1, b2=1)), ("twolayer_linear_s4", dict(n=4, b=1, b2=2))]
+
+
+@pytest.mark.parametrize("algo,kw", ALL, ids=[f"{a}-{'-'.join(f'{k}{v}' for k, v in kw.items())}" for a, kw in ALL])
+def test_all_algorithms_p8(algo, kw):
+    counts = dist.uniform(8, 300, seed=3)
+    counts[counts < 30] = 0
+    run_case(8, algo, 4, counts, packed=False, seed=5, **kw)
+
+
+@pytest.mark.parametrize("P", [1, 2, 3, 5, 6, 7, 12, 16])
+def test_rank_counts(P):
+    counts = dist.uniform(P, 100, seed=P)
+    for algo, kw in [("spreadout", {}), ("rbruck", dict(r=2)), ("tuna2", dict(r=3, b=2)), ("rbruck_om", dict(r=max(P, 2)))]:
+        run_case(P, algo, 8, counts, packed=(P % 2 == 0), seed=P, **kw)
+
+
+@pytest.mark.parametrize("ts", [1, 2, 4, 8, 16])
+def test_type_sizes_unaligned(ts):
+    counts = dist.uniform(8, 777, seed=ts)
+    run_case(8, "tuna2", ts, counts, packed=False, seed=ts, r=2, b=1)
+    run_case(8, "spreadout", ts, counts, packed=False, seed=ts + 1)
+
+
+def test_large_blocks_multi_chunk():
+    counts = dist.normal(4, 300_000, seed=1)           # ~1.2 MB blocks of 4-byte elements
+    run_case(4, "spreadout", 4, counts, seed=1, chunk_bytes=64 << 10)
+    run_case(4, "rbruck", 4, counts, seed=2, r=2, chunk_bytes=96 << 10, grid=37)
+
+
+def test_zipf_and_empty():
+    counts = dist.zipf(8, 16384, seed=11)
+    run_case(8, "rbruck", 4, counts, seed=11, r=2)
+    run_case(8, "tuna2", 4, np.zeros((8, 8), dtype=np.int64), seed=1, r=2)
+
+
+def test_device_resident_counts():
+    counts = dist.uniform(8, 500, seed=21)
+    run_case(8, "tuna2", 2, counts, seed=21, device_counts=True, r=2, b=1)
+    run_case(8, "spreadout", 2, counts, seed=22, device_counts=True, with_recvcounts=False)
+
+
+def test_back_to_back_calls_alternate_parity():
+    counts = dist.uniform(8, 200, seed=31)
+    for i in range(6):
+        run_case(8, "rbruck", 4, counts, seed=31 + i, r=2)
+
+
+def test_inplace():
+    P, ts = 8, 4
+    comm = get_comm(P)
+    counts = dist.uniform(P, 120, seed=41)
+    prob = oracle.make_problem(counts, ts, 41, packed=True)
+    send_h = oracle.fill_send(prob, 41)
+    want = oracle.expected_recv(prob, send_h, tail=0)
+    recv = []
+    for d in range(P):
+        n = max(len(want[d]), len(send_h[d]))
+        t = comm.symm_empty(n, torch.uint8)
+        t.fill_(oracle.CANARY)
+        t[: len(send_h[d])] = torch.from_numpy(send_h[d]).cuda()
+        recv.append(t)
+    comm.alltoallv(None, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="ttpl_bt_s2",
+                   n=4, r=2, type_size=ts, inplace=True)
+    comm.check()
+    for d in range(P):
+        got = recv[d].cpu().numpy()[: len(want[d])]
+        assert np.array_equal(got, want[d])
+
+
+def test_truncation_is_reported_not_written():
+    P, ts = 4, 4
+    comm = get_comm(P)
+    counts = dist.constant(P, 64)
+    prob = oracle.make_problem(counts, ts, 0)
+    send = [torch.zeros(int(b), dtype=torch.uint8, device="cuda") for b in prob.send_bytes]
+    recv = [comm.symm_empty(int(b), torch.uint8) for b in prob.recv_bytes]
+    rc = prob.recvcounts.copy()
+    rc[2, 1] = 10                      # rank 2 expects less from rank 1 than rank 1 sends
+    comm.alltoallv(send, recv, prob.counts, prob.sdispls, rc, prob.rdispls, algo="spreadout", type_size=ts)
+    st = comm.status()
+    assert st["name"] == "truncate" and st["detail"] == (1, 2)
+    comm.reset()
+    run_case(P, "spreadout", ts, counts)
+
+
+def test_absent_rank_times_out_and_context_recovers():
+    P, ts = 4, 4
+    comm = get_comm(P)
+    counts = dist.constant(P, 16)
+    prob = oracle.make_problem(counts, ts, 0)
+    send = [torch.zeros(int(b), dtype=torch.uint8, device="cuda") for b in prob.send_bytes]
+    recv = [comm.symm_empty(int(b), torch.uint8) for b in prob.recv_bytes]
+    comm.set_timeout_ms(50)
+    comm.inject_absent_rank(2)
+    comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="tuna2", r=2,
+                   type_size=ts)
+    st = comm.status()
+    assert st["name"] == "timeout" and st["site"] == "metadata"
+    comm.inject_absent_rank(-1)
+    comm.set_timeout_ms(2000)
+    comm.reset()
+    run_case(P, "tuna2", ts, counts, r=2)
+
+
+def test_staging_capacity_error():
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    comm = Communicator(nranks=8, heap_bytes=64 << 20, arena_bytes=64 << 10)
+    counts = dist.constant(8, 16384)   # 64 KB blocks, r=2 needs 5 cells
+    prob = oracle.make_problem(counts, 4, 0)
+    send = [torch.zeros(int(b), dtype=torch.uint8, device="cuda") for b in prob.send_bytes]
+    recv = [comm.symm_empty(int(b), torch.uint8) for b in prob.recv_bytes]
+    comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="rbruck", r=2,
+                   type_size=4)
+    assert comm.status()["name"] == "staging_capacity"
+    comm.close()
+
+
+def test_plan_errors_surface():
+    from rbruck_alltoallv_b200.parallel.comm import CommError
+    comm = get_comm(6)
+    t = comm.symm_empty(64, torch.uint8)
+    with pytest.raises(CommError):
+        comm.alltoallv([t] * 6, [t] * 6, np.zeros((6, 6)), None, np.zeros((6, 6)), None, algo="xor")
