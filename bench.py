@@ -1,0 +1,292 @@
+#!/usr/bin/env python
+"""Headline benchmark: two-phase tunable radix-r Bruck alltoallv on a Zipf-skewed count matrix.
+
+Workload (fixed, whatever the GPU count): an 8-rank alltoallv of fp32 elements; per-pair block sizes are
+Zipf-skewed (s = 1.2, largest block 64 KB, about 10 % empty blocks) from a fixed seed.  The 8 logical ranks
+are spread over the N GPUs (8/N ranks per GPU), so N = 8 is one rank per B200 and N = 1 keeps the whole
+exchange inside one GPU: strong scaling of a fixed problem.  A step is one `twophase_rbruck_alltoallv`
+call whose radix is picked from {2, 3, 4, 8} by timing during warm-up (the tunable radix is the point of
+the algorithm; at 8 ranks radix 8 degenerates to one direct round).
+
+    python bench.py --gpus N --steps K --warmup W            # this library (device kernels)
+    python bench.py --impl reference --gpus N --steps K ...  # the unmodified reference on CPU threads
+
+Prints one JSON line.  `value` = total bytes sent by all ranks / device time of the slowest rank, in GB/s,
+summed over the job; `e2e` is the same metric through the public Python API including the host->device
+copy of every rank's send buffer from pinned memory and the device->host copy of every receive buffer.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NRANKS = 8
+TYPE_SIZE = 4
+MAX_BLOCK_ELEMS = 16384          # 64 KB of fp32
+SEED = 20240104
+RADICES = (2, 3, 4, 8)
+METRIC = "alltoallv_algbw_GBps"
+
+
+def workload():
+    from rbruck_alltoallv_b200.utils import distributions as dist
+    return dist.zipf(NRANKS, MAX_BLOCK_ELEMS, s=1.2, zero_frac=0.10, seed=SEED)
+
+
+def config_dict(n_gpus, extra=None):
+    cfg = {"model": "twophase_rbruck_alltoallv (radix tuned over {2,3,4,8})", "ranks": NRANKS,
+           "ranks_per_gpu": NRANKS // max(n_gpus, 1), "global_batch": NRANKS * NRANKS, "seq_len": MAX_BLOCK_ELEMS,
+           "distribution": f"zipf s=1.2, max block 64 KB, ~10% empty, seed {SEED}", "payload": "fp32",
+           "parallelism": f"a2a{n_gpus}"}
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+# --------------------------------------------------------------------------------------------------
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        import install_reference
+        runner = install_reference.ensure_built()
+    except Exception as e:  # build failure
+        print(json.dumps({"impl": "reference", "unavailable": f"reference build failed: {str(e)[:200]}"}))
+        return 0
+    if runner is None:
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is absent: run baseline/install_reference.py"}))
+        return 0
+    from rbruck_alltoallv_b200.utils import distributions as dist
+    counts = workload()
+    total_bytes = int(counts.sum()) * TYPE_SIZE
+    with tempfile.NamedTemporaryFile("w", suffix=".txt", delete=False) as f:
+        path = f.name
+    dist.write_matrix(path, counts)
+    per_radix = {}
+    try:
+        for r in RADICES:
+            out = subprocess.run([str(runner), "rbruck", str(NRANKS), str(TYPE_SIZE), path, str(max(args.steps, 1)),
+                                  str(max(args.warmup, 3)), "0", str(r)], capture_output=True, text=True, timeout=600)
+            per_radix[r] = json.loads(out.stdout.strip().splitlines()[-1])
+    finally:
+        os.unlink(path)
+    best = min(per_radix, key=lambda r: per_radix[r]["sum_s"])
+    res = per_radix[best]
+    ms = res["sum_s"] / max(args.steps, 1) * 1e3
+    value = total_bytes / (ms * 1e-3) / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": config_dict(args.gpus, {"radix": best, "transport": "threads-as-ranks MPI stand-in, host memory",
+                                              "us_per_radix": {str(r): per_radix[r]["mean_us"] for r in RADICES},
+                                              "mismatched_bytes": res["mismatched_bytes"]}),
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "CPU code on host buffers: there is no device copy to include"},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+    return 0
+
+
+# --------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    from rbruck_alltoallv_b200.utils import oracle
+    from rbruck_alltoallv_b200.utils.timing import ClockSampler, L2Flusher, RankAligner, time_steps
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    n_gpus = world
+    if NRANKS % n_gpus:
+        raise SystemExit(f"--gpus must divide {NRANKS}")
+    comm = Communicator(nranks=NRANKS, heap_bytes=512 << 20, arena_bytes=8 << 20)
+    rank0 = comm.proc == 0
+    dev = f"cuda:{comm.device}"
+    L, P = comm.L, comm.P
+    mine = comm.local_ranks
+
+    counts = workload()
+    prob = oracle.make_problem(counts, TYPE_SIZE, SEED, packed=True)
+    total_bytes = int(counts.sum()) * TYPE_SIZE
+    send_h = oracle.fill_send(prob, SEED)
+    want = oracle.expected_recv(prob, send_h, tail=0)
+
+    # one pinned + one device slab for the send side and for the receive side (one copy each way per step)
+    s_sizes = [int(prob.send_bytes[r]) for r in mine]
+    r_sizes = [int(prob.recv_bytes[r]) for r in mine]
+    al = lambda v: (v + 255) // 256 * 256
+    s_off = np.concatenate([[0], np.cumsum([al(v) for v in s_sizes])]).astype(int)
+    r_off = np.concatenate([[0], np.cumsum([al(v) for v in r_sizes])]).astype(int)
+    pin_send = torch.empty(int(s_off[-1]) or 1, dtype=torch.uint8).pin_memory()
+    pin_recv = torch.empty(int(r_off[-1]) or 1, dtype=torch.uint8).pin_memory()
+    dev_send = torch.empty(int(s_off[-1]) or 1, dtype=torch.uint8, device=dev)
+    dev_recv = comm.symm_empty(int(r_off[-1]) or 1, torch.uint8)
+    for i, r in enumerate(mine):
+        pin_send[s_off[i]:s_off[i] + s_sizes[i]] = torch.from_numpy(send_h[r][:s_sizes[i]])
+    dev_send.copy_(pin_send)
+    send = [dev_send[s_off[i]:s_off[i] + max(s_sizes[i], 1)] for i in range(L)]
+    recv = [dev_recv[r_off[i]:r_off[i] + max(r_sizes[i], 1)] for i in range(L)]
+    sc = prob.counts[mine].astype(np.int32)
+    rc = prob.recvcounts[mine].astype(np.int32)
+    sd = prob.sdispls[mine]
+    rd = prob.rdispls[mine]
+
+    # persistent calls (resolved once, one kernel launch per step), one per candidate radix
+    calls = {r: comm.prepare(send, recv, sc, sd, rc, rd, algo="rbruck", r=r, type_size=TYPE_SIZE) for r in RADICES}
+
+    def step(radix):
+        calls[radix].launch()
+
+    flush = L2Flusher(dev)
+    align = RankAligner(comm)
+
+    # correctness once, before timing
+    dev_recv.fill_(0xA5)
+    step(2)
+    comm.check()
+    got = dev_recv.cpu().numpy()
+    for i, r in enumerate(mine):
+        if not np.array_equal(got[r_off[i]:r_off[i] + r_sizes[i]], want[r]):
+            raise SystemExit(f"rank {r}: receive buffer differs from the direct-copy expectation")
+
+    # radix choice by measurement (part of warm-up)
+    per_radix = {}
+    for r in RADICES:
+        t = time_steps(lambda: step(r), steps=20, warmup=3, flush=flush, align=align)
+        per_radix[r] = float(np.mean(t)) * 1e3
+    best = min(per_radix, key=per_radix.get)
+    if world > 1:
+        b = torch.tensor([best], device=dev)
+        dist.broadcast(b, 0)
+        best = int(b.item())
+
+    warm = max(args.warmup, 3)
+    with ClockSampler(comm.device) as clocks:
+        t = time_steps(lambda: step(best), steps=args.steps, warmup=warm, flush=flush, align=align)
+        comm.check()
+
+        # end to end through the public API: pinned host -> device, alltoallv, device -> pinned host
+        def e2e_step():
+            dev_send.copy_(pin_send, non_blocking=True)
+            step(best)
+            pin_recv.copy_(dev_recv, non_blocking=True)
+        te = time_steps(e2e_step, steps=args.steps, warmup=warm, flush=flush, align=align)
+        comm.check()
+    got = pin_recv.numpy()
+    for i, r in enumerate(mine):
+        if not np.array_equal(got[r_off[i]:r_off[i] + r_sizes[i]], want[r]):
+            raise SystemExit(f"rank {r}: end-to-end result differs from the expectation")
+
+    ms = float(np.sum(t)) / args.steps
+    ms_e = float(np.sum(te)) / args.steps
+    value = total_bytes / (ms * 1e-3) / 1e9
+    value_e = total_bytes / (ms_e * 1e-3) / 1e9
+    h2d, d2h = int(sum(s_sizes)), int(sum(r_sizes))
+    if world > 1:
+        hb = torch.tensor([h2d, d2h], device=dev, dtype=torch.int64)
+        dist.all_reduce(hb)
+        h2d, d2h = int(hb[0]) , int(hb[1])
+
+    sweep = None
+    if args.sweep:
+        sweep = run_sweep(comm, flush, align, world)
+
+    if rank0:
+        line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": warm,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
+                "data": "synthetic",
+                "config": config_dict(n_gpus, {
+                    "radix": best, "us_per_radix": {str(k): round(v, 2) for k, v in per_radix.items()},
+                    "total_bytes": total_bytes, "us_median": float(np.median(t)) * 1e3,
+                    "l2": "flushed: a 256 MiB buffer is written before every timed step (outside the timed span); "
+                          "a zero-byte alltoallv then lines the ranks up",
+                    "timing": "CUDA events around each step, per-step max over ranks, summed over the K steps"}),
+                "clocks": clocks.summary(),
+                "e2e": {"value": value_e, "unit": "GB/s", "ms_per_step": ms_e, "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h},
+                "gpu_launches": args.steps}
+        if sweep is not None:
+            line["sweep"] = sweep
+        print(json.dumps(line), flush=True)
+    comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_sweep(comm, flush, align, world):
+    """Latency / bandwidth over block sizes for a few algorithm families (not part of the timed K steps)."""
+    import torch
+    import torch.distributed as dist
+    from rbruck_alltoallv_b200.utils import distributions as D
+    from rbruck_alltoallv_b200.utils.timing import time_steps
+
+    out = []
+    dev = f"cuda:{comm.device}"
+    L, P = comm.L, comm.P
+    mine = comm.local_ranks
+    for k in (4, 10, 14, 18, 22):           # mean block 16 B ... 4 MB of bf16
+        mean_elems = max(1, (1 << k) // 2)
+        counts = D.normal(P, mean_elems, 0.25, seed=k)
+        sc = counts[mine].astype(np.int32)
+        rc = counts.T[mine].astype(np.int32)
+        send = [torch.empty(max(int(sc[i].sum()), 1) * 2, dtype=torch.uint8, device=dev) for i in range(L)]
+        recv = [comm.symm_empty(max(int(rc[i].sum()), 1) * 2, torch.uint8) for i in range(L)]
+        tot = int(counts.sum()) * 2
+        row = {"mean_block_bytes": 1 << k, "total_bytes": tot, "us": {}}
+        for name, kw in (("spreadout", {}), ("rbruck_r2", dict(algo="rbruck", r=2)), ("tuna2_r2", dict(algo="tuna2", r=2)),
+                         ("ttpl_bt_s1_n4", dict(algo="ttpl_bt_s1", n=4, r=2))):
+            kw = dict(kw)
+            algo = kw.pop("algo", name)
+            fn = lambda: comm.alltoallv(send, recv, sc, None, rc, None, algo=algo, type_size=2, **kw)
+            t = time_steps(fn, steps=10, warmup=3, flush=flush, align=align)
+            if comm.status()["code"]:
+                comm.reset()
+                row["us"][name] = None
+                continue
+            row["us"][name] = round(float(np.median(t)) * 1e3, 2)
+        if world > 1 and L == 1:
+            s1 = send[0].view(torch.bfloat16)
+            r1 = torch.empty(max(int(rc[0].sum()), 1), dtype=torch.bfloat16, device=dev)
+            fn = lambda: dist.all_to_all_single(r1[: int(rc[0].sum())], s1[: int(sc[0].sum())],
+                                                output_split_sizes=[int(x) for x in rc[0]],
+                                                input_split_sizes=[int(x) for x in sc[0]])
+            t = time_steps(fn, steps=10, warmup=3, flush=flush, align=align)
+            row["us"]["nccl_grouped_sendrecv"] = round(float(np.median(t)) * 1e3, 2)
+        out.append(row)
+        del send, recv
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--sweep", action="store_true", help="also report a block-size sweep (outside the timed steps)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -42,3 +42,11 @@ def declare_cuda(lib):
         C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
         C.c_int, C.c_longlong, C.c_uint, C.c_int, C.c_size_t, C.c_void_p]
     lib.rbv_update_timers.argtypes = [C.c_void_p]
+    lib.rbv_prepare.restype = C.c_void_p
+    lib.rbv_prepare.argtypes = [C.c_void_p] + [C.c_int] * 7 + [
+        C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+        C.c_int, C.c_longlong, C.c_uint, C.c_int, C.c_size_t]
+    lib.rbv_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_set_cooperative.argtypes = [C.c_void_p, C.c_int]

@@ -94,7 +94,7 @@ int rbv_ctx_reset(rbv_ctx_t ctx) {
 }
 int rbv_ctx_info(rbv_ctx_t ctx, long long* o) {
   o[0] = ctx->c->P(); o[1] = ctx->c->L(); o[2] = ctx->c->nproc(); o[3] = ctx->c->proc();
-  o[4] = ctx->c->device(); o[5] = ctx->c->seq(); o[6] = ctx->c->max_ctas(); o[7] = ctx->c->sm_count();
+  o[4] = ctx->c->device(); o[5] = 0; o[6] = ctx->c->max_ctas(); o[7] = ctx->c->sm_count();
   return 0;
 }
 void* rbv_ctx_heap(rbv_ctx_t ctx, int proc) { return ctx->c->peer_heap(proc); }
@@ -130,6 +130,43 @@ int rbv_alltoallv(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
     return RBV_ERR_BAD_ARG;
   }
 }
+
+void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
+                  const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
+                  const int* recvcounts, const long long* sdispls, const long long* rdispls,
+                  int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes) {
+  try {
+    AlgoSpec s;
+    s.algo = algo; s.P = ctx->c->P(); s.n = n; s.r = r; s.r2 = r2; s.b = b; s.b2 = b2;
+    CallArgs ca;
+    ca.sendbufs = sendbufs; ca.recvbufs = recvbufs;
+    ca.sendcounts = sendcounts; ca.recvcounts = recvcounts; ca.sdispls = sdispls; ca.rdispls = rdispls;
+    ca.counts_on_device = counts_on_device != 0;
+    ca.bytes_hint = bytes_hint;
+    CallOptions opt;
+    opt.grid = grid; opt.chunk_bytes = chunk_bytes; opt.flags = flags;
+    auto pc = std::make_unique<Prepared>();
+    int rc = ctx->c->prepare(s, type_size, ca, opt, nullptr, true, pc.get());
+    if (rc) { g_err = ctx->c->last_error(); return nullptr; }
+    return pc.release();
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    return nullptr;
+  }
+}
+int rbv_launch(rbv_ctx_t ctx, void* prepared, void* cuda_stream) {
+  int rc = ctx->c->launch(*static_cast<Prepared*>(prepared), static_cast<cudaStream_t>(cuda_stream));
+  if (rc) g_err = ctx->c->last_error();
+  return rc;
+}
+void rbv_prepared_free(rbv_ctx_t ctx, void* prepared) {
+  Prepared* pc = static_cast<Prepared*>(prepared);
+  if (!pc) return;
+  ctx->c->release(*pc);
+  delete pc;
+}
+void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
+void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on) { ctx->c->set_cooperative(on != 0); }
 
 int rbv_update_timers(rbv_ctx_t ctx) {
   StatusBlock s = ctx->c->status(ctx->stream);

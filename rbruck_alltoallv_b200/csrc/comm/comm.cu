@@ -1,7 +1,9 @@
 // Context implementation: heap layout, CUDA IPC peer mapping, symmetric allocator, plan cache and
 // the launch path of the alltoallv kernel.
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 
@@ -36,6 +38,7 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   RBV_CUDA_THROW(a2av_configure(P, &per_sm));
   per_sm = std::max(1, std::min(per_sm, 2));
   max_ctas_ = sm_count_ * per_sm;
+  if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_ = std::atoi(e) != 0;
 
   lay_.ctrl_off = 0;
   lay_.flags_off = align_up(sizeof(CtrlBlock), 256);
@@ -170,8 +173,30 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
   return out;
 }
 
-int Context::alltoallv(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const CallOptions& opt,
+int Context::alltoallv(const AlgoSpec& spec, int ts, const CallArgs& ca, const CallOptions& opt,
                        cudaStream_t stream) {
+  Prepared pc;
+  int rc = prepare(spec, ts, ca, opt, stream, false, &pc);
+  if (rc) return rc;
+  return launch(pc, stream);
+}
+
+int Context::launch(const Prepared& pc, cudaStream_t stream) {
+  cudaError_t e = a2av_launch(pc.ka, pc.grid, cooperative_, stream);
+  if (e != cudaSuccess) {
+    last_error_ = std::string("kernel launch failed: ") + cudaGetErrorString(e);
+    return RBV_ERR_BAD_ARG;
+  }
+  return 0;
+}
+
+void Context::release(Prepared& pc) {
+  if (pc.owned_meta) cudaFree(pc.owned_meta);
+  pc.owned_meta = nullptr;
+}
+
+int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const CallOptions& opt,
+                     cudaStream_t stream, bool persistent, Prepared* out) {
   AlgoSpec spec = spec_in;
   spec.P = P_;
   const DevPlan* dp = plan_for(spec);
@@ -183,12 +208,12 @@ int Context::alltoallv(const AlgoSpec& spec_in, int ts, const CallArgs& ca, cons
     last_error_ = "null argument"; return RBV_ERR_BAD_ARG;
   }
 
-  KernelArgs ka;
+  KernelArgs& ka = out->ka;
   std::memset(&ka, 0, sizeof ka);
+  out->owned_meta = nullptr;
   ka.P = P_; ka.L = L_; ka.nproc = nproc_; ka.proc = proc_;
   ka.type_size = ts;
-  ka.seq = seq_;
-  ka.flags = opt.flags & CALL_INPLACE;
+  ka.flags = (opt.flags & CALL_INPLACE) | (trace_ ? (unsigned)CALL_TRACE : 0u);
   ka.nops = dp->nops;
   ka.absent_rank = absent_rank_;
   ka.ncells = dp->plan.ncells;
@@ -250,6 +275,24 @@ int Context::alltoallv(const AlgoSpec& spec_in, int ts, const CallArgs& ca, cons
         ka.inl.sdispls[i] = ca.sdispls[i];
         ka.inl.rdispls[i] = ca.rdispls[i];
       }
+    } else if (persistent) {
+      // a prepared call owns a device copy of its count arrays
+      const size_t need = n * (4 + 4 + 8 + 8);
+      std::vector<char> h(need);
+      long long* h_sd = reinterpret_cast<long long*>(h.data());
+      long long* h_rd = h_sd + n;
+      int* h_sc = reinterpret_cast<int*>(h_rd + n);
+      int* h_rc = h_sc + n;
+      for (size_t i = 0; i < n; i++) {
+        h_sd[i] = ca.sdispls[i]; h_rd[i] = ca.rdispls[i];
+        h_sc[i] = ca.sendcounts[i]; h_rc[i] = ca.recvcounts ? ca.recvcounts[i] : -1;
+      }
+      RBV_CUDA_THROW(cudaMalloc(&out->owned_meta, need));
+      RBV_CUDA_THROW(cudaMemcpy(out->owned_meta, h.data(), need, cudaMemcpyHostToDevice));
+      long long* d_sd = reinterpret_cast<long long*>(out->owned_meta);
+      int* d_sc = reinterpret_cast<int*>(d_sd + 2 * n);
+      ka.sdispls = d_sd; ka.rdispls = d_sd + n;
+      ka.sendcounts = d_sc; ka.recvcounts = d_sc + n;
     } else {
       const size_t need = n * (4 + 4 + 8 + 8);
       if (need > ring_bytes_) {
@@ -296,13 +339,14 @@ int Context::alltoallv(const AlgoSpec& spec_in, int ts, const CallArgs& ca, cons
   double work = send_bytes >= 0 ? (double)send_bytes * std::max(1.0, hop_factor) : -1.0;
   unsigned long long chunk = opt.chunk_bytes;
   int grid = opt.grid;
+  const int warps_per_cta = kThreads / 32;
   if (!chunk) {
-    if (work < 0) chunk = 64 << 10;
+    if (work < 0) chunk = 32 << 10;
     else {
-      // aim at ~4 chunks per CTA at full grid, within [16 KB, 512 KB]
-      double c = work / (4.0 * max_ctas_);
-      chunk = (unsigned long long)std::min(512.0 * 1024, std::max(16.0 * 1024, c));
-      chunk = align_up(chunk, 4096);
+      // a chunk is one warp's unit of work: aim at ~4 chunks per warp at full grid, within [8 KB, 64 KB]
+      double c = work / (4.0 * max_ctas_ * warps_per_cta);
+      chunk = (unsigned long long)std::min(64.0 * 1024, std::max(8.0 * 1024, c));
+      chunk = align_up(chunk, 1024);
     }
   }
   chunk = align_up(chunk, 16);
@@ -310,24 +354,20 @@ int Context::alltoallv(const AlgoSpec& spec_in, int ts, const CallArgs& ca, cons
     if (work < 0) grid = max_ctas_;
     else {
       double chunks = work / (double)chunk + dp->nops;
-      grid = (int)std::min<double>(max_ctas_, std::max<double>(1.0, chunks));
+      grid = (int)std::min<double>(max_ctas_, std::max<double>(1.0, std::ceil(chunks / warps_per_cta)));
     }
   }
   grid = std::max(1, std::min(grid, max_ctas_));
   ka.chunk_bytes = chunk;
-
-  cudaError_t e = a2av_launch(ka, grid, stream);
-  if (e != cudaSuccess) {
-    last_error_ = std::string("kernel launch failed: ") + cudaGetErrorString(e);
-    return RBV_ERR_BAD_ARG;
-  }
-  seq_++;
+  out->grid = grid;
   return 0;
 }
 
 StatusBlock Context::status(cudaStream_t stream) {
   cudaStreamSynchronize(stream);
-  return *host_status_;
+  StatusBlock s = *host_status_;
+  host_status_->code = 0;   // errors are sticky until they have been read once
+  return s;
 }
 
 cudaError_t Context::reset() {
@@ -339,7 +379,6 @@ cudaError_t Context::reset() {
   if (e != cudaSuccess) return e;
   for (auto& kv : plans_)
     if (kv.second->d_done) cudaMemset(kv.second->d_done, 0, kv.second->nops * sizeof(unsigned));
-  seq_ = 0;
   std::memset(host_status_, 0, sizeof(StatusBlock));
   return cudaDeviceSynchronize();
 }

@@ -41,6 +41,14 @@ struct CallArgs {
   long long bytes_hint = -1;               // total bytes sent by this process, if known (device counts)
 };
 
+// A fully resolved call: launching it again repeats the collective with the same buffers and counts
+// (the call number lives in device memory, so nothing in here changes between launches).
+struct Prepared {
+  KernelArgs ka;
+  int grid = 1;
+  void* owned_meta = nullptr;   // device copy of host count arrays that did not fit the kernel parameters
+};
+
 class Context {
  public:
   Context(int P, int nproc, int proc, int device, size_t user_bytes, size_t arena_bytes);
@@ -52,7 +60,6 @@ class Context {
   int nproc() const { return nproc_; }
   int proc() const { return proc_; }
   int device() const { return device_; }
-  unsigned seq() const { return seq_; }
   const HeapLayout& layout() const { return lay_; }
   char* heap() const { return heap_; }
   char* peer_heap(int q) const { return peer_[q]; }
@@ -71,7 +78,19 @@ class Context {
   int alltoallv(const AlgoSpec& spec, int type_size, const CallArgs& args, const CallOptions& opt,
                 cudaStream_t stream);
 
-  // Status of the most recent call; synchronises `stream` first.
+  // The two halves of alltoallv(): resolve everything once, launch many times (the analogue of MPI's
+  // persistent collectives).  `persistent` makes the call own a device copy of large host count arrays.
+  int prepare(const AlgoSpec& spec, int type_size, const CallArgs& args, const CallOptions& opt,
+              cudaStream_t stream, bool persistent, Prepared* out);
+  int launch(const Prepared& pc, cudaStream_t stream);
+  void release(Prepared& pc);
+  // Cooperative launches guarantee that all CTAs are resident (needed when other kernels share the GPU);
+  // a plain launch is a little cheaper.  Default: cooperative; RBV_COOPERATIVE=0 switches it off.
+  void set_cooperative(bool on) { cooperative_ = on; }
+  // Copy the phase time stamps to the host after every call (off: only failing calls report).
+  void set_trace(bool on) { trace_ = on; }
+
+  // First error since the last status() call (0 if none); synchronises `stream` first.
   StatusBlock status(cudaStream_t stream);
   // Clears all synchronisation state.  Every process must call it between the same two calls,
   // with a host barrier before and after.
@@ -88,7 +107,8 @@ class Context {
   char* heap_ = nullptr;
   char* peer_[kMaxProcs] = {};
   bool opened_[kMaxProcs] = {};
-  unsigned seq_ = 0;
+  bool cooperative_ = true;
+  bool trace_ = false;
   int absent_rank_ = -1;
   unsigned long long timeout_ns_ = 2000000000ull;
   int max_ctas_ = 1, sm_count_ = 1;
@@ -114,6 +134,6 @@ class Context {
 // implemented in kernels/a2av_kernel.cu
 size_t a2av_smem_bytes(int P);
 cudaError_t a2av_configure(int P, int* max_ctas_per_sm);
-cudaError_t a2av_launch(const KernelArgs& args, int grid, cudaStream_t stream);
+cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream);
 
 }  // namespace rbv

@@ -59,7 +59,8 @@ struct CtrlBlock {
   unsigned int abort_flag;       // set locally on error, and by peers that want everyone to stop
   unsigned int pad0;
   unsigned int exit_count;       // CTAs that finished the current call (the last one publishes the status)
-  unsigned int pad1;
+  unsigned int call_seq;         // 0-based number of the next call; bumped by the last CTA of every call, so
+                                 // that kernel arguments do not change from call to call
   StatusBlock status;
 };
 
@@ -91,6 +92,8 @@ __host__ __device__ inline unsigned long long meta_table_bytes(int P) {
 enum CallFlags : unsigned {
   CALL_INPLACE = 1u,      // send data is taken from recvbuf (copied to a private region first)
   CALL_META_INLINE = 2u,  // counts/displacements are in KernelArgs::inl, not behind the pointers
+  CALL_TRACE = 4u,        // copy the status block (with the phase time stamps) to the host after every call,
+                          // not only after a failing one
 };
 
 struct InlineMeta {
@@ -103,7 +106,6 @@ struct InlineMeta {
 struct KernelArgs {
   int P, L, nproc, proc;
   int type_size;
-  unsigned seq;            // 0-based call number on this communicator
   unsigned flags;
   int nops;                // ops executed by this process
   int absent_rank;         // fault injection for tests: this local rank never publishes its metadata (-1: none)

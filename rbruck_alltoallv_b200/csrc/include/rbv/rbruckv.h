@@ -78,7 +78,19 @@ int rbv_alltoallv(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
                   int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes,
                   void* cuda_stream);
 
-/* Phase timers of the most recent call, filled by rbv_update_timers() (which synchronises).
+/* Persistent form (the analogue of MPI_Alltoallv_init / MPI_Start): resolve a call once, launch it many
+ * times with one cheap call each.  Buffers and counts are fixed at preparation. */
+void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
+                  const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
+                  const int* recvcounts, const long long* sdispls, const long long* rdispls,
+                  int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes);
+int rbv_launch(rbv_ctx_t ctx, void* prepared, void* cuda_stream);
+void rbv_prepared_free(rbv_ctx_t ctx, void* prepared);
+void rbv_ctx_set_trace(rbv_ctx_t ctx, int on);       /* report phase time stamps after every call */
+void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on); /* cooperative (default) or plain kernel launches */
+
+/* Phase timers of the most recent call, filled by rbv_update_timers() (which synchronises;
+ * call rbv_ctx_set_trace(ctx, 1) first).
  * Names as in the reference (src/rbruckv.h:13-18); phases that no longer exist as separate steps
  * (pack, unpack, organise) stay 0. */
 extern double init_time, findMax_time, rotateIndex_time, alcCopy_time, getBlock_time, prepData_time,

@@ -10,9 +10,16 @@
 //   (3) completion          -- waits until all P blocks of every local rank have landed.
 //
 // Work distribution: ops are cut into chunks of `chunk_bytes`; chunk c of the process-wide
-// sequence is handled by CTA c mod gridDim.  CTAs walk their chunks in plan order, so a wait on a
-// staging cell only ever depends on chunks of an earlier plan key, which rules out cycles as long
-// as all CTAs are resident (cooperative launch).
+// sequence is handled by WARP c mod (warps in the grid).  A warp copies its chunk with 16-byte
+// vectors (512 contiguous bytes per warp instruction) and, when it completes an op, signals the
+// destination.  Small blocks thus proceed in parallel, one warp each, and large blocks are spread
+// over all warps of all SMs.  Warps walk their chunks in plan order, so a wait on a staging cell
+// only ever depends on chunks of an earlier plan key, which rules out cycles as long as all CTAs
+// are resident (cooperative launch).
+//
+// Signals use gpu scope when producer and consumer are on the same GPU and system scope across
+// GPUs.  The call number lives in device memory (CtrlBlock::call_seq), so the kernel arguments of
+// a repeated call are constant.
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
@@ -28,8 +35,6 @@ namespace {
 constexpr int kOpTile = 1024;
 
 struct Smem {
-  // dynamic layout: int counts[P*P]; int caps[P*P]; long long rdispl[P*P]; ull recvoff[P];
-  // then unsigned prefix[kOpTile + 1]
   int* counts;
   int* caps;
   long long* rdispl;
@@ -79,10 +84,10 @@ __device__ __forceinline__ const long long* in_rdispls(const KernelArgs& a) {
 }
 
 // Metadata rows of local rank lr go to process q: one warp per (lr, q) pair.
-__device__ void publish_metadata(const KernelArgs& a) {
-  const int P = a.P, parity = a.seq & 1;
+__device__ void publish_metadata(const KernelArgs& a, int parity) {
+  const int P = a.P;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  const bool have_rc = (a.flags & CALL_META_INLINE) ? true : (a.recvcounts != nullptr);
+  const int* rc = in_recvcounts(a);
   for (int pair = warp; pair < a.L * a.nproc; pair += nwarps) {
     const int lr = pair / a.nproc, q = pair % a.nproc;
     if (lr == a.absent_rank) continue;  // host-injected fault: the rank "never joins"
@@ -93,19 +98,15 @@ __device__ void publish_metadata(const KernelArgs& a) {
     long long* rd = reinterpret_cast<long long*>(mt + meta_rdispl_off(P)) + (size_t)me * P;
     unsigned long long* ro = reinterpret_cast<unsigned long long*>(mt + meta_recvoff_off(P)) + me;
     const int* sc = in_sendcounts(a) + (size_t)lr * P;
-    const int* rc = in_recvcounts(a);
     const long long* rdi = in_rdispls(a) + (size_t)lr * P;
     for (int i = lane; i < P; i += 32) {
       counts[i] = sc[i];
-      caps[i] = (have_rc && rc) ? rc[(size_t)lr * P + i] : -1;
+      caps[i] = rc ? rc[(size_t)lr * P + i] : -1;
       rd[i] = rdi[i];
     }
     if (lane == 0) *ro = a.recvoff[lr];
     __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
-      dev::red_release_sys_add(&ctrl_of(a, q)->meta_arrivals[parity], 1ull);
-    }
+    if (lane == 0) dev::signal_add(&ctrl_of(a, q)->meta_arrivals[parity], 1ull, q != a.proc);
   }
 }
 
@@ -119,9 +120,12 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_flag;
   __shared__ unsigned s_total;
+  __shared__ unsigned s_seq;
   const int P = a.P, L = a.L, ts = a.type_size;
-  const int parity = a.seq & 1;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned warps_per_cta = blockDim.x >> 5;
+  const unsigned gwarp = blockIdx.x * warps_per_cta + warp, nwarps = gridDim.x * warps_per_cta;
+  const bool multi = a.nproc > 1;   // some producers are on other GPUs
   CtrlBlock* my = ctrl_of(a, a.proc);
   dev::WaitCfg wc{&my->abort_flag, a.timeout_ns};
 
@@ -135,7 +139,13 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     sm.prefix = reinterpret_cast<unsigned*>(p);
   }
 
-  if (blockIdx.x == 0 && tid == 0) my->status.trace[0] = dev::globaltimer();
+  if (tid == 0) {
+    s_seq = __ldcg(&my->call_seq);
+    if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
+  }
+  __syncthreads();
+  const unsigned seq = s_seq;
+  const int parity = seq & 1;
 
   // ---- in-place calls: move the send data out of recvbuf before anyone may write into it ----
   if (a.flags & CALL_INPLACE) {
@@ -154,13 +164,14 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
 
   // ---- (1) metadata phase ----
   if (blockIdx.x == 0) {
-    publish_metadata(a);
+    publish_metadata(a, parity);
     if (tid == 0) my->status.trace[1] = dev::globaltimer();
   }
   if (tid == 0) {
-    const unsigned long long target = ((unsigned long long)(a.seq >> 1) + 1ull) * (unsigned long long)P;
-    int r = dev::wait_ge(&my->meta_arrivals[parity], target, wc);
-    if (r == dev::WAIT_TIMEOUT) report_error(a, RBV_ERR_TIMEOUT, WAIT_META, (int)my->meta_arrivals[parity], (int)target);
+    const unsigned long long target = ((unsigned long long)(seq >> 1) + 1ull) * (unsigned long long)P;
+    int r = dev::wait_ge(&my->meta_arrivals[parity], target, wc, multi);
+    if (r == dev::WAIT_TIMEOUT)
+      report_error(a, RBV_ERR_TIMEOUT, WAIT_META, (int)my->meta_arrivals[parity], (int)target);
     s_flag = r;
   }
   __syncthreads();
@@ -184,17 +195,17 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     }
     for (int i = tid; i < P; i += blockDim.x) sm.recvoff[i] = __ldcg(go + i);
     // global max block -> staging cell stride (the reference's max_send_count allreduce)
-    mx = __reduce_max_sync(0xffffffffu, mx);
-    if (tid == 0) s_flag = 0;
-    __syncthreads();
-    if ((tid & 31) == 0) atomicMax(&s_flag, mx);
-    __syncthreads();
-    stride = (((size_t)s_flag * ts) + 15) & ~(size_t)15;
-    __syncthreads();
-    if (a.ncells > 0 && stride * (size_t)a.ncells > a.lay.arena_bytes) {
-      if (blockIdx.x == 0 && tid == 0)
-        report_error(a, RBV_ERR_CAPACITY, 0, a.ncells, (int)(stride >> 10));
-      alive = false;
+    if (a.ncells > 0) {
+      mx = __reduce_max_sync(0xffffffffu, mx);
+      if (tid == 0) s_flag = 0;
+      __syncthreads();
+      if (lane == 0) atomicMax(&s_flag, mx);
+      __syncthreads();
+      stride = (((size_t)s_flag * ts) + 15) & ~(size_t)15;
+      if (stride * (size_t)a.ncells > a.lay.arena_bytes) {
+        if (blockIdx.x == 0 && tid == 0) report_error(a, RBV_ERR_CAPACITY, 0, a.ncells, (int)(stride >> 10));
+        alive = false;
+      }
     }
     if (blockIdx.x == 0 && tid == 0) my->status.trace[2] = dev::globaltimer();
   }
@@ -203,7 +214,6 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   unsigned base = 0;  // chunks before the current tile
   for (int t0 = 0; t0 < a.nops; t0 += kOpTile) {
     const int tn = min(kOpTile, a.nops - t0);
-    // chunks per op of this tile, then an exclusive scan (tile sizes are small: serial per warp 0)
     for (int i = tid; i < tn; i += blockDim.x) {
       const Op o = a.ops[t0 + i];
       size_t b = alive ? op_bytes(o, sm, P, ts) : 0;
@@ -231,16 +241,17 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     __syncthreads();
     const unsigned total = s_total;
 
-    // first chunk of this tile owned by this CTA
-    unsigned c = (blockIdx.x + gridDim.x - (base % gridDim.x)) % gridDim.x;
+    // first chunk of this tile owned by this warp
+    unsigned c = (gwarp + nwarps - (base % nwarps)) % nwarps;
     int oi = 0;
-    for (; c < total; c += gridDim.x) {
-      while (sm.prefix[oi + 1] <= c) oi++;   // ops are visited in order: monotone search
+    for (; c < total; c += nwarps) {
+      while (sm.prefix[oi + 1] <= c) oi++;   // chunks are visited in order: monotone search
       const Op o = a.ops[t0 + oi];
       const unsigned k = c - sm.prefix[oi];
       const unsigned nch = sm.prefix[oi + 1] - sm.prefix[oi];
       const int lsrc = o.src - a.proc * L;
       const int dproc = o.dst / L, ldst = o.dst - dproc * L;
+      const bool remote = dproc != a.proc;
       bool ok = alive;
       size_t bytes = ok ? op_bytes(o, sm, P, ts) : 0;
 
@@ -248,20 +259,19 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
       if (ok && o.dst_cell < 0) {
         const int cap = sm.caps[(size_t)o.dst * P + o.origin];
         if (cap >= 0 && sm.counts[(size_t)o.origin * P + o.dest] > cap) {
-          if (tid == 0 && k == 0) report_error(a, RBV_ERR_TRUNCATE, 0, o.origin, o.dest);
+          if (lane == 0 && k == 0) report_error(a, RBV_ERR_TRUNCATE, 0, o.origin, o.dest);
           bytes = 0;
         }
       }
       // wait for the source cell
       if (ok && o.src_cell >= 0) {
-        if (tid == 0) {
-          int r = dev::wait_ge(cell_flag_of(a, a.proc, parity, lsrc, o.src_cell), a.seq + 1u, wc);
+        int r = 0;
+        if (lane == 0) {
+          r = dev::wait_ge(cell_flag_of(a, a.proc, parity, lsrc, o.src_cell), seq + 1u, wc, multi);
           if (r == dev::WAIT_TIMEOUT) report_error(a, RBV_ERR_TIMEOUT, WAIT_CELL, t0 + oi, o.src_cell);
-          s_flag = r;
         }
-        __syncthreads();
-        if (s_flag != dev::WAIT_OK) { ok = false; alive = false; }
-        __syncthreads();
+        r = __shfl_sync(0xffffffffu, r, 0);
+        if (r != dev::WAIT_OK) { ok = false; alive = false; }
       }
       if (ok && bytes) {
         const size_t off = (size_t)k * a.chunk_bytes;
@@ -278,24 +288,23 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
           dst = a.heap[dproc] + sm.recvoff[o.dst] + (size_t)sm.rdispl[(size_t)o.dst * P + o.origin] * ts;
         else
           dst = stage_of(a, dproc, parity, ldst) + (size_t)o.dst_cell * stride;
-        dev::cta_copy(dst + off, src + off, len);
+        dev::group_copy(dst + off, src + off, len, lane, 32);
       }
-      __syncthreads();
-      // completion: the CTA that finishes the last chunk of the op signals the destination
-      if (tid == 0) {
+      __syncwarp();
+      // completion: the warp that finishes the last chunk of the op signals the destination
+      if (lane == 0) {
         bool last = true;
         if (nch > 1) {
-          __threadfence_system();
+          dev::fence_acq_rel(remote);   // this chunk's stores become visible before the count does
           unsigned old = atomicAdd(&a.op_done[t0 + oi], 1u);
           last = (old == nch - 1);
           if (last) a.op_done[t0 + oi] = 0;
         }
         if (last) {
-          __threadfence_system();
           if (o.dst_cell < 0)
-            dev::red_release_sys_add(&ctrl_of(a, dproc)->recv_arrivals[ldst], 1ull);
+            dev::signal_add(&ctrl_of(a, dproc)->recv_arrivals[ldst], 1ull, remote);
           else if (ok)
-            dev::st_release_sys(cell_flag_of(a, dproc, parity, ldst, o.dst_cell), a.seq + 1u);
+            dev::signal_store(cell_flag_of(a, dproc, parity, ldst, o.dst_cell), seq + 1u, remote);
         }
       }
     }
@@ -307,8 +316,8 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   if (blockIdx.x == 0) {
     if (tid == 0) my->status.trace[3] = dev::globaltimer();
     if (tid < L) {
-      const unsigned long long target = ((unsigned long long)a.seq + 1ull) * (unsigned long long)P;
-      int r = dev::wait_ge(&my->recv_arrivals[tid], target, wc);
+      const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)P;
+      int r = dev::wait_ge(&my->recv_arrivals[tid], target, wc, multi);
       if (r == dev::WAIT_TIMEOUT)
         report_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, tid, (int)(target - my->recv_arrivals[tid]));
     }
@@ -321,12 +330,10 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     __threadfence();
     if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
       my->exit_count = 0;
+      my->call_seq = seq + 1u;
       if (my->status.code == 0 && dev::ld_relaxed_sys(&my->abort_flag)) my->status.code = RBV_ERR_ABORTED;
       __threadfence();
-      if (a.host_status) {
-        *a.host_status = my->status;
-        __threadfence_system();
-      }
+      if (a.host_status && (my->status.code != 0 || (a.flags & CALL_TRACE))) *a.host_status = my->status;
       my->status.code = 0;
     }
   }
@@ -349,10 +356,13 @@ cudaError_t a2av_configure(int P, int* max_ctas_per_sm) {
   return e;
 }
 
-cudaError_t a2av_launch(const KernelArgs& args, int grid, cudaStream_t stream) {
+cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream) {
   void* params[] = {(void*)&args};
-  return cudaLaunchCooperativeKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params,
-                                     a2av_smem_bytes(args.P), stream);
+  if (cooperative)
+    return cudaLaunchCooperativeKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params,
+                                       a2av_smem_bytes(args.P), stream);
+  return cudaLaunchKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params, a2av_smem_bytes(args.P),
+                          stream);
 }
 
 }  // namespace rbv

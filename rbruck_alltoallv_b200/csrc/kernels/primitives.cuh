@@ -49,13 +49,29 @@ struct WaitCfg {
   unsigned long long timeout_ns;
 };
 
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
 template <typename T>
-__device__ __forceinline__ WaitResult wait_ge(const T* p, T target, const WaitCfg& cfg) {
-  if (ld_acquire_sys(p) >= target) return WAIT_OK;
+__device__ __forceinline__ T ld_acquire(const T* p, bool sys) {
+  return sys ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+}
+
+// `sys` = the value may be written by another GPU (system-scope acquire); otherwise gpu scope.
+template <typename T>
+__device__ __forceinline__ WaitResult wait_ge(const T* p, T target, const WaitCfg& cfg, bool sys = true) {
+  if (ld_acquire(p, sys) >= target) return WAIT_OK;
   unsigned long long t0 = globaltimer();
   unsigned it = 0;
   for (;;) {
-    if (ld_acquire_sys(p) >= target) return WAIT_OK;
+    if (ld_acquire(p, sys) >= target) return WAIT_OK;
     if ((++it & 31u) == 0) {
       if (ld_relaxed_sys(cfg.abort_flag)) return WAIT_ABORTED;
       if (globaltimer() - t0 > cfg.timeout_ns) return WAIT_TIMEOUT;
@@ -109,12 +125,11 @@ __device__ __forceinline__ void copy_shifted(uint4* d, const uint4* s, size_t nv
   }
 }
 
-// Copies n bytes with all threads of the CTA.  dst and src may have any alignment, relative to
-// each other too: stores are 16-byte aligned vectors, loads are aligned vectors re-assembled with
-// funnel shifts when the two phases differ.  Loads bypass L1 (the source may have been written by
-// another GPU).  The caller synchronises.
-__device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t n) {
-  const unsigned tid = threadIdx.x, nt = blockDim.x;
+// Copies n bytes with a group of nt threads (tid = index in the group: a warp or a whole CTA).
+// dst and src may have any alignment, relative to each other too: stores are 16-byte aligned
+// vectors, loads are aligned vectors re-assembled with funnel shifts when the two phases differ.
+// Loads bypass L1 (the source may have been written by another GPU).  The caller synchronises.
+__device__ __forceinline__ void group_copy(char* dst, const char* src, size_t n, unsigned tid, unsigned nt) {
   if (n == 0) return;
   size_t head = (16 - ((uintptr_t)dst & 15)) & 15;
   if (head > n) head = n;
@@ -147,6 +162,28 @@ __device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t n) {
   }
   const size_t done = nvec << 4, tail = n - done;
   if (tid < tail) dst[done + tid] = (char)ld_cg_u8((const unsigned char*)src + done + tid);
+}
+
+__device__ __forceinline__ void cta_copy(char* dst, const char* src, size_t n) {
+  group_copy(dst, src, n, threadIdx.x, blockDim.x);
+}
+
+// ---- scope-selectable signals: gpu scope when producer and consumer share the GPU ----------------
+__device__ __forceinline__ void st_release_gpu(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel(bool sys) {
+  if (sys) asm volatile("fence.acq_rel.sys;" ::: "memory");
+  else asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
+__device__ __forceinline__ void signal_store(unsigned* p, unsigned v, bool sys) {
+  if (sys) st_release_sys(p, v); else st_release_gpu(p, v);
+}
+__device__ __forceinline__ void signal_add(unsigned long long* p, unsigned long long v, bool sys) {
+  if (sys) red_release_sys_add(p, v); else red_release_gpu_add(p, v);
 }
 
 }  // namespace dev

@@ -48,6 +48,30 @@ class _Block:
             self.ptr = None
 
 
+class PreparedCall:
+    """A resolved collective; see :meth:`Communicator.prepare`."""
+
+    def __init__(self, comm: "Communicator", handle, keep):
+        self._comm, self._h, self._keep = comm, C.c_void_p(handle), keep
+        self._launch = comm._lib.rbv_launch
+        self._ctx = comm._ctx
+        self._dev = comm.device
+
+    def launch(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        st = stream or torch.cuda.current_stream(self._dev)
+        rc = self._launch(self._ctx, self._h, C.c_void_p(st.cuda_stream))
+        if rc:
+            raise CommError("launch failed: " + self._comm._lib.rbv_last_error().decode())
+
+    __call__ = launch
+
+    def __del__(self):
+        comm, h = getattr(self, "_comm", None), getattr(self, "_h", None)
+        if comm is not None and h and getattr(comm, "_ctx", None):
+            comm._lib.rbv_prepared_free(comm._ctx, h)
+            self._h = None
+
+
 class Communicator:
     def __init__(self, nranks: Optional[int] = None, device: Optional[int] = None,
                  heap_bytes: int = 1 << 30, arena_bytes: int = 32 << 20, timeout_ms: float = 2000.0):
@@ -138,29 +162,16 @@ class Communicator:
         return t
 
     # ---- collectives --------------------------------------------------------------------------
-    def alltoallv(self, send: Sequence[torch.Tensor] | torch.Tensor, recv: Sequence[torch.Tensor] | torch.Tensor,
-                  sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, algo: str = "spreadout",
-                  n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0, type_size: Optional[int] = None,
-                  inplace: bool = False, grid: int = 0, chunk_bytes: int = 0, bytes_hint: int = -1,
-                  stream: Optional[torch.cuda.Stream] = None) -> None:
-        """Non-uniform all-to-all of the L local ranks (asynchronous on the current stream).
-
-        ``send`` / ``recv`` are one tensor per local rank (a bare tensor when L == 1); ``recv`` must come
-        from :meth:`symm_empty`.  Counts and displacements are in elements, shaped ``[L, P]`` (``[P]`` when
-        L == 1): numpy / lists (host) or int32 / int64 CUDA tensors (device-resident, e.g. produced by a
-        router kernel).  ``sdispls`` / ``rdispls`` default to the packed layout when counts are on the host.
-        ``recvcounts`` is optional: when given, a block larger than its slot is refused (status
-        ``truncate``) instead of overrunning the buffer.
-        """
+    def _marshal(self, send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size):
+        """Normalises the arguments of one collective: pointer arrays, [L, P] count arrays, keep-alive list."""
         L, P = self.L, self.P
         send_l = [send] if isinstance(send, torch.Tensor) else (list(send) if send is not None else [None] * L)
         recv_l = [recv] if isinstance(recv, torch.Tensor) else list(recv)
         if len(send_l) != L or len(recv_l) != L:
             raise ValueError(f"expected {L} send and receive tensors")
-        ref = recv_l[0]
-        ts = int(type_size) if type_size else ref.element_size()
+        ts = int(type_size) if type_size else recv_l[0].element_size()
         on_dev = isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda
-        keep = []
+        keep = [send_l, recv_l]
         if on_dev:
             def dev(a, dt):
                 if a is None:
@@ -172,8 +183,7 @@ class Communicator:
             sd, rd = dev(sdispls, torch.int64), dev(rdispls, torch.int64)
             if sd is None or rd is None:
                 raise ValueError("device-resident counts need explicit displacements")
-            p_sc, p_rc = sc.data_ptr(), (rc.data_ptr() if rc is not None else None)
-            p_sd, p_rd = sd.data_ptr(), rd.data_ptr()
+            ptrs = (sc.data_ptr(), rc.data_ptr() if rc is not None else None, sd.data_ptr(), rd.data_ptr())
         else:
             sc = np.ascontiguousarray(np.asarray(sendcounts, dtype=np.int32).reshape(L, P))
             rc = None if recvcounts is None else np.ascontiguousarray(np.asarray(recvcounts, dtype=np.int32).reshape(L, P))
@@ -190,10 +200,28 @@ class Communicator:
             else:
                 rd = np.ascontiguousarray(np.asarray(rdispls, dtype=np.int64).reshape(L, P))
             keep += [sc, rc, sd, rd]
-            p_sc, p_rc = sc.ctypes.data, (rc.ctypes.data if rc is not None else None)
-            p_sd, p_rd = sd.ctypes.data, rd.ctypes.data
+            ptrs = (sc.ctypes.data, rc.ctypes.data if rc is not None else None, sd.ctypes.data, rd.ctypes.data)
         sp = (C.c_void_p * L)(*[(t.data_ptr() if t is not None else None) for t in send_l])
         rp = (C.c_void_p * L)(*[t.data_ptr() for t in recv_l])
+        keep += [sp, rp]
+        return ts, on_dev, sp, rp, ptrs, keep
+
+    def alltoallv(self, send: Sequence[torch.Tensor] | torch.Tensor, recv: Sequence[torch.Tensor] | torch.Tensor,
+                  sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, algo: str = "spreadout",
+                  n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0, type_size: Optional[int] = None,
+                  inplace: bool = False, grid: int = 0, chunk_bytes: int = 0, bytes_hint: int = -1,
+                  stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Non-uniform all-to-all of the L local ranks (asynchronous on the current stream).
+
+        ``send`` / ``recv`` are one tensor per local rank (a bare tensor when L == 1); ``recv`` must come
+        from :meth:`symm_empty`.  Counts and displacements are in elements, shaped ``[L, P]`` (``[P]`` when
+        L == 1): numpy / lists (host) or int32 / int64 CUDA tensors (device-resident, e.g. produced by a
+        router kernel).  ``sdispls`` / ``rdispls`` default to the packed layout when counts are on the host.
+        ``recvcounts`` is optional: when given, a block larger than its slot is refused (status
+        ``truncate``) instead of overrunning the buffer.
+        """
+        ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
+            send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         st = stream or torch.cuda.current_stream(self.device)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
         rcode = self._lib.rbv_alltoallv(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
@@ -201,6 +229,23 @@ class Communicator:
                                         int(chunk_bytes), C.c_void_p(st.cuda_stream))
         if rcode:
             raise CommError(f"alltoallv({algo}) failed with code {rcode}: {self._lib.rbv_last_error().decode()}")
+
+    def prepare(self, send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None, *,
+                algo: str = "spreadout", n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0,
+                type_size: Optional[int] = None, inplace: bool = False, grid: int = 0, chunk_bytes: int = 0,
+                bytes_hint: int = -1) -> "PreparedCall":
+        """Persistent form of :meth:`alltoallv` (compare ``MPI_Alltoallv_init``): everything is resolved once;
+        ``.launch()`` then costs one kernel launch.  Buffers and counts are fixed (device-resident counts are
+        re-read by every launch, so a router may still change their values)."""
+        ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
+            send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
+        algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
+        h = self._lib.rbv_prepare(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
+                                  1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
+                                  int(chunk_bytes))
+        if not h:
+            raise CommError(f"prepare({algo}) failed: {self._lib.rbv_last_error().decode()}")
+        return PreparedCall(self, h, keep)
 
     # ---- status -------------------------------------------------------------------------------
     def status(self) -> dict:
@@ -225,6 +270,13 @@ class Communicator:
         self.host_barrier()
         self._lib.rbv_ctx_reset(self._ctx)
         self.host_barrier()
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Have every following call report its phase time stamps (``status()['phases_us']``)."""
+        self._lib.rbv_ctx_set_trace(self._ctx, 1 if on else 0)
+
+    def set_cooperative(self, on: bool) -> None:
+        self._lib.rbv_ctx_set_cooperative(self._ctx, 1 if on else 0)
 
     def set_timeout_ms(self, ms: float) -> None:
         self._lib.rbv_ctx_set_timeout_ms(self._ctx, float(ms))

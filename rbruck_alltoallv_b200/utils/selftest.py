@@ -1,0 +1,139 @@
+"""Multi-process self test: every algorithm against the direct-copy expectation, one process per GPU.
+
+    torchrun --nproc-per-node N --master-addr 127.0.0.1 -m rbruck_alltoallv_b200.utils.selftest [--nranks P]
+
+Each process checks its own ranks; the exit code is non-zero when any block differs.  With ``--bench`` it
+also prints device-timed latencies next to NCCL's grouped send/recv for a few block sizes.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..parallel.comm import Communicator
+from . import distributions as D
+from . import oracle
+from .timing import L2Flusher, RankAligner, time_steps
+
+CASES = [("linear", {}), ("spreadout", {}), ("scattered", dict(b=2)), ("pairwise", {}), ("xor", {}),
+         ("rbruck", dict(r=2)), ("rbruck", dict(r=3)), ("rbruck_om", dict(r=2)), ("tuna", dict(r=2, b=1)),
+         ("tuna2", dict(r=2, b=0)), ("ttpl", dict(n=2, r=2)), ("ttpl_bt", dict(n=2, r=2)),
+         ("ttpl_bt_s1", dict(n=2, r=2, b=2)), ("ttpl_bt_s2", dict(n=2, r=2)),
+         ("uniform_spreadout_twolayer", dict(n=2, r=2)), ("uniform_isplit_rbruck", dict(n=2, r=2, r2=2)),
+         ("twolayer_linear", dict(n=2)), ("twolayer_linear_s2", dict(n=2, b=1, b2=2)),
+         ("twolayer_linear_s3", dict(n=2, b=1, b2=1))]
+
+
+def check_all(comm: Communicator, ts: int = 4, seed: int = 3) -> int:
+    P, mine = comm.P, comm.local_ranks
+    failures = 0
+    for ci, (algo, kw) in enumerate(CASES):
+        if algo == "xor" and P & (P - 1):
+            continue
+        if kw.get("n") and (P % kw["n"] or kw["n"] >= P):
+            continue
+        counts = D.uniform(P, 3000, seed=seed + ci)
+        counts[counts < 200] = 0
+        prob = oracle.make_problem(counts, ts, seed + ci, packed=(ci % 2 == 0))
+        send_h = oracle.fill_send(prob, seed + ci)
+        want = oracle.expected_recv(prob, send_h)
+        send = [torch.from_numpy(send_h[r]).cuda() for r in mine]
+        recv = [comm.symm_empty(len(want[r]), torch.uint8) for r in mine]
+        for t in recv:
+            t.fill_(oracle.CANARY)
+        torch.cuda.synchronize()
+        comm.host_barrier()
+        for rep in range(3):   # back-to-back calls exercise both parities
+            comm.alltoallv(send, recv, prob.counts[mine], prob.sdispls[mine], prob.recvcounts[mine], prob.rdispls[mine],
+                           algo=algo, type_size=ts, **kw)
+        st = comm.status()
+        bad = oracle.first_mismatch([t.cpu().numpy() for t in recv], [want[r] for r in mine])
+        if st["code"] or bad is not None:
+            failures += 1
+            print(f"[proc {comm.proc}] FAIL {algo} {kw}: status={st['name']}@{st['site']} {st['detail']} mismatch={bad}",
+                  flush=True)
+            comm.reset()
+        comm.host_barrier()
+        del send, recv
+    return failures
+
+
+def bench(comm: Communicator, sizes=(16, 1024, 65536, 1 << 20, 4 << 20)) -> list:
+    P, L, mine = comm.P, comm.L, comm.local_ranks
+    dev = f"cuda:{comm.device}"
+    flush, align = L2Flusher(dev), RankAligner(comm)
+    rows = []
+    for nbytes in sizes:
+        elems = max(1, nbytes // 2)
+        counts = D.normal(P, elems, 0.25, seed=nbytes)
+        sc = counts[mine].astype(np.int32)
+        rc = counts.T[mine].astype(np.int32)
+        send = [torch.zeros(max(int(sc[i].sum()), 1), dtype=torch.bfloat16, device=dev) for i in range(L)]
+        recv = [comm.symm_empty(max(int(rc[i].sum()), 1), torch.bfloat16) for i in range(L)]
+        row = {"mean_block_bytes": nbytes, "total_bytes": int(counts.sum()) * 2, "us": {}}
+        for name, kw in (("spreadout", dict(algo="spreadout")), ("rbruck_r2", dict(algo="rbruck", r=2)),
+                         ("tuna2_r2", dict(algo="tuna2", r=2)), ("pairwise", dict(algo="pairwise"))):
+            try:
+                call = comm.prepare(send, recv, sc, None, rc, None, **kw)
+            except Exception as e:  # noqa: BLE001
+                row["us"][name] = f"n/a ({e})"
+                continue
+            t = time_steps(call.launch, steps=20, warmup=3, flush=flush, align=align)
+            st = comm.status()
+            if st["code"]:
+                row["us"][name] = st["name"]
+                comm.reset()
+            else:
+                row["us"][name] = round(float(np.median(t)) * 1e3, 2)
+        if comm.nproc > 1 and L == 1:
+            r1 = torch.empty(max(int(rc[0].sum()), 1), dtype=torch.bfloat16, device=dev)
+            ns, nr = int(sc[0].sum()), int(rc[0].sum())
+            ins, outs = [int(x) for x in sc[0]], [int(x) for x in rc[0]]
+            fn = lambda: dist.all_to_all_single(r1[:nr], send[0][:ns], output_split_sizes=outs, input_split_sizes=ins)
+            t = time_steps(fn, steps=20, warmup=3, flush=flush, align=align)
+            row["us"]["nccl_grouped_sendrecv"] = round(float(np.median(t)) * 1e3, 2)
+        rows.append(row)
+        del send, recv
+    return rows
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--nranks", type=int, default=0)
+    ap.add_argument("--bench", action="store_true")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    comm = Communicator(nranks=args.nranks or max(world, 1), heap_bytes=1 << 30, arena_bytes=64 << 20)
+    failures = check_all(comm)
+    if world > 1:
+        f = torch.tensor([failures], device="cuda")
+        dist.all_reduce(f)
+        failures = int(f.item())
+    rows = bench(comm) if args.bench and failures == 0 else None
+    if comm.proc == 0:
+        line = {"selftest": "ok" if failures == 0 else "FAILED", "failures": failures, "P": comm.P, "gpus": comm.nproc}
+        if rows is not None:
+            line["bench"] = rows
+        print(json.dumps(line), flush=True)
+        if args.out:
+            with open(args.out, "a") as fh:
+                fh.write(json.dumps(line) + "\n")
+    comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 1 if failures else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,35 @@
+"""Multi-process tests (one process per GPU); skipped where fewer than two GPUs are visible."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ngpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _torchrun(nproc, args, port):
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "rbruck_alltoallv_b200.utils.selftest", *args]
+    return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+def test_two_processes(nranks):
+    res = _torchrun(2, ["--nranks", str(nranks)], 29611 + nranks)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert '"selftest": "ok"' in res.stdout
+
+
+@pytest.mark.skipif(_ngpus() < 4, reason="needs 4 GPUs")
+def test_four_processes():
+    res = _torchrun(4, ["--nranks", "8"], 29631)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
