@@ -50,3 +50,13 @@ def declare_cuda(lib):
     lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
     lib.rbv_ctx_set_cooperative.argtypes = [C.c_void_p, C.c_int]
+    declare_moe(lib)
+
+
+def declare_moe(lib):
+    vp, i, ll, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_ulonglong
+    lib.rbv_grouped_gemm_bf16.argtypes = [vp, ll, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    lib.rbv_moe_route.argtypes = [vp, i, i, vp, vp, vp, vp]
+    lib.rbv_moe_layout.argtypes = [vp, i, i, i, vp, vp, vp, vp, vp, vp]
+    lib.rbv_moe_dispatch.argtypes = [vp, vp, i, i, vp, vp, vp, vp, ull, ll, i, vp, vp]
+    lib.rbv_moe_combine.argtypes = [vp, vp, i, i, vp, vp, vp, ull, i, vp, vp]

@@ -7,31 +7,9 @@
 
 #include "rbv/context.h"
 #include "rbv/rbruckv.h"
+#include "api/ctx_internal.h"
 
 using namespace rbv;
-
-struct rbv_comm_s {
-  rbv_ctx_s* ctx;
-  int local;
-};
-
-struct rbv_ctx_s {
-  std::unique_ptr<Context> c;
-  cudaStream_t stream = nullptr;
-  int grid = 0;
-  size_t chunk = 0;
-  std::vector<rbv_comm_s> comms;
-  // calls of the local ranks collected until all L have arrived
-  int pend = 0;
-  AlgoSpec spec;
-  int ts = 0;
-  unsigned flags = 0;
-  std::vector<char> seen;
-  std::vector<const void*> sendbufs;
-  std::vector<void*> recvbufs;
-  std::vector<int> sc, rc;
-  std::vector<long long> sd, rd;
-};
 
 static thread_local std::string g_err;
 

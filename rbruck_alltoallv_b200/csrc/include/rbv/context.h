@@ -96,6 +96,7 @@ class Context {
   // with a host barrier before and after.
   cudaError_t reset();
   void set_timeout_ns(unsigned long long ns) { timeout_ns_ = ns; }
+  unsigned long long timeout_ns() const { return timeout_ns_; }
   // Fault injection for tests: the given local rank skips its metadata row in the next calls (-1: off).
   void set_absent_rank(int lr) { absent_rank_ = lr; }
   const std::string& last_error() const { return last_error_; }

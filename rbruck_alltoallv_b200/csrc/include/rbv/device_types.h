@@ -62,6 +62,11 @@ struct CtrlBlock {
   unsigned int call_seq;         // 0-based number of the next call; bumped by the last CTA of every call, so
                                  // that kernel arguments do not change from call to call
   StatusBlock status;
+  // Auxiliary barriers of the fused kernels built on the same heap (0 MoE dispatch, 1 MoE combine,
+  // 2 FFT transpose, 3 spare): arrivals are monotonic, seq counts finished calls, exit counts CTAs.
+  unsigned long long aux_arrivals[4];
+  unsigned int aux_seq[4];
+  unsigned int aux_exit[4];
 };
 
 // Byte offsets of the regions of a heap; identical on every process of a communicator.

@@ -1,0 +1,55 @@
+/* Expert-parallel MoE path: router, dispatch (permute fused with the all-to-all), grouped expert GEMM on
+ * the sm_100a tensor cores, combine (return all-to-all fused with the gate-weighted sum).  Nothing of this
+ * exists in the reference, which ships only the alltoallv primitive and recorded MoE-like traffic traces
+ * (inputs/, examples/MLinputs_example.cpp); it is built on the same symmetric heap and peer mappings as the
+ * alltoallv kernels.
+ */
+#ifndef RBV_MOE_H_
+#define RBV_MOE_H_
+
+#include "rbv/rbruckv.h"
+
+#ifdef __cplusplus
+namespace rbv { constexpr int kMoeMaxGroups = 64; constexpr int kMoeMaxExperts = 256; }
+extern "C" {
+#endif
+
+/* C[rows of group g] = epi(A[rows of group g] * B_g^T), bf16 in / bf16 out, fp32 accumulation.
+ *   A: [a_rows, K] row-major.  B: [G, N, K] (each expert's weight with K contiguous).  C: rows of ldc elements.
+ *   group_start / group_rows: device int32[G].  N % 256 == 0, K % 64 == 0.
+ *   epilogue 0: C is [*, N];  epilogue 1 (SwiGLU): B rows interleave gate and up (2j = gate_j, 2j+1 = up_j) and
+ *   C is [*, N/2] with C[:, j] = silu(gate_j) * up_j.
+ *   error_flag: device int, set non-zero if a bounded wait inside the kernel ran out.
+ * Returns 0 or a CUDA error code. */
+int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void* B, void* C, const int* group_start,
+                          const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
+                          int max_ctas, void* cuda_stream);
+
+/* Router: softmax over E logits per token, top-2, weights renormalised to sum to one.
+ *   logits [T, E] fp32;  topk_idx [T, 2] int32;  topk_w [T, 2] fp32;  hist [E] int32 (zeroed by the call). */
+int rbv_moe_route(const float* logits, int T, int E, int* topk_idx, float* topk_w, int* hist, void* cuda_stream);
+
+/* From the all-gathered histograms hist_all [P, E] computes, for rank `me`:
+ *   dst_base [E]   first row of this rank's rows for expert e inside the owner's receive buffer,
+ *   group_start / group_rows [E / P]  row ranges of the local experts, cursor [E] zeroed,
+ *   totals [2]     rows received by this rank, rows sent by this rank. */
+int rbv_moe_layout(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start, int* group_rows,
+                   int* cursor, int* totals, void* cuda_stream);
+
+/* Dispatch: every routed (token, k) row of x [T, H] bf16 is stored straight into its expert-sorted row of the
+ * owner GPU's receive buffer (`xrecv_off` = byte offset of that buffer inside every process's heap).  slot [T, 2]
+ * receives the destination row.  The kernel returns when the rows of ALL ranks have landed here (bounded wait).
+ * One logical rank per process. */
+int rbv_moe_dispatch(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                     int* cursor, int* slot, unsigned long long xrecv_off, long long recv_capacity_rows,
+                     int E, int* error_flag, void* cuda_stream);
+
+/* Combine: out[t] = sum_k w[t,k] * Y_owner(k)[slot[t,k]], rows pulled from the owners' `y_off` buffers over
+ * NVLink after a bounded cross-GPU barrier ("all expert outputs are complete"). */
+int rbv_moe_combine(rbv_ctx_t ctx, void* out, int T, int H, const int* topk_idx, const float* topk_w,
+                    const int* slot, unsigned long long y_off, int E, int* error_flag, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,331 @@
+// MoE expert-parallel kernels around the grouped GEMM: router, layout, dispatch (permute fused with the
+// all-to-all: every routed row is stored straight into its expert-sorted position on the owner GPU over
+// NVLink) and combine (the return all-to-all fused with the gate-weighted sum: rows are pulled from the
+// owners' output buffers).  The reference has no counterpart; the cross-GPU synchronisation follows the
+// same rules as the alltoallv kernel (monotonic counters, bounded waits, no reset between calls).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "api/ctx_internal.h"
+#include "kernels/primitives.cuh"
+#include "rbv/device_types.h"
+#include "rbv/moe.h"
+
+namespace rbv {
+namespace {
+
+constexpr int kMoeThreads = 512;
+
+// ---------------------------------------------------------------------------------------------
+// Router: one warp per token.
+// ---------------------------------------------------------------------------------------------
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int* __restrict__ topk_idx,
+                                 float* __restrict__ topk_w, int* __restrict__ hist) {
+  __shared__ int s_hist[kMoeMaxExperts];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) s_hist[i] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    const float* row = logits + (size_t)t * E;
+    float v[kMoeMaxExperts / 32];
+    float mx = -INFINITY;
+    #pragma unroll
+    for (int j = 0; j < kMoeMaxExperts / 32; j++) {
+      int e = j * 32 + lane;
+      v[j] = e < E ? row[e] : -INFINITY;
+      mx = fmaxf(mx, v[j]);
+    }
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // top-2 by (value, lower index wins ties)
+    float best[2]; int bi[2];
+    #pragma unroll
+    for (int k = 0; k < 2; k++) {
+      float bv = -INFINITY; int be = 0x7fffffff;
+      #pragma unroll
+      for (int j = 0; j < kMoeMaxExperts / 32; j++) {
+        int e = j * 32 + lane;
+        bool taken = (k == 1 && e == bi[0]);
+        if (e < E && !taken && (v[j] > bv || (v[j] == bv && e < be))) { bv = v[j]; be = e; }
+      }
+      #pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+      }
+      best[k] = bv; bi[k] = be;
+    }
+    // softmax probabilities of the two winners, renormalised: p_k / (p_0 + p_1)
+    const float p0 = __expf(best[0] - mx), p1 = __expf(best[1] - mx);
+    const float inv = 1.0f / (p0 + p1);
+    if (lane == 0) {
+      topk_idx[2 * t] = bi[0]; topk_idx[2 * t + 1] = bi[1];
+      topk_w[2 * t] = p0 * inv; topk_w[2 * t + 1] = p1 * inv;
+      atomicAdd(&s_hist[bi[0]], 1);
+      atomicAdd(&s_hist[bi[1]], 1);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += blockDim.x)
+    if (s_hist[i]) atomicAdd(&hist[i], s_hist[i]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layout: one CTA.  Receive buffer of a rank = its local experts in order; inside an expert the
+// rows of source rank 0, then 1, ...
+// ---------------------------------------------------------------------------------------------
+__global__ void moe_layout_kernel(const int* __restrict__ hist_all, int P, int E, int me, int* dst_base,
+                                  int* group_start, int* group_rows, int* cursor, int* totals) {
+  __shared__ int s_tot[kMoeMaxExperts];      // rows of expert e over all sources
+  __shared__ int s_before[kMoeMaxExperts];   // rows of expert e from sources < me
+  const int El = E / P;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, before = 0;
+    for (int s = 0; s < P; s++) {
+      int c = hist_all[s * E + e];
+      if (s < me) before += c;
+      tot += c;
+    }
+    s_tot[e] = tot; s_before[e] = before;
+    cursor[e] = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int owner = e / El;
+    int base = 0;
+    for (int e2 = owner * El; e2 < e; e2++) base += s_tot[e2];
+    dst_base[e] = base + s_before[e];
+    if (owner == me) { group_start[e - owner * El] = base; group_rows[e - owner * El] = s_tot[e]; }
+  }
+  if (threadIdx.x == 0) {
+    int recv = 0, sent = 0;
+    for (int e = me * El; e < (me + 1) * El; e++) recv += s_tot[e];
+    for (int e = 0; e < E; e++) sent += hist_all[me * E + e];
+    totals[0] = recv; totals[1] = sent;
+  }
+}
+
+struct MoeComm {
+  int nproc, proc;
+  unsigned long long ctrl_off;
+  unsigned long long timeout_ns;
+  int* error;               // device flag: 0 ok, else (site << 8 | detail)
+  char* heap[kMaxProcs];
+};
+
+__device__ __forceinline__ CtrlBlock* ctrl_of(const MoeComm& c, int q) {
+  return reinterpret_cast<CtrlBlock*>(c.heap[q] + c.ctrl_off);
+}
+
+__device__ void moe_fail(const MoeComm& c, int site, int detail) {
+  atomicCAS(c.error, 0, (site << 8) | (detail & 0xff));
+}
+
+}  // namespace
+}  // namespace rbv
+
+namespace rbv {
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Dispatch: one warp per routed row.
+// ---------------------------------------------------------------------------------------------
+struct DispatchArgs {
+  MoeComm comm;
+  const char* x;            // [T, H] bf16
+  int T, H, E, El;
+  const int* topk_idx;      // [T, 2]
+  const int* dst_base;      // [E]
+  int* cursor;              // [E], zero on entry
+  int* slot;                // [T, 2] out
+  unsigned long long xrecv_off;
+  long long capacity_rows;
+};
+
+__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
+  const MoeComm& c = a.comm;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const size_t row_bytes = (size_t)a.H * 2;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < 2 * a.T; r += warps) {
+    const int e = a.topk_idx[r];
+    int pos = 0;
+    if (lane == 0) pos = a.dst_base[e] + atomicAdd(&a.cursor[e], 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (lane == 0) a.slot[r] = pos;
+    if (pos >= a.capacity_rows) { if (lane == 0) moe_fail(c, 4, e); continue; }
+    const int owner = e / a.El;
+    char* dst = c.heap[owner] + a.xrecv_off + (size_t)pos * row_bytes;
+    dev::group_copy(dst, a.x + (size_t)(r >> 1) * row_bytes, row_bytes, lane, 32);
+  }
+  // completion: the last CTA tells every process that this rank's rows are in place, then waits for all ranks
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    CtrlBlock* my = ctrl_of(c, c.proc);
+    dev::fence_acq_rel(c.nproc > 1);
+    if (atomicAdd(&my->aux_exit[0], 1u) == gridDim.x - 1) {
+      my->aux_exit[0] = 0;
+      const unsigned seq = my->aux_seq[0];
+      for (int q = 0; q < c.nproc; q++) dev::signal_add(&ctrl_of(c, q)->aux_arrivals[0], 1ull, q != c.proc);
+      dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
+      const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
+      if (dev::wait_ge(&my->aux_arrivals[0], target, wc, c.nproc > 1) != dev::WAIT_OK) moe_fail(c, 1, 0);
+      my->aux_seq[0] = seq + 1u;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Combine: cross-GPU barrier, then one warp per token pulls its two expert rows.
+// ---------------------------------------------------------------------------------------------
+struct CombineArgs {
+  MoeComm comm;
+  char* out;                // [T, H] bf16
+  int T, H, E, El;
+  const int* topk_idx;
+  const float* topk_w;
+  const int* slot;
+  unsigned long long y_off;
+};
+
+__device__ __forceinline__ void bf16x8_fma(float (&acc)[8], const uint4& v, float w) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  #pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+    acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+  }
+}
+
+__global__ void __launch_bounds__(kMoeThreads) moe_combine_kernel(const __grid_constant__ CombineArgs a) {
+  const MoeComm& c = a.comm;
+  __shared__ int s_ok;
+  CtrlBlock* my = ctrl_of(c, c.proc);
+  if (threadIdx.x == 0) {
+    const unsigned seq = __ldcg(&my->aux_seq[1]);
+    if (blockIdx.x == 0)
+      for (int q = 0; q < c.nproc; q++) dev::signal_add(&ctrl_of(c, q)->aux_arrivals[1], 1ull, q != c.proc);
+    dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
+    const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
+    int r = dev::wait_ge(&my->aux_arrivals[1], target, wc, c.nproc > 1);
+    if (r != dev::WAIT_OK) moe_fail(c, 2, 0);
+    s_ok = (r == dev::WAIT_OK);
+  }
+  __syncthreads();
+  if (s_ok) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nvec = a.H / 8;   // 16-byte vectors per row
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < a.T; t += warps) {
+      const int e0 = a.topk_idx[2 * t], e1 = a.topk_idx[2 * t + 1];
+      const float w0 = a.topk_w[2 * t], w1 = a.topk_w[2 * t + 1];
+      const uint4* r0 = reinterpret_cast<const uint4*>(c.heap[e0 / a.El] + a.y_off + (size_t)a.slot[2 * t] * a.H * 2);
+      const uint4* r1 = reinterpret_cast<const uint4*>(c.heap[e1 / a.El] + a.y_off + (size_t)a.slot[2 * t + 1] * a.H * 2);
+      uint4* o = reinterpret_cast<uint4*>(a.out + (size_t)t * a.H * 2);
+      for (int i = lane; i < nvec; i += 32) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        bf16x8_fma(acc, dev::ld_cg_v4(r0 + i), w0);
+        bf16x8_fma(acc, dev::ld_cg_v4(r1 + i), w1);
+        uint4 v;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+        #pragma unroll
+        for (int j = 0; j < 4; j++) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o[i] = v;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(&my->aux_exit[1], 1u) == gridDim.x - 1) {
+      my->aux_exit[1] = 0;
+      my->aux_seq[1] = my->aux_seq[1] + 1u;
+    }
+  }
+}
+
+MoeComm make_comm(rbv_ctx_t ctx, int* error) {
+  MoeComm m;
+  const Context& c = *ctx->c;
+  m.nproc = c.nproc(); m.proc = c.proc();
+  m.ctrl_off = c.layout().ctrl_off;
+  m.timeout_ns = c.timeout_ns();
+  m.error = error;
+  for (int q = 0; q < kMaxProcs; q++) m.heap[q] = q < c.nproc() ? c.peer_heap(q) : nullptr;
+  return m;
+}
+
+}  // namespace
+}  // namespace rbv
+
+using namespace rbv;
+
+extern "C" {
+
+int rbv_moe_route(const float* logits, int T, int E, int* topk_idx, float* topk_w, int* hist, void* stream) {
+  if (E < 2 || E > kMoeMaxExperts) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(hist, 0, sizeof(int) * E, st);
+  if (e != cudaSuccess) return (int)e;
+  const int warps_per_cta = 8;
+  int grid = (T + warps_per_cta - 1) / warps_per_cta;
+  grid = grid < 1 ? 1 : (grid > 1184 ? 1184 : grid);
+  moe_route_kernel<<<grid, warps_per_cta * 32, 0, st>>>(logits, T, E, topk_idx, topk_w, hist);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_layout(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start, int* group_rows,
+                   int* cursor, int* totals, void* stream) {
+  if (E > kMoeMaxExperts || E % P) return (int)cudaErrorInvalidValue;
+  moe_layout_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(hist_all, P, E, me, dst_base, group_start,
+                                                                        group_rows, cursor, totals);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+extern "C" {
+
+int rbv_moe_dispatch(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                     int* cursor, int* slot, unsigned long long xrecv_off, long long recv_capacity_rows,
+                     int E, int* error_flag, void* stream) {
+  const Context& c = *ctx->c;
+  if (c.L() != 1 || E % c.P() || (H % 8)) return (int)cudaErrorInvalidValue;
+  DispatchArgs a;
+  a.comm = make_comm(ctx, error_flag);
+  a.x = static_cast<const char*>(x);
+  a.T = T; a.H = H; a.E = E; a.El = E / c.P();
+  a.topk_idx = topk_idx; a.dst_base = dst_base; a.cursor = cursor; a.slot = slot;
+  a.xrecv_off = xrecv_off; a.capacity_rows = recv_capacity_rows;
+  const int warps_per_cta = kMoeThreads / 32;
+  int grid = (2 * T + warps_per_cta - 1) / warps_per_cta;
+  const int cap = c.sm_count() * 2;
+  grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
+  moe_dispatch_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_combine(rbv_ctx_t ctx, void* out, int T, int H, const int* topk_idx, const float* topk_w,
+                    const int* slot, unsigned long long y_off, int E, int* error_flag, void* stream) {
+  const Context& c = *ctx->c;
+  if (c.L() != 1 || E % c.P() || (H % 8)) return (int)cudaErrorInvalidValue;
+  CombineArgs a;
+  a.comm = make_comm(ctx, error_flag);
+  a.out = static_cast<char*>(out);
+  a.T = T; a.H = H; a.E = E; a.El = E / c.P();
+  a.topk_idx = topk_idx; a.topk_w = topk_w; a.slot = slot; a.y_off = y_off;
+  const int warps_per_cta = kMoeThreads / 32;
+  int grid = (T + warps_per_cta - 1) / warps_per_cta;
+  // every CTA waits on the barrier, so all of them must be able to run without waiting for each other:
+  // only CTA 0 signals and the signal does not depend on any other CTA, which keeps any grid size safe
+  const int cap = c.sm_count() * 2;
+  grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
+  moe_combine_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,153 @@
+"""Expert-parallel MoE forward on the symmetric heap: router -> dispatch -> grouped SwiGLU FFN -> combine.
+
+Kernels: ``csrc/kernels/moe_kernels.cu`` (router, layout, dispatch fused with the token permute, combine
+fused with the gate-weighted sum) and ``csrc/kernels/grouped_gemm_sm100.cu`` (tcgen05 / TMEM grouped GEMM
+fed by TMA).  The reference library has no MoE code; its only trace of this workload are the recorded
+all-to-all count matrices under ``inputs/``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import _native
+
+
+def _p(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def grouped_gemm(A: torch.Tensor, B: torch.Tensor, group_start: torch.Tensor, group_rows: torch.Tensor,
+                 out: Optional[torch.Tensor] = None, swiglu: bool = False, error: Optional[torch.Tensor] = None,
+                 max_ctas: int = 0) -> torch.Tensor:
+    """``out[rows of g] = epi(A[rows of g] @ B[g].T)`` with bf16 operands and fp32 accumulation.
+
+    ``A`` [M, K], ``B`` [G, N, K], ``group_start`` / ``group_rows`` int32 CUDA tensors [G].  With ``swiglu``
+    the rows of ``B[g]`` interleave gate and up projections and ``out`` is [M, N // 2]."""
+    lib = _native.cuda_lib()
+    assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
+    G, N, K = B.shape
+    M = A.shape[0]
+    assert A.shape[1] == K
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(M, n_out, dtype=torch.bfloat16, device=A.device)
+    if error is None:
+        error = torch.zeros(1, dtype=torch.int32, device=A.device)
+    st = torch.cuda.current_stream(A.device).cuda_stream
+    rc = lib.rbv_grouped_gemm_bf16(_p(A), M, _p(B), _p(out), _p(group_start), _p(group_rows), G, N, K,
+                                   out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas), C.c_void_p(st))
+    if rc:
+        raise RuntimeError(f"grouped GEMM launch failed (CUDA error {rc})")
+    return out
+
+
+def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Interleaves [G, I, H] gate and up weights into the [G, 2I, H] layout the SwiGLU epilogue expects."""
+    G, I, H = gate.shape
+    return torch.stack([gate, up], dim=2).reshape(G, 2 * I, H).contiguous()
+
+
+class MoEExpertParallel:
+    """One MoE FFN layer sharded by experts over the ranks of a communicator (one rank per GPU)."""
+
+    def __init__(self, comm, num_experts: int, hidden: int, inter: int, tokens: int, capacity_factor: float = 2.0,
+                 seed: int = 0, init_std: float = 0.02):
+        if comm.L != 1:
+            raise ValueError("the MoE path needs one rank per process")
+        if num_experts % comm.P:
+            raise ValueError("experts must divide evenly over the ranks")
+        self.comm, self.lib = comm, _native.cuda_lib()
+        self.P, self.me = comm.P, comm.proc
+        self.E, self.El, self.H, self.I, self.T = num_experts, num_experts // comm.P, hidden, inter, tokens
+        dev = f"cuda:{comm.device}"
+        self.dev = dev
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed * 1000 + self.me)
+        bf = torch.bfloat16
+        self.w13 = (torch.randn(self.El, 2 * inter, hidden, device=dev, generator=g) * init_std).to(bf)
+        self.w2 = (torch.randn(self.El, hidden, inter, device=dev, generator=g) * init_std).to(bf)
+        self.cap = int(np.ceil(capacity_factor * 2 * tokens / 128.0)) * 128
+        i32 = torch.int32
+        self.xrecv = comm.symm_empty((self.cap, hidden), bf)
+        self.y = comm.symm_empty((self.cap, hidden), bf)
+        self.h = torch.empty(self.cap, inter, dtype=bf, device=dev)
+        self.hist = torch.zeros(self.E, dtype=i32, device=dev)
+        self.hist_all = comm.symm_zeros((self.P, self.E), i32)
+        self.topk_idx = torch.empty(tokens, 2, dtype=i32, device=dev)
+        self.topk_w = torch.empty(tokens, 2, dtype=torch.float32, device=dev)
+        self.slot = torch.empty(tokens, 2, dtype=i32, device=dev)
+        self.dst_base = torch.empty(self.E, dtype=i32, device=dev)
+        self.cursor = torch.zeros(self.E, dtype=i32, device=dev)
+        self.group_start = torch.zeros(self.El, dtype=i32, device=dev)
+        self.group_rows = torch.zeros(self.El, dtype=i32, device=dev)
+        self.totals = torch.zeros(2, dtype=i32, device=dev)
+        self.error = torch.zeros(4, dtype=i32, device=dev)
+        heap0 = self.lib.rbv_ctx_heap(comm._ctx, comm.proc)
+        self.xrecv_off = self.xrecv.data_ptr() - heap0
+        self.y_off = self.y.data_ptr() - heap0
+        # the histogram all-gather: every rank sends the same E counters to every rank
+        cnt = np.full((1, self.P), self.E, dtype=np.int32)
+        self._gather = comm.prepare(self.hist, self.hist_all.view(-1), cnt, np.zeros((1, self.P), dtype=np.int64), cnt,
+                                    (np.arange(self.P, dtype=np.int64) * self.E).reshape(1, self.P),
+                                    algo="spreadout", type_size=4, grid=1)
+
+    def _check(self, rc, what):
+        if rc:
+            raise RuntimeError(f"{what} failed (CUDA error {rc})")
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, H = x.shape
+        assert T == self.T and H == self.H and x.dtype == torch.bfloat16 and x.is_contiguous()
+        assert logits.shape == (T, self.E) and logits.dtype == torch.float32 and logits.is_contiguous()
+        lib, ctx = self.lib, self.comm._ctx
+        st = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        if out is None:
+            out = torch.empty_like(x)
+        self._check(lib.rbv_moe_route(_p(logits), T, self.E, _p(self.topk_idx), _p(self.topk_w), _p(self.hist), st),
+                    "router")
+        self._gather.launch()
+        self._check(lib.rbv_moe_layout(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
+                                       _p(self.group_start), _p(self.group_rows), _p(self.cursor), _p(self.totals),
+                                       st), "layout")
+        self._check(lib.rbv_moe_dispatch(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base), _p(self.cursor),
+                                         _p(self.slot), self.xrecv_off, self.cap, self.E, _p(self.error[0:1]), st),
+                    "dispatch")
+        grouped_gemm(self.xrecv, self.w13, self.group_start, self.group_rows, out=self.h, swiglu=True,
+                     error=self.error[1:2])
+        grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False,
+                     error=self.error[2:3])
+        self._check(lib.rbv_moe_combine(ctx, _p(out), T, H, _p(self.topk_idx), _p(self.topk_w), _p(self.slot),
+                                        self.y_off, self.E, _p(self.error[3:4]), st), "combine")
+        return out
+
+    def check(self):
+        """Synchronises and raises if any kernel of the layer recorded an error."""
+        e = self.error.cpu().tolist()
+        if any(e):
+            raise RuntimeError(f"MoE kernels reported errors (dispatch, gemm1, gemm2, combine) = {e}")
+        self.comm.check()
+
+    def flops(self, routed_rows: int) -> float:
+        return routed_rows * (2.0 * self.H * 2 * self.I + 2.0 * self.I * self.H)
+
+
+def reference_forward(x, logits, w13_all, w2_all):
+    """fp32 PyTorch reference of the whole layer on one device.  ``w13_all`` [E, 2I, H] interleaved,
+    ``w2_all`` [E, H, I]; intermediate activations are rounded to bf16 where the kernels round them."""
+    xf = x.float()
+    p = torch.softmax(logits.float(), dim=-1)
+    top_p, top_i = torch.topk(p, 2, dim=-1)
+    w = top_p / top_p.sum(-1, keepdim=True)
+    out = torch.zeros_like(xf)
+    for k in range(2):
+        for e in torch.unique(top_i[:, k]).tolist():
+            rows = (top_i[:, k] == e).nonzero().squeeze(1)
+            gu = xf[rows] @ w13_all[e].float().t()
+            hmid = (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]).to(torch.bfloat16).float()
+            yv = (hmid @ w2_all[e].float().t()).to(torch.bfloat16).float()
+            out[rows] += w[rows, k:k + 1] * yv
+    return out, top_i, w

@@ -1,0 +1,79 @@
+"""GPU tests of the MoE path: grouped tcgen05 GEMM, router, and the full dispatch/FFN/combine layer."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _groups(rows, device):
+    start = np.concatenate([[0], np.cumsum(rows)[:-1]]).astype(np.int32)
+    return (torch.from_numpy(start).to(device), torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(device))
+
+
+@pytest.mark.parametrize("rows,N,K", [([128, 128], 256, 64), ([100, 37, 0, 300], 256, 128), ([513, 64, 1], 512, 256),
+                                      ([1000, 24], 1024, 512)])
+def test_grouped_gemm_matches_fp32(rows, N, K):
+    from rbruck_alltoallv_b200.ops.moe import grouped_gemm
+    torch.manual_seed(0)
+    G, M = len(rows), int(sum(rows))
+    A = torch.randn(M + 5, K, device="cuda").to(torch.bfloat16)
+    B = (torch.randn(G, N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    gs, gr = _groups(rows, "cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((M + 5, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    grouped_gemm(A, B, gs, gr, out=out, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    r0 = 0
+    for g, n in enumerate(rows):
+        ref = A[r0:r0 + n].float() @ B[g].float().t()
+        got = out[r0:r0 + n].float()
+        tol = 0.02 * ref.abs().max().item() + 1e-3 if n else 0
+        assert n == 0 or (got - ref).abs().max().item() <= tol, f"group {g}"
+        r0 += n
+    assert torch.all(out[M:] == 7.0), "rows beyond the last group must stay untouched"
+
+
+def test_grouped_gemm_swiglu():
+    from rbruck_alltoallv_b200.ops.moe import grouped_gemm, pack_gate_up
+    torch.manual_seed(1)
+    rows, I, K = [200, 56], 256, 128
+    M = sum(rows)
+    A = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn(2, I, K, device="cuda") * 0.1).to(torch.bfloat16)
+    up = (torch.randn(2, I, K, device="cuda") * 0.1).to(torch.bfloat16)
+    gs, gr = _groups(rows, "cuda")
+    out = grouped_gemm(A, pack_gate_up(gate, up), gs, gr, swiglu=True)
+    torch.cuda.synchronize()
+    r0 = 0
+    for g, n in enumerate(rows):
+        a = A[r0:r0 + n].float()
+        ref = torch.nn.functional.silu(a @ gate[g].float().t()) * (a @ up[g].float().t())
+        assert (out[r0:r0 + n].float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3
+        r0 += n
+
+
+def test_router_top2():
+    import ctypes as C
+    from rbruck_alltoallv_b200 import _native
+    lib = _native.cuda_lib()
+    T, E = 1000, 64
+    torch.manual_seed(2)
+    logits = torch.randn(T, E, device="cuda")
+    idx = torch.empty(T, 2, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, 2, device="cuda")
+    hist = torch.empty(E, dtype=torch.int32, device="cuda")
+    p = lambda t: C.c_void_p(t.data_ptr())
+    assert lib.rbv_moe_route(p(logits), T, E, p(idx), p(w), p(hist), None) == 0
+    torch.cuda.synchronize()
+    pr = torch.softmax(logits, -1)
+    tp, ti = torch.topk(pr, 2, dim=-1)
+    assert torch.equal(ti.int(), idx)
+    assert torch.allclose(w, tp / tp.sum(-1, keepdim=True), atol=1e-5)
+    assert torch.equal(hist.long(), torch.bincount(ti.reshape(-1), minlength=E))
+
+
+def test_moe_layer_single_gpu():
+    from rbruck_alltoallv_b200.models.moe_layer import smoke_moe
+    smoke_moe()
