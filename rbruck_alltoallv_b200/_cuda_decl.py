@@ -51,6 +51,10 @@ def declare_cuda(lib):
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
     lib.rbv_ctx_set_cooperative.argtypes = [C.c_void_p, C.c_int]
     declare_moe(lib)
+    lib.rbv_alltoallv_noalloc.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.rbv_noalloc_status.argtypes = [C.c_void_p]
+    lib.rbv_noalloc_last_error.restype = C.c_char_p
 
 
 def declare_moe(lib):
