@@ -10,6 +10,12 @@ class Status(C.Structure):
                 ("trace", C.c_ulonglong * 8)]
 
 
+class Box(C.Structure):
+    _fields_ = [("n0", C.c_int), ("n1", C.c_int), ("n2", C.c_int), ("src_off", C.c_longlong), ("s0", C.c_longlong),
+                ("s1", C.c_longlong), ("dst_off", C.c_longlong), ("t0", C.c_longlong), ("t1", C.c_longlong),
+                ("t2", C.c_longlong)]
+
+
 STATUS_NAMES = {0: "ok", 1: "timeout", 2: "bad_argument", 3: "staging_capacity", 4: "truncate", 5: "aborted"}
 SITE_NAMES = {0: "-", 1: "metadata", 2: "staging_cell", 3: "final_arrival"}
 
@@ -55,6 +61,8 @@ def declare_cuda(lib):
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_noalloc_status.argtypes = [C.c_void_p]
     lib.rbv_noalloc_last_error.restype = C.c_char_p
+    lib.rbv_transpose_exchange.argtypes = [C.c_void_p, C.c_void_p, C.c_ulonglong, C.c_int, C.c_void_p, C.c_void_p,
+                                           C.c_int, C.c_void_p]
 
 
 def declare_moe(lib):
