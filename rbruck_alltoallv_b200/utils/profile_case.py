@@ -1,0 +1,89 @@
+"""Small, self-terminating workloads of one kernel each, sized for profiler captures (inputs larger than the
+126 MB L2, at most a few GB on the device, a handful of launches).
+
+    python -m rbruck_alltoallv_b200.utils.profile_case a2av        # spread-out alltoallv, 8 ranks on one GPU, 4 MB blocks
+    python -m rbruck_alltoallv_b200.utils.profile_case a2av_bruck  # radix-2 two-phase Bruck, same sizes
+    python -m rbruck_alltoallv_b200.utils.profile_case a2av_small  # Zipf blocks <= 64 KB (latency regime)
+    python -m rbruck_alltoallv_b200.utils.profile_case gemm1       # grouped SwiGLU GEMM, 2 experts x 2048 rows, 4096 -> 2 x 14336
+    python -m rbruck_alltoallv_b200.utils.profile_case gemm2       # grouped down GEMM, 14336 -> 4096
+    python -m rbruck_alltoallv_b200.utils.profile_case transpose   # fused pencil transpose, 384^3 complex64
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+import torch
+
+
+def _a2av(algo, small=False, **kw):
+    from ..parallel.comm import Communicator
+    from . import distributions as D
+    P = 8
+    comm = Communicator(nranks=P, heap_bytes=1 << 30, arena_bytes=24 << 20)
+    counts = D.zipf(P, 16384, seed=1) if small else D.normal(P, 1 << 20, 0.25, seed=1)   # fp32 elements
+    sc, rc = counts.astype(np.int32), counts.T.astype(np.int32).copy()
+    send = [torch.zeros(max(int(sc[i].sum()), 1), dtype=torch.float32, device="cuda") for i in range(P)]
+    recv = [comm.symm_empty(max(int(rc[i].sum()), 1), torch.float32) for i in range(P)]
+    call = comm.prepare(send, recv, sc, None, rc, None, algo=algo, **kw)
+    for _ in range(4):
+        call.launch()
+    comm.check()
+    comm.close()
+
+
+def _gemm(which):
+    from ..ops.moe import grouped_gemm
+    G, rows, H, I = 2, 2048, 4096, 14336
+    gs = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    gr = torch.tensor([rows, rows], dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    if which == 1:
+        A = torch.randn(G * rows, H, device="cuda").to(torch.bfloat16)
+        B = (torch.randn(G, 2 * I, H, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.empty(G * rows, I, dtype=torch.bfloat16, device="cuda")
+    else:
+        A = torch.randn(G * rows, I, device="cuda").to(torch.bfloat16)
+        B = (torch.randn(G, H, I, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.empty(G * rows, H, dtype=torch.bfloat16, device="cuda")
+    for _ in range(4):
+        grouped_gemm(A, B, gs, gr, out=out, swiglu=(which == 1), error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+
+
+def _transpose():
+    from ..ops.fft import PencilTranspose
+    from ..parallel.comm import Communicator
+    n = 384
+    comm = Communicator(nranks=1, heap_bytes=(n ** 3 * 8) * 2 + (64 << 20), arena_bytes=1 << 20)
+    tp = PencilTranspose(comm, n, 1, 1, seed=1)
+    src = torch.view_as_complex(torch.randn(n, n, n, 2, device="cuda"))
+    for _ in range(4):
+        tp.x_to_y(src)
+    tp.check()
+    comm.close()
+
+
+def main() -> int:
+    case = sys.argv[1] if len(sys.argv) > 1 else "a2av"
+    if case == "a2av":
+        _a2av("spreadout")
+    elif case == "a2av_bruck":
+        _a2av("rbruck", r=2)
+    elif case == "a2av_small":
+        _a2av("rbruck", small=True, r=2)
+    elif case == "gemm1":
+        _gemm(1)
+    elif case == "gemm2":
+        _gemm(2)
+    elif case == "transpose":
+        _transpose()
+    else:
+        raise SystemExit("unknown case")
+    print("case", case, "done")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
