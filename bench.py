@@ -149,33 +149,43 @@ def run_ours(args):
     rd = prob.rdispls[mine]
 
     # persistent calls (resolved once, one kernel launch per step), one per candidate radix
-    calls = {r: comm.prepare(send, recv, sc, sd, rc, rd, algo="rbruck", r=r, type_size=TYPE_SIZE) for r in RADICES}
+    # Two protocols per radix: rendezvous (blocks go straight to the final address) and eager (blocks travel as
+    # self-validating units through library cells; lower latency for small blocks).
+    emax = comm.max_block_bytes(prob.counts, TYPE_SIZE)
+    calls = {}
+    for r in RADICES:
+        calls[(r, "rendezvous")] = comm.prepare(send, recv, sc, sd, rc, rd, algo="rbruck", r=r, type_size=TYPE_SIZE)
+        calls[(r, "eager")] = comm.prepare(send, recv, sc, sd, rc, rd, algo="rbruck", r=r, type_size=TYPE_SIZE,
+                                           eager_max_bytes=emax)
 
-    def step(radix):
-        calls[radix].launch()
+    def step(key):
+        calls[key].launch()
 
     flush = L2Flusher(dev)
     align = RankAligner(comm)
 
     # correctness once, before timing
-    dev_recv.fill_(0xA5)
-    step(2)
-    comm.check()
-    got = dev_recv.cpu().numpy()
-    for i, r in enumerate(mine):
-        if not np.array_equal(got[r_off[i]:r_off[i] + r_sizes[i]], want[r]):
-            raise SystemExit(f"rank {r}: receive buffer differs from the direct-copy expectation")
+    for key in ((2, "rendezvous"), (2, "eager"), (8, "eager")):
+        dev_recv.fill_(0xA5)
+        step(key)
+        comm.check()
+        got = dev_recv.cpu().numpy()
+        for i, r in enumerate(mine):
+            if not np.array_equal(got[r_off[i]:r_off[i] + r_sizes[i]], want[r]):
+                raise SystemExit(f"rank {r}: receive buffer differs from the direct-copy expectation ({key})")
 
     # radix choice by measurement (part of warm-up)
     per_radix = {}
-    for r in RADICES:
-        t = time_steps(lambda: step(r), steps=20, warmup=3, flush=flush, align=align)
-        per_radix[r] = float(np.mean(t)) * 1e3
-    best = min(per_radix, key=per_radix.get)
+    for key in calls:
+        t = time_steps(lambda: step(key), steps=20, warmup=3, flush=flush, align=align)
+        per_radix[key] = float(np.mean(t)) * 1e3
+    keys = list(calls)
+    best_i = min(range(len(keys)), key=lambda i: per_radix[keys[i]])
     if world > 1:
-        b = torch.tensor([best], device=dev)
+        b = torch.tensor([best_i], device=dev)
         dist.broadcast(b, 0)
-        best = int(b.item())
+        best_i = int(b.item())
+    best = keys[best_i]
 
     warm = max(args.warmup, 3)
     with ClockSampler(comm.device) as clocks:
@@ -213,7 +223,8 @@ def run_ours(args):
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
                 "data": "synthetic",
                 "config": config_dict(n_gpus, {
-                    "radix": best, "us_per_radix": {str(k): round(v, 2) for k, v in per_radix.items()},
+                    "radix": best[0], "protocol": best[1],
+                    "us_per_radix": {f"{k[0]}/{k[1]}": round(v, 2) for k, v in per_radix.items()},
                     "total_bytes": total_bytes, "us_median": float(np.median(t)) * 1e3,
                     "l2": "flushed: a 256 MiB buffer is written before every timed step (outside the timed span); "
                           "a zero-byte alltoallv then lines the ranks up",

@@ -27,6 +27,7 @@ CUDA_SOURCES = [
     "plan/capi_host.cpp",
     "comm/comm.cu",
     "kernels/a2av_kernel.cu",
+    "kernels/a2av_eager.cu",
     "kernels/moe_kernels.cu",
     "kernels/grouped_gemm_sm100.cu",
     "kernels/fft_transpose.cu",

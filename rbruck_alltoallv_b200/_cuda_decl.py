@@ -55,6 +55,7 @@ def declare_cuda(lib):
     lib.rbv_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_set_eager.argtypes = [C.c_void_p, C.c_ulonglong]
     lib.rbv_ctx_set_cooperative.argtypes = [C.c_void_p, C.c_int]
     declare_moe(lib)
     lib.rbv_alltoallv_noalloc.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,

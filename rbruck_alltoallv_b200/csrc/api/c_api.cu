@@ -100,6 +100,7 @@ int rbv_alltoallv(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
     ca.bytes_hint = bytes_hint;
     CallOptions opt;
     opt.grid = grid; opt.chunk_bytes = chunk_bytes; opt.flags = flags;
+    opt.eager_max_bytes = ctx->eager;
     int rc = ctx->c->alltoallv(s, type_size, ca, opt, static_cast<cudaStream_t>(cuda_stream));
     if (rc) g_err = ctx->c->last_error();
     return rc;
@@ -123,6 +124,7 @@ void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
     ca.bytes_hint = bytes_hint;
     CallOptions opt;
     opt.grid = grid; opt.chunk_bytes = chunk_bytes; opt.flags = flags;
+    opt.eager_max_bytes = ctx->eager;
     auto pc = std::make_unique<Prepared>();
     int rc = ctx->c->prepare(s, type_size, ca, opt, nullptr, true, pc.get());
     if (rc) { g_err = ctx->c->last_error(); return nullptr; }
@@ -143,6 +145,7 @@ void rbv_prepared_free(rbv_ctx_t ctx, void* prepared) {
   ctx->c->release(*pc);
   delete pc;
 }
+void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes) { ctx->eager = max_block_bytes; }
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on) { ctx->c->set_cooperative(on != 0); }
 

@@ -19,6 +19,7 @@ struct rbv_ctx_s {
   cudaStream_t stream = nullptr;
   int grid = 0;
   size_t chunk = 0;
+  unsigned long long eager = 0;   // cell payload bytes of the eager protocol for the following calls (0: off)
   std::vector<rbv_comm_s> comms;
   // calls of the local ranks collected until all L have arrived
   int pend = 0;

@@ -67,6 +67,7 @@ Context::~Context() {
   for (auto& kv : plans_) {
     if (kv.second->d_ops) cudaFree(kv.second->d_ops);
     if (kv.second->d_done) cudaFree(kv.second->d_done);
+    if (kv.second->d_eops) cudaFree(kv.second->d_eops);
   }
   for (int q = 0; q < nproc_; q++)
     if (opened_[q] && peer_[q]) cudaIpcCloseMemHandle(peer_[q]);
@@ -166,6 +167,31 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
         RBV_CUDA_THROW(cudaMalloc(&dp->d_done, ops.size() * sizeof(unsigned)));
         RBV_CUDA_THROW(cudaMemset(dp->d_done, 0, ops.size() * sizeof(unsigned)));
       }
+      // eager variant of the op list
+      std::vector<Op> eops;
+      eops.reserve(ops.size() + (size_t)L_ * P_);
+      for (Op o : ops) {
+        if (!(o.flags & 1u)) {
+          if (o.src_cell >= 0) o.src_cell += P_;
+          o.dst_cell = o.dst_cell >= 0 ? o.dst_cell + P_ : (int)o.origin;
+        }
+        eops.push_back(o);
+      }
+      for (int lr = 0; lr < L_; lr++) {
+        const int d = proc_ * L_ + lr;
+        for (int s = 0; s < P_; s++) {
+          if (s == d) continue;
+          Op u{};
+          u.src = u.dst = u.dest = (uint16_t)d; u.origin = (uint16_t)s;
+          u.src_cell = s; u.dst_cell = -1; u.key = 0xffffffffu; u.flags = 2u;
+          eops.push_back(u);
+        }
+      }
+      dp->n_eops = (int)eops.size();
+      if (dp->n_eops) {
+        RBV_CUDA_THROW(cudaMalloc(&dp->d_eops, eops.size() * sizeof(Op)));
+        RBV_CUDA_THROW(cudaMemcpy(dp->d_eops, eops.data(), eops.size() * sizeof(Op), cudaMemcpyHostToDevice));
+      }
     }
   }
   const DevPlan* out = dp.get();
@@ -182,7 +208,8 @@ int Context::alltoallv(const AlgoSpec& spec, int ts, const CallArgs& ca, const C
 }
 
 int Context::launch(const Prepared& pc, cudaStream_t stream) {
-  cudaError_t e = a2av_launch(pc.ka, pc.grid, cooperative_, stream);
+  cudaError_t e = pc.eager ? a2av_eager_launch(pc.ka, pc.grid, cooperative_, stream)
+                           : a2av_launch(pc.ka, pc.grid, cooperative_, stream);
   if (e != cudaSuccess) {
     last_error_ = std::string("kernel launch failed: ") + cudaGetErrorString(e);
     return RBV_ERR_BAD_ARG;
@@ -203,6 +230,15 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   if (dp->plan.err) { last_error_ = dp->plan.errmsg; return dp->plan.err; }
   if (ts < 1) { last_error_ = "type size must be positive"; return RBV_ERR_BAD_ARG; }
   const bool inplace = (opt.flags & CALL_INPLACE) != 0;
+  const bool eager = opt.eager_max_bytes > 0;
+  const unsigned long long emax = (opt.eager_max_bytes + 7) & ~7ull;
+  if (eager) {
+    if (inplace) { last_error_ = "the eager protocol does not take in-place calls"; return RBV_ERR_BAD_ARG; }
+    if ((unsigned long long)(P_ + dp->plan.ncells) * (16 + 2 * emax) > lay_.arena_bytes) {
+      last_error_ = "staging arena too small for the eager cells of this plan";
+      return RBV_ERR_CAPACITY;
+    }
+  }
   if (inplace && ca.counts_on_device) { last_error_ = "in-place calls need host-side counts"; return RBV_ERR_BAD_ARG; }
   if (!ca.sendcounts || !ca.sdispls || !ca.rdispls || !ca.recvbufs || (!inplace && !ca.sendbufs)) {
     last_error_ = "null argument"; return RBV_ERR_BAD_ARG;
@@ -227,7 +263,7 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   }
   ka.host_status = host_status_dev_;
   for (int lr = 0; lr < L_; lr++) {
-    if (!in_heap(ca.recvbufs[lr], 1)) {
+    if (!eager && !in_heap(ca.recvbufs[lr], 1)) {
       last_error_ = "recvbuf must be allocated from the symmetric heap";
       return RBV_ERR_BAD_ARG;
     }
@@ -245,6 +281,9 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
         last_error_ = "negative count or displacement"; return RBV_ERR_BAD_ARG;
       }
       send_bytes += (long long)ca.sendcounts[i] * ts;
+      if (eager && (unsigned long long)ca.sendcounts[i] * ts > emax) {
+        last_error_ = "a block is larger than the eager cell size"; return RBV_ERR_CAPACITY;
+      }
     }
     if (inplace) {
       size_t total = 0;
@@ -360,6 +399,29 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   grid = std::max(1, std::min(grid, max_ctas_));
   ka.chunk_bytes = chunk;
   out->grid = grid;
+  out->eager = eager;
+  if (eager) {
+    ka.ops = dp->d_eops;
+    ka.nops = dp->n_eops;
+    ka.eager_payload = emax;
+    // work items: one warp per chunk of payload; relay and unpack items are sized by the cell
+    unsigned long long ech = opt.chunk_bytes ? align_up(opt.chunk_bytes, 16) : 2048;
+    ka.chunk_bytes = ech;
+    const double per_cell = std::ceil((double)emax / (double)ech);
+    double items = (double)dp->n_eops * std::max(1.0, per_cell);
+    if (send_bytes >= 0) {
+      // first hops are sized exactly; the rest (relays, unpacks) by the largest of this process's blocks
+      long long mx = 0;
+      if (!ca.counts_on_device)
+        for (size_t i = 0; i < n; i++) {
+          mx = std::max<long long>(mx, (long long)ca.sendcounts[i] * ts);
+          if (ca.recvcounts) mx = std::max<long long>(mx, (long long)ca.recvcounts[i] * ts);
+        }
+      if (mx > 0) items = (double)dp->n_eops * std::max(1.0, std::ceil((double)mx / (double)ech));
+    }
+    int g = opt.grid > 0 ? opt.grid : (int)std::min<double>(max_ctas_, std::max(1.0, std::ceil(items / warps_per_cta)));
+    out->grid = std::max(1, std::min(g, max_ctas_));
+  }
   return 0;
 }
 

@@ -21,12 +21,17 @@ struct DevPlan {
   Op* d_ops = nullptr;     // ops of this process's ranks
   unsigned* d_done = nullptr;
   int nops = 0;
+  // eager protocol: the same ops retargeted at arrival / staging cells, followed by one unpack op per
+  // (local rank, source); cell indices: 0..P-1 arrival cell of source s, P + c staging cell c
+  Op* d_eops = nullptr;
+  int n_eops = 0;
 };
 
 struct CallOptions {
   int grid = 0;                       // CTAs; 0 = choose
   unsigned long long chunk_bytes = 0; // 0 = choose
   unsigned flags = 0;                 // CALL_INPLACE
+  unsigned long long eager_max_bytes = 0;  // > 0: eager protocol with cells of this payload size (same on all ranks)
 };
 
 // Arguments of one collective call for all L local ranks.  Count arrays are [L][P].
@@ -46,6 +51,7 @@ struct CallArgs {
 struct Prepared {
   KernelArgs ka;
   int grid = 1;
+  bool eager = false;
   void* owned_meta = nullptr;   // device copy of host count arrays that did not fit the kernel parameters
 };
 
@@ -136,5 +142,7 @@ class Context {
 size_t a2av_smem_bytes(int P);
 cudaError_t a2av_configure(int P, int* max_ctas_per_sm);
 cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream);
+// implemented in kernels/a2av_eager.cu
+cudaError_t a2av_eager_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream);
 
 }  // namespace rbv

@@ -118,6 +118,7 @@ struct KernelArgs {
   const Op* ops;           // device copy of the process's op list
   unsigned* op_done;       // [nops] completion counters of multi-chunk ops (zero between calls)
   unsigned long long chunk_bytes;
+  unsigned long long eager_payload;  // eager protocol: payload bytes a cell can hold (0: rendezvous protocol)
   unsigned long long timeout_ns;
   HeapLayout lay;
   char* heap[kMaxProcs];   // heap base of every process as mapped in this process

@@ -86,6 +86,9 @@ void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
                   int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes);
 int rbv_launch(rbv_ctx_t ctx, void* prepared, void* cuda_stream);
 void rbv_prepared_free(rbv_ctx_t ctx, void* prepared);
+/* Protocol of the following calls: 0 = rendezvous (any size); > 0 = eager, for blocks of at most this many bytes
+ * (every rank must pass the same value; needs (P + cells) * (16 + 2 * bytes) of staging arena per rank). */
+void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes);
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on);       /* report phase time stamps after every call */
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on); /* cooperative (default) or plain kernel launches */
 

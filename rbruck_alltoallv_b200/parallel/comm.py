@@ -210,7 +210,7 @@ class Communicator:
                   sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, algo: str = "spreadout",
                   n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0, type_size: Optional[int] = None,
                   inplace: bool = False, grid: int = 0, chunk_bytes: int = 0, bytes_hint: int = -1,
-                  stream: Optional[torch.cuda.Stream] = None) -> None:
+                  eager_max_bytes: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
         """Non-uniform all-to-all of the L local ranks (asynchronous on the current stream).
 
         ``send`` / ``recv`` are one tensor per local rank (a bare tensor when L == 1); ``recv`` must come
@@ -219,27 +219,43 @@ class Communicator:
         router kernel).  ``sdispls`` / ``rdispls`` default to the packed layout when counts are on the host.
         ``recvcounts`` is optional: when given, a block larger than its slot is refused (status
         ``truncate``) instead of overrunning the buffer.
+
+        ``eager_max_bytes`` > 0 selects the low-latency eager protocol: blocks (at most that many bytes, the same
+        value on every rank) travel as self-validating units into library-owned cells and the receiver copies
+        them out, so there is no metadata phase and ``recv`` may be any device memory.  :meth:`max_block_bytes`
+        agrees on the value across ranks.
         """
         ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         st = stream or torch.cuda.current_stream(self.device)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
+        self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
         rcode = self._lib.rbv_alltoallv(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
                                         1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
                                         int(chunk_bytes), C.c_void_p(st.cuda_stream))
         if rcode:
             raise CommError(f"alltoallv({algo}) failed with code {rcode}: {self._lib.rbv_last_error().decode()}")
 
+    def max_block_bytes(self, sendcounts, type_size: int) -> int:
+        """Largest block of the whole exchange in bytes (host counts; collective over the processes)."""
+        m = int(np.max(np.asarray(sendcounts))) * int(type_size) if np.size(sendcounts) else 0
+        if self._side is not None:
+            t = torch.tensor([m], dtype=torch.int64)
+            self._dist.all_reduce(t, op=self._dist.ReduceOp.MAX, group=self._side)
+            m = int(t.item())
+        return m
+
     def prepare(self, send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None, *,
                 algo: str = "spreadout", n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0,
                 type_size: Optional[int] = None, inplace: bool = False, grid: int = 0, chunk_bytes: int = 0,
-                bytes_hint: int = -1) -> "PreparedCall":
+                bytes_hint: int = -1, eager_max_bytes: int = 0) -> "PreparedCall":
         """Persistent form of :meth:`alltoallv` (compare ``MPI_Alltoallv_init``): everything is resolved once;
         ``.launch()`` then costs one kernel launch.  Buffers and counts are fixed (device-resident counts are
         re-read by every launch, so a router may still change their values)."""
         ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
+        self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
         h = self._lib.rbv_prepare(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
                                   1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
                                   int(chunk_bytes))

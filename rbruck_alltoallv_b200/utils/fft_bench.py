@@ -1,7 +1,7 @@
 """Check and time the fused pencil transposes (optionally next to the NCCL baseline).
 
-    python -m rbruck_alltoallv_b200.utils.fft_bench --n 256 --check
-    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 -m rbruck_alltoallv_b200.utils.fft_bench --n 1024 --pr 2 --pc 4
+    python -m rbruck_alltoallv_b200.utils.fft_bench --size 256 --check
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 -m rbruck_alltoallv_b200.utils.fft_bench --size 1024 --pr 2 --pc 4
 """
 from __future__ import annotations
 
@@ -21,7 +21,7 @@ from .timing import L2Flusher, time_steps
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--n", type=int, default=256)
+    ap.add_argument("--size", dest="n", type=int, default=256, help="grid points per dimension")
     ap.add_argument("--pr", type=int, default=0)
     ap.add_argument("--pc", type=int, default=0)
     ap.add_argument("--steps", type=int, default=10)

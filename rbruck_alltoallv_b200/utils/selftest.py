@@ -49,9 +49,11 @@ def check_all(comm: Communicator, ts: int = 4, seed: int = 3) -> int:
             t.fill_(oracle.CANARY)
         torch.cuda.synchronize()
         comm.host_barrier()
-        for rep in range(3):   # back-to-back calls exercise both parities
+        emax = comm.max_block_bytes(prob.counts[mine], ts)
+        inplace_algo = algo == "ttpl_bt_s2"
+        for rep in range(4):   # back-to-back calls exercise both parities; even: rendezvous, odd: eager protocol
             comm.alltoallv(send, recv, prob.counts[mine], prob.sdispls[mine], prob.recvcounts[mine], prob.rdispls[mine],
-                           algo=algo, type_size=ts, **kw)
+                           algo=algo, type_size=ts, eager_max_bytes=(emax if rep % 2 and not inplace_algo else 0), **kw)
         st = comm.status()
         bad = oracle.first_mismatch([t.cpu().numpy() for t in recv], [want[r] for r in mine])
         if st["code"] or bad is not None:
@@ -77,8 +79,13 @@ def bench(comm: Communicator, sizes=(16, 1024, 65536, 1 << 20, 4 << 20)) -> list
         send = [torch.zeros(max(int(sc[i].sum()), 1), dtype=torch.bfloat16, device=dev) for i in range(L)]
         recv = [comm.symm_empty(max(int(rc[i].sum()), 1), torch.bfloat16) for i in range(L)]
         row = {"mean_block_bytes": nbytes, "total_bytes": int(counts.sum()) * 2, "us": {}}
-        for name, kw in (("spreadout", dict(algo="spreadout")), ("rbruck_r2", dict(algo="rbruck", r=2)),
-                         ("tuna2_r2", dict(algo="tuna2", r=2)), ("pairwise", dict(algo="pairwise"))):
+        emax = comm.max_block_bytes(sc, 2)
+        cases = [("spreadout", dict(algo="spreadout")), ("rbruck_r2", dict(algo="rbruck", r=2)),
+                 ("tuna2_r2", dict(algo="tuna2", r=2)), ("pairwise", dict(algo="pairwise"))]
+        if emax <= (256 << 10):
+            cases += [("spreadout_eager", dict(algo="spreadout", eager_max_bytes=emax)),
+                      ("rbruck_r2_eager", dict(algo="rbruck", r=2, eager_max_bytes=emax))]
+        for name, kw in cases:
             try:
                 call = comm.prepare(send, recv, sc, None, rc, None, **kw)
             except Exception as e:  # noqa: BLE001

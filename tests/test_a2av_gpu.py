@@ -172,3 +172,51 @@ def test_plan_errors_surface():
     t = comm.symm_empty(64, torch.uint8)
     with pytest.raises(CommError):
         comm.alltoallv([t] * 6, [t] * 6, np.zeros((6, 6)), None, np.zeros((6, 6)), None, algo="xor")
+
+
+EAGER = [("spreadout", {}), ("linear", {}), ("pairwise", {}), ("rbruck", dict(r=2)), ("rbruck", dict(r=3)),
+         ("rbruck_om", dict(r=2)), ("tuna2", dict(r=2, b=0)), ("ttpl_bt_s1", dict(n=4, r=2)), ("ttpl", dict(n=2, r=2)),
+         ("ttpl_bt", dict(n=4, r=2, b=1)), ("twolayer_linear_s2", dict(n=4, b=2, b2=3))]
+
+
+@pytest.mark.parametrize("algo,kw", EAGER, ids=[f"{a}-{'-'.join(f'{k}{v}' for k, v in kw.items())}" for a, kw in EAGER])
+@pytest.mark.parametrize("ts", [1, 4, 8])
+def test_eager_protocol(algo, kw, ts):
+    counts = dist.uniform(8, 700, seed=ts)
+    counts[counts < 60] = 0
+    run_case(8, algo, ts, counts, packed=False, seed=ts + 3, eager_max_bytes=700 * ts, **kw)
+
+
+def test_eager_plain_receive_buffers_and_repeated_calls():
+    P, ts = 8, 4
+    comm = get_comm(P)
+    for rep in range(5):
+        counts = dist.zipf(P, 2048, seed=rep)
+        prob = oracle.make_problem(counts, ts, rep, packed=True)
+        send_h = oracle.fill_send(prob, rep)
+        want = oracle.expected_recv(prob, send_h)
+        send = [torch.from_numpy(b).cuda() for b in send_h]
+        recv = [torch.full((len(w),), oracle.CANARY, dtype=torch.uint8, device="cuda") for w in want]   # not symmetric
+        comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="rbruck", r=2,
+                       type_size=ts, eager_max_bytes=comm.max_block_bytes(prob.counts, ts))
+        comm.check()
+        assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
+
+
+def test_eager_rejects_oversize_block_on_the_host():
+    from rbruck_alltoallv_b200.parallel.comm import CommError
+    comm = get_comm(4)
+    counts = dist.constant(4, 1000)
+    prob = oracle.make_problem(counts, 4, 0)
+    send = [torch.zeros(int(b), dtype=torch.uint8, device="cuda") for b in prob.send_bytes]
+    recv = [comm.symm_empty(int(b), torch.uint8) for b in prob.recv_bytes]
+    with pytest.raises(CommError):
+        comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="spreadout",
+                       type_size=4, eager_max_bytes=1024)
+
+
+def test_protocols_can_alternate_on_one_communicator():
+    counts = dist.uniform(8, 300, seed=77)
+    for i in range(6):
+        run_case(8, "rbruck", 4, counts, seed=80 + i, r=2, eager_max_bytes=(1200 if i % 2 == 0 else 0))
+        run_case(8, "spreadout", 4, counts, seed=90 + i, eager_max_bytes=(0 if i % 3 == 0 else 1200))
