@@ -55,7 +55,8 @@ struct StatusBlock {
 // Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.
 struct CtrlBlock {
   unsigned long long meta_arrivals[2];
-  unsigned long long recv_arrivals[kMaxRanks];
+  unsigned long long recv_arrivals[kMaxRanks];   // += 1 per chunk landed in a local rank's recvbuf
+  unsigned long long recv_target[kMaxRanks];     // running total of chunks expected so far (kept by the owner)
   unsigned int abort_flag;       // set locally on error, and by peers that want everyone to stop
   unsigned int pad0;
   unsigned int exit_count;       // CTAs that finished the current call (the last one publishes the status)
@@ -86,12 +87,16 @@ struct HeapLayout {
 //   int32  caps  [P][P]   row d written by rank d: recvcounts of d per source, -1 = unchecked
 //   int64  rdispl[P][P]   row d written by rank d, in elements
 //   uint64 recvoff[P]     offset of rank d's recvbuf inside its process's heap
-__host__ __device__ inline unsigned long long meta_counts_off(int P) { (void)P; return 0; }
-__host__ __device__ inline unsigned long long meta_caps_off(int P) { return 4ull * P * P; }
-__host__ __device__ inline unsigned long long meta_rdispl_off(int P) { return 8ull * P * P; }
-__host__ __device__ inline unsigned long long meta_recvoff_off(int P) { return 16ull * P * P; }
+// Stored as self-validating 16-byte units { word0, flag, word1, flag } with flag = call number + 1, so that a
+// reader needs no separate arrival signal (one NVLink trip instead of store + acknowledged release):
+//   CT[s][d]  { count, chunk bytes of sender s }        row s written by rank s
+//   RT[d][s]  { cap, 0 } { rdispl lo, rdispl hi }       row d written by rank d (two units per entry)
+//   RO[d]     { recvoff lo, recvoff hi }                written by rank d
+__host__ __device__ inline unsigned long long meta_ct_off(int P) { (void)P; return 0; }
+__host__ __device__ inline unsigned long long meta_rt_off(int P) { return 16ull * P * P; }
+__host__ __device__ inline unsigned long long meta_ro_off(int P) { return 48ull * P * P; }
 __host__ __device__ inline unsigned long long meta_table_bytes(int P) {
-  return (16ull * P * P + 8ull * P + 255) & ~255ull;
+  return (48ull * P * P + 16ull * P + 255) & ~255ull;
 }
 
 enum CallFlags : unsigned {

@@ -279,10 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
     if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
       my->exit_count = 0;
       my->call_seq = seq + 1u;
-      // keep the rendezvous protocol's arrival counters in step with the call number, so that calls of the
-      // two protocols can be mixed on one communicator (peers may already be adding to them for the next call)
-      atomicAdd(&my->meta_arrivals[parity], (unsigned long long)P);
-      for (int lr = 0; lr < L; lr++) atomicAdd(&my->recv_arrivals[lr], (unsigned long long)P);
+      // (the rendezvous protocol keeps no per-call counter targets, so the two protocols can be mixed freely)
       my->status.trace[4] = dev::globaltimer();
       if (my->status.code == 0 && dev::ld_relaxed_sys(&my->abort_flag)) my->status.code = RBV_ERR_ABORTED;
       __threadfence();

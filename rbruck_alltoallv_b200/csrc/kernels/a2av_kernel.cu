@@ -39,6 +39,7 @@ struct Smem {
   int* caps;
   long long* rdispl;
   unsigned long long* recvoff;
+  unsigned* schunk;     // chunk size used by each sending rank
   unsigned* prefix;
 };
 
@@ -83,8 +84,19 @@ __device__ __forceinline__ const long long* in_rdispls(const KernelArgs& a) {
   return (a.flags & CALL_META_INLINE) ? a.inl.rdispls : a.rdispls;
 }
 
-// Metadata rows of local rank lr go to process q: one warp per (lr, q) pair.
-__device__ void publish_metadata(const KernelArgs& a, int parity) {
+__device__ __forceinline__ void st_unit(uint4* p, unsigned w0, unsigned w1, unsigned flag) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(w0), "r"(flag), "r"(w1), "r"(flag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_unit(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// Metadata rows of local rank lr go to process q: one warp per (lr, q) pair.  Every unit carries the call
+// number, so nothing else has to be signalled.
+__device__ void publish_metadata(const KernelArgs& a, int parity, unsigned flag) {
   const int P = a.P;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int* rc = in_recvcounts(a);
@@ -93,20 +105,18 @@ __device__ void publish_metadata(const KernelArgs& a, int parity) {
     if (lr == a.absent_rank) continue;  // host-injected fault: the rank "never joins"
     const int me = a.proc * a.L + lr;
     char* mt = meta_of(a, q, parity);
-    int* counts = reinterpret_cast<int*>(mt + meta_counts_off(P)) + (size_t)me * P;
-    int* caps = reinterpret_cast<int*>(mt + meta_caps_off(P)) + (size_t)me * P;
-    long long* rd = reinterpret_cast<long long*>(mt + meta_rdispl_off(P)) + (size_t)me * P;
-    unsigned long long* ro = reinterpret_cast<unsigned long long*>(mt + meta_recvoff_off(P)) + me;
+    uint4* ct = reinterpret_cast<uint4*>(mt + meta_ct_off(P)) + (size_t)me * P;
+    uint4* rt = reinterpret_cast<uint4*>(mt + meta_rt_off(P)) + (size_t)me * P * 2;
+    uint4* ro = reinterpret_cast<uint4*>(mt + meta_ro_off(P)) + me;
     const int* sc = in_sendcounts(a) + (size_t)lr * P;
     const long long* rdi = in_rdispls(a) + (size_t)lr * P;
     for (int i = lane; i < P; i += 32) {
-      counts[i] = sc[i];
-      caps[i] = rc ? rc[(size_t)lr * P + i] : -1;
-      rd[i] = rdi[i];
+      const unsigned long long rd = (unsigned long long)rdi[i];
+      st_unit(ct + i, (unsigned)sc[i], (unsigned)a.chunk_bytes, flag);
+      st_unit(rt + 2 * i, rc ? (unsigned)rc[(size_t)lr * P + i] : 0xffffffffu, 0u, flag);
+      st_unit(rt + 2 * i + 1, (unsigned)rd, (unsigned)(rd >> 32), flag);
     }
-    if (lane == 0) *ro = a.recvoff[lr];
-    __syncwarp();
-    if (lane == 0) dev::signal_add(&ctrl_of(a, q)->meta_arrivals[parity], 1ull, q != a.proc);
+    if (lane == 0) st_unit(ro, (unsigned)a.recvoff[lr], (unsigned)(a.recvoff[lr] >> 32), flag);
   }
 }
 
@@ -136,6 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     sm.recvoff = reinterpret_cast<unsigned long long*>(p); p += 8ull * P;
     sm.counts = reinterpret_cast<int*>(p); p += 4ull * P * P;
     sm.caps = reinterpret_cast<int*>(p); p += 4ull * P * P;
+    sm.schunk = reinterpret_cast<unsigned*>(p); p += 4ull * P;
     sm.prefix = reinterpret_cast<unsigned*>(p);
   }
 
@@ -164,36 +175,58 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
 
   // ---- (1) metadata phase ----
   if (blockIdx.x == 0) {
-    publish_metadata(a, parity);
+    publish_metadata(a, parity, seq + 1u);
     if (tid == 0) my->status.trace[1] = dev::globaltimer();
   }
-  if (tid == 0) {
-    const unsigned long long target = ((unsigned long long)(seq >> 1) + 1ull) * (unsigned long long)P;
-    int r = dev::wait_ge(&my->meta_arrivals[parity], target, wc, multi);
-    if (r == dev::WAIT_TIMEOUT)
-      report_error(a, RBV_ERR_TIMEOUT, WAIT_META, (int)my->meta_arrivals[parity], (int)target);
-    s_flag = r;
+  // every CTA polls the table units until they carry this call's number and keeps a copy in shared memory
+  bool alive = true;
+  int mx = 0;
+  {
+    const char* mt = meta_of(a, a.proc, parity);
+    const uint4* ct = reinterpret_cast<const uint4*>(mt + meta_ct_off(P));
+    const uint4* rt = reinterpret_cast<const uint4*>(mt + meta_rt_off(P));
+    const uint4* ro = reinterpret_cast<const uint4*>(mt + meta_ro_off(P));
+    const unsigned flag = seq + 1u;
+    const int nunits = 3 * P * P + P;
+    unsigned long long t_start = 0;
+    bool failed = false;
+    for (int u = tid; u < nunits && !failed; u += blockDim.x) {
+      const uint4* src = u < P * P ? ct + u : (u < 3 * P * P ? rt + (u - P * P) : ro + (u - 3 * P * P));
+      uint4 v = ld_unit(src);
+      unsigned it = 0;
+      while (v.y != flag || v.w != flag) {
+        if ((++it & 63u) == 0) {
+          if (!t_start) t_start = dev::globaltimer();
+          if (dev::ld_relaxed_sys(&my->abort_flag) || dev::globaltimer() - t_start > a.timeout_ns) { failed = true; break; }
+        }
+        v = ld_unit(src);
+      }
+      if (failed) {
+        if (!dev::ld_relaxed_sys(&my->abort_flag)) report_error(a, RBV_ERR_TIMEOUT, WAIT_META, u, nunits);
+        break;
+      }
+      if (u < P * P) {
+        sm.counts[u] = (int)v.x;
+        if (u % P == 0) sm.schunk[u / P] = v.z;
+        mx = max(mx, (int)v.x);
+      } else if (u < 3 * P * P) {
+        const int e = (u - P * P) >> 1;
+        if (((u - P * P) & 1) == 0) sm.caps[e] = (int)v.x;
+        else sm.rdispl[e] = (long long)((unsigned long long)v.x | ((unsigned long long)v.z << 32));
+      } else {
+        sm.recvoff[u - 3 * P * P] = (unsigned long long)v.x | ((unsigned long long)v.z << 32);
+      }
+    }
+    alive = !__syncthreads_or(failed ? 1 : 0);
   }
-  __syncthreads();
-  bool alive = (s_flag == dev::WAIT_OK);
-  __syncthreads();
 
+  // Chunking must be the same on every rank (receivers count chunks): use the largest proposal.
+  unsigned long long chunk_b = a.chunk_bytes;
+  if (alive) {
+    for (int s = 0; s < P; s++) chunk_b = max(chunk_b, (unsigned long long)sm.schunk[s]);
+  }
   size_t stride = 0;
   if (alive) {
-    const char* mt = meta_of(a, a.proc, parity);
-    const int* gc = reinterpret_cast<const int*>(mt + meta_counts_off(P));
-    const int* gk = reinterpret_cast<const int*>(mt + meta_caps_off(P));
-    const long long* gr = reinterpret_cast<const long long*>(mt + meta_rdispl_off(P));
-    const unsigned long long* go = reinterpret_cast<const unsigned long long*>(mt + meta_recvoff_off(P));
-    int mx = 0;
-    for (int i = tid; i < P * P; i += blockDim.x) {
-      int c = __ldcg(gc + i);
-      sm.counts[i] = c;
-      sm.caps[i] = __ldcg(gk + i);
-      sm.rdispl[i] = __ldcg(gr + i);
-      mx = max(mx, c);
-    }
-    for (int i = tid; i < P; i += blockDim.x) sm.recvoff[i] = __ldcg(go + i);
     // global max block -> staging cell stride (the reference's max_send_count allreduce)
     if (a.ncells > 0) {
       mx = __reduce_max_sync(0xffffffffu, mx);
@@ -207,6 +240,17 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
         alive = false;
       }
     }
+    // the owner of a receive buffer adds the chunks it expects in this call to its running target
+    if (blockIdx.x == 0 && tid < L) {
+      const int me = a.proc * L + tid;
+      unsigned long long expect = 0;
+      for (int s = 0; s < P; s++) {
+        const unsigned long long b = (unsigned long long)sm.counts[s * P + me] * (unsigned long long)ts;
+        const unsigned long long n = (b + chunk_b - 1) / chunk_b;
+        expect += n ? n : 1ull;
+      }
+      my->recv_target[tid] += expect;
+    }
     if (blockIdx.x == 0 && tid == 0) my->status.trace[2] = dev::globaltimer();
   }
 
@@ -217,7 +261,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     for (int i = tid; i < tn; i += blockDim.x) {
       const Op o = a.ops[t0 + i];
       size_t b = alive ? op_bytes(o, sm, P, ts) : 0;
-      unsigned nch = (unsigned)((b + a.chunk_bytes - 1) / a.chunk_bytes);
+      unsigned nch = (unsigned)((b + chunk_b - 1) / chunk_b);
       sm.prefix[i + 1] = nch ? nch : 1u;   // empty blocks still signal their arrival
     }
     __syncthreads();
@@ -274,8 +318,8 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
         if (r != dev::WAIT_OK) { ok = false; alive = false; }
       }
       if (ok && bytes) {
-        const size_t off = (size_t)k * a.chunk_bytes;
-        const size_t len = (off + a.chunk_bytes <= bytes) ? (size_t)a.chunk_bytes : bytes - off;
+        const size_t off = (size_t)k * chunk_b;
+        const size_t len = (off + chunk_b <= bytes) ? (size_t)chunk_b : bytes - off;
         const char* src;
         if (o.src_cell < 0) {
           const char* sb = (a.flags & CALL_INPLACE) ? (a.heap[a.proc] + a.sendcopy_off[lsrc]) : a.sendbuf[lsrc];
@@ -291,20 +335,20 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
         dev::group_copy(dst + off, src + off, len, lane, 32);
       }
       __syncwarp();
-      // completion: the warp that finishes the last chunk of the op signals the destination
+      // completion.  Final hops: every chunk reports to the receiver, which knows how many to expect.
+      // Staging cells: the warp that finishes the last chunk of the op raises the cell's flag.
       if (lane == 0) {
-        bool last = true;
-        if (nch > 1) {
-          dev::fence_acq_rel(remote);   // this chunk's stores become visible before the count does
-          unsigned old = atomicAdd(&a.op_done[t0 + oi], 1u);
-          last = (old == nch - 1);
-          if (last) a.op_done[t0 + oi] = 0;
-        }
-        if (last) {
-          if (o.dst_cell < 0)
-            dev::signal_add(&ctrl_of(a, dproc)->recv_arrivals[ldst], 1ull, remote);
-          else if (ok)
-            dev::signal_store(cell_flag_of(a, dproc, parity, ldst, o.dst_cell), seq + 1u, remote);
+        if (o.dst_cell < 0) {
+          dev::signal_add(&ctrl_of(a, dproc)->recv_arrivals[ldst], 1ull, remote);
+        } else {
+          bool last = true;
+          if (nch > 1) {
+            dev::fence_acq_rel(remote);   // this chunk's stores become visible before the count does
+            unsigned old = atomicAdd(&a.op_done[t0 + oi], 1u);
+            last = (old == nch - 1);
+            if (last) a.op_done[t0 + oi] = 0;
+          }
+          if (last && ok) dev::signal_store(cell_flag_of(a, dproc, parity, ldst, o.dst_cell), seq + 1u, remote);
         }
       }
     }
@@ -316,8 +360,8 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   if (blockIdx.x == 0) {
     if (tid == 0) my->status.trace[3] = dev::globaltimer();
     if (tid < L) {
-      const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)P;
-      int r = dev::wait_ge(&my->recv_arrivals[tid], target, wc, multi);
+      const unsigned long long target = my->recv_target[tid];
+      int r = alive ? dev::wait_ge(&my->recv_arrivals[tid], target, wc, multi) : (int)dev::WAIT_ABORTED;
       if (r == dev::WAIT_TIMEOUT)
         report_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, tid, (int)(target - my->recv_arrivals[tid]));
     }
@@ -340,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
 }
 
 size_t a2av_smem_bytes(int P) {
-  return 8ull * P * P + 8ull * P + 4ull * P * P * 2 + 4ull * (kOpTile + 1) + 16;
+  return 8ull * P * P + 8ull * P + 4ull * P * P * 2 + 4ull * P + 4ull * (kOpTile + 1) + 16;
 }
 
 cudaError_t a2av_configure(int P, int* max_ctas_per_sm) {

@@ -27,12 +27,13 @@ constexpr size_t kCtrlOff = 0;
 constexpr size_t kFlagsOff = align_up_c(sizeof(CtrlBlock), 256);
 constexpr size_t kFlagsBytes = sizeof(unsigned) * 2ull * kNR * kMaxCellsPerRank;
 constexpr size_t kMetaOff = kFlagsOff + kFlagsBytes;
-constexpr size_t kMetaBytes = 1536;                  // >= meta_table_bytes(8)
+constexpr size_t kMetaBytes = 3584;                  // >= meta_table_bytes(8)
 constexpr size_t kDoneOff = kMetaOff + 2 * kMetaBytes;
 constexpr size_t kOpsOff = align_up_c(kDoneOff + sizeof(unsigned) * kMaxOpsNA, 256);
 constexpr size_t kClearBytes = kOpsOff;              // everything before the schedule starts at zero per call
 constexpr size_t kStageOff = align_up_c(kOpsOff + sizeof(Op) * kMaxOpsNA, 4096);
 constexpr size_t kTotal = kStageOff + 2ull * kNR * kArena;
+static_assert(kMetaBytes >= 48 * kNR * kNR + 16 * kNR, "metadata tables do not fit");
 static_assert(kTotal <= RBV_NOALLOC_SCRATCH_BYTES, "scratch array too small for the stated limits");
 
 // The one scratch array.  Device code may name it directly; host code must not use this name as an address.
