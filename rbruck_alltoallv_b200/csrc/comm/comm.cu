@@ -382,8 +382,8 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   if (!chunk) {
     if (work < 0) chunk = 32 << 10;
     else {
-      // a chunk is one warp's unit of work: aim at ~4 chunks per warp at full grid, within [8 KB, 64 KB]
-      double c = work / (4.0 * max_ctas_ * warps_per_cta);
+      // a chunk is one warp's unit of work: aim at ~2 chunks per warp at full grid, within [8 KB, 64 KB]
+      double c = work / (2.0 * max_ctas_ * warps_per_cta);
       chunk = (unsigned long long)std::min(64.0 * 1024, std::max(8.0 * 1024, c));
       chunk = align_up(chunk, 1024);
     }

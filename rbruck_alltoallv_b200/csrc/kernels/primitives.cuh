@@ -142,6 +142,14 @@ __device__ __forceinline__ void group_copy(char* dst, const char* src, size_t n,
     if (sh == 0) {
       const uint4* s = reinterpret_cast<const uint4*>(src);
       size_t i = tid;
+      // 8 independent 16-byte loads in flight per thread (4 KB per warp) before the first store
+      for (; i + 7 * (size_t)nt < nvec; i += 8 * (size_t)nt) {
+        uint4 v[8];
+        #pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = ld_cg_v4(s + i + j * (size_t)nt);
+        #pragma unroll
+        for (int j = 0; j < 8; j++) st_v4(d + i + j * (size_t)nt, v[j]);
+      }
       for (; i + 3 * (size_t)nt < nvec; i += 4 * (size_t)nt) {
         uint4 v0 = ld_cg_v4(s + i), v1 = ld_cg_v4(s + i + nt);
         uint4 v2 = ld_cg_v4(s + i + 2 * nt), v3 = ld_cg_v4(s + i + 3 * nt);

@@ -29,6 +29,12 @@ def alltoallv(send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=Non
             mean_block = float(np.mean(np.asarray(sendcounts))) * ts
         choice = _tuner.choose(c.P, c.nproc, mean_block)
         algo = choice.pop("algo")
+        protocol = choice.pop("protocol", "rendezvous")
+        host_counts = not (isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda)
+        if protocol == "eager" and host_counts and "eager_max_bytes" not in kw:
+            emax = c.max_block_bytes(sendcounts, ts)       # collective: agrees on the cell size
+            if 0 < emax <= (256 << 10) and (c.P + 64) * (2 * emax + 16) <= c.arena_bytes:
+                kw["eager_max_bytes"] = emax
         for k, v in choice.items():
             kw.setdefault(k, v)
     c.alltoallv(send, recv, sendcounts, sdispls, recvcounts, rdispls, algo=algo, **kw)

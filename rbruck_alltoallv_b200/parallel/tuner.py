@@ -88,3 +88,61 @@ def candidates(P: int, groups: Optional[List[int]] = None) -> List[dict]:
         out.append({"algo": "ttpl_bt_s1", "n": n, "r": 2, "b": 0})
         out.append({"algo": "ttpl_bt", "n": n, "r": 2, "b": 0})
     return out
+
+
+def sweep(comm, mean_block_bytes=(16, 256, 4096, 65536, 1 << 20, 4 << 20), type_size: int = 2, skew: str = "normal",
+          steps: int = 10, warmup: int = 3, seed: int = 0, groups=None, verbose: bool = True) -> List[dict]:
+    """Times every candidate (both protocols where the blocks fit the eager cells) for each size class on
+    ``comm`` and records the winners in the table.  Collective: every process of the communicator calls it."""
+    import numpy as np
+    import torch
+
+    from ..utils import distributions as D
+    from ..utils.timing import L2Flusher, RankAligner, time_steps
+
+    dev = f"cuda:{comm.device}"
+    flush, align = L2Flusher(dev), RankAligner(comm)
+    L, P, mine = comm.L, comm.P, comm.local_ranks
+    rows = []
+    for nbytes in mean_block_bytes:
+        elems = max(1, nbytes // type_size)
+        counts = D.zipf(P, 4 * elems, seed=seed) if skew == "zipf" else D.normal(P, elems, 0.25, seed=seed)
+        sc = counts[mine].astype(np.int32)
+        rc = counts.T[mine].astype(np.int32)
+        send = [torch.zeros(max(int(sc[i].sum()), 1) * type_size, dtype=torch.uint8, device=dev) for i in range(L)]
+        recv = [comm.symm_empty(max(int(rc[i].sum()), 1) * type_size, torch.uint8) for i in range(L)]
+        emax = comm.max_block_bytes(sc, type_size)
+        cell_room = comm.arena_bytes // (2 * max(emax, 8) + 16)
+        row = {"mean_block_bytes": nbytes, "skew": skew, "max_block_bytes": emax, "us": {}}
+        best, best_us = None, float("inf")
+        for cand in candidates(P, groups):
+            for eager in (False, True):
+                kw = dict(cand)
+                if eager:
+                    if emax > (256 << 10) or cell_room < P + 64:
+                        continue
+                    kw["eager_max_bytes"] = emax
+                name = "/".join(f"{k}={v}" for k, v in kw.items() if k != "eager_max_bytes") + ("/eager" if eager else "")
+                try:
+                    call = comm.prepare(send, recv, sc, None, rc, None, type_size=type_size, **kw)
+                except Exception:
+                    row["us"][name] = None
+                    continue
+                t = time_steps(call.launch, steps, warmup, flush=flush, align=align)
+                if comm.status()["code"]:
+                    comm.reset()
+                    row["us"][name] = None
+                    continue
+                us = float(np.median(t)) * 1e3
+                row["us"][name] = round(us, 2)
+                if us < best_us:
+                    best, best_us = dict(cand, protocol="eager" if eager else "rendezvous"), us
+        if best is not None:
+            record(P, comm.nproc, nbytes, best, best_us)
+            row["best"] = best
+            row["best_us"] = round(best_us, 2)
+        rows.append(row)
+        if verbose and comm.proc == 0:
+            print(json.dumps(row), flush=True)
+        del send, recv
+    return rows
