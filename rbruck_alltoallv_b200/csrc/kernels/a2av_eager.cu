@@ -232,16 +232,28 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         const size_t nunits = (bytes + 7) / 8;
         const size_t uend = min(nunits, u0 + cu);
         if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-          // 16-byte loads: two units per lane and step
-          for (size_t u = u0 + 2 * lane; u < uend; u += 64) {
-            if (u + 2 <= uend && (u + 2) * 8 <= bytes) {
-              const uint4 v = dev::ld_cg_v4(reinterpret_cast<const uint4*>(src + u * 8));
-              st_unit(dcell + 1 + u, v.x, v.y, ec.flag);
-              st_unit(dcell + 2 + u, v.z, v.w, ec.flag);
-            } else {
-              st_unit(dcell + 1 + u, load_word(src, 2 * u, bytes), load_word(src, 2 * u + 1, bytes), ec.flag);
-              if (u + 1 < uend)
-                st_unit(dcell + 2 + u, load_word(src, 2 * u + 2, bytes), load_word(src, 2 * u + 3, bytes), ec.flag);
+          // 16-byte loads, two units each; up to four loads per lane are issued before the first store so that
+          // their DRAM latencies overlap
+          for (size_t ub = u0; ub < uend; ub += 256) {
+            uint4 v[4];
+            bool full[4];
+            #pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const size_t u = ub + 64 * j + 2 * lane;
+              full[j] = (u + 2 <= uend) && ((u + 2) * 8 <= bytes);
+              if (full[j]) v[j] = dev::ld_cg_v4(reinterpret_cast<const uint4*>(src + u * 8));
+            }
+            #pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const size_t u = ub + 64 * j + 2 * lane;
+              if (full[j]) {
+                st_unit(dcell + 1 + u, v[j].x, v[j].y, ec.flag);
+                st_unit(dcell + 2 + u, v[j].z, v[j].w, ec.flag);
+              } else if (u < uend) {
+                st_unit(dcell + 1 + u, load_word(src, 2 * u, bytes), load_word(src, 2 * u + 1, bytes), ec.flag);
+                if (u + 1 < uend)
+                  st_unit(dcell + 2 + u, load_word(src, 2 * u + 2, bytes), load_word(src, 2 * u + 3, bytes), ec.flag);
+              }
             }
           }
         } else {
