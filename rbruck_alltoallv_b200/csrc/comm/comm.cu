@@ -382,9 +382,10 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   if (!chunk) {
     if (work < 0) chunk = 32 << 10;
     else {
-      // a chunk is one warp's unit of work: aim at ~2 chunks per warp at full grid, within [8 KB, 64 KB]
-      double c = work / (2.0 * max_ctas_ * warps_per_cta);
-      chunk = (unsigned long long)std::min(64.0 * 1024, std::max(8.0 * 1024, c));
+      // a chunk is one warp's unit of work: about one chunk per resident warp, within [2 KB, 64 KB].  Measured
+      // on B200: with fewer, larger chunks most warps idle and a 4 MB exchange takes twice as long.
+      double c = work / (1.0 * max_ctas_ * warps_per_cta);
+      chunk = (unsigned long long)std::min(64.0 * 1024, std::max(2.0 * 1024, c));
       chunk = align_up(chunk, 1024);
     }
   }
