@@ -40,6 +40,7 @@ def declare_cuda(lib):
     lib.rbv_symm_alloc.restype = C.c_void_p
     lib.rbv_symm_alloc.argtypes = [C.c_void_p, C.c_size_t]
     lib.rbv_symm_free.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_ctx_in_heap.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
     lib.rbv_comm.restype = C.c_void_p
     lib.rbv_comm.argtypes = [C.c_void_p, C.c_int]
     lib.rbv_comm_rank.argtypes = [C.c_void_p]

@@ -76,6 +76,7 @@ int rbv_ctx_info(rbv_ctx_t ctx, long long* o) {
   return 0;
 }
 void* rbv_ctx_heap(rbv_ctx_t ctx, int proc) { return ctx->c->peer_heap(proc); }
+int rbv_ctx_in_heap(rbv_ctx_t ctx, const void* p, size_t bytes) { return ctx->c->in_heap(p, bytes ? bytes : 1) ? 1 : 0; }
 void* rbv_symm_alloc(rbv_ctx_t ctx, size_t bytes) { return ctx->c->symm_alloc(bytes); }
 int rbv_symm_free(rbv_ctx_t ctx, void* p) { return ctx->c->symm_free(p); }
 rbv_comm_t rbv_comm(rbv_ctx_t ctx, int local_rank) {

@@ -63,6 +63,7 @@ int rbv_ctx_status(rbv_ctx_t ctx, rbv_status* out); /* synchronises the stream *
 int rbv_ctx_reset(rbv_ctx_t ctx);
 int rbv_ctx_info(rbv_ctx_t ctx, long long* out8); /* P, L, nproc, proc, device, seq, max_ctas, sm_count */
 void* rbv_ctx_heap(rbv_ctx_t ctx, int proc);
+int rbv_ctx_in_heap(rbv_ctx_t ctx, const void* ptr, size_t bytes); /* 1 if [ptr, ptr+bytes) lies in the symmetric heap */
 void* rbv_symm_alloc(rbv_ctx_t ctx, size_t bytes);
 int rbv_symm_free(rbv_ctx_t ctx, void* ptr);
 rbv_comm_t rbv_comm(rbv_ctx_t ctx, int local_rank);

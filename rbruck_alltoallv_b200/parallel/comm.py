@@ -225,6 +225,25 @@ class Communicator:
         them out, so there is no metadata phase and ``recv`` may be any device memory.  :meth:`max_block_bytes`
         agrees on the value across ranks.
         """
+        # Receive buffers outside the symmetric heap cannot be written by peers: the rendezvous protocol then goes
+        # through a symmetric bounce buffer (two extra local copies; the eager protocol needs none).
+        recv_l = [recv] if isinstance(recv, torch.Tensor) else list(recv)
+        bounce = None
+        if not eager_max_bytes and not inplace:
+            outside = [not self._lib.rbv_ctx_in_heap(self._ctx, C.c_void_p(t.data_ptr()), t.numel() * t.element_size())
+                       for t in recv_l]
+            if any(outside):
+                bounce = []
+                for t, out in zip(recv_l, outside):
+                    if out:
+                        bt = self._bounce_for(t)
+                        bt.copy_(t.reshape(-1).view(torch.uint8), non_blocking=True)   # keep what lies between the blocks
+                        bounce.append(bt)
+                    else:
+                        bounce.append(t)
+                recv = bounce
+                if type_size is None:
+                    type_size = recv_l[0].element_size()
         ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         st = stream or torch.cuda.current_stream(self.device)
@@ -235,6 +254,19 @@ class Communicator:
                                         int(chunk_bytes), C.c_void_p(st.cuda_stream))
         if rcode:
             raise CommError(f"alltoallv({algo}) failed with code {rcode}: {self._lib.rbv_last_error().decode()}")
+        if bounce is not None:
+            for t, bt in zip(recv_l, bounce):
+                if bt is not t:
+                    t.reshape(-1).view(torch.uint8).copy_(bt, non_blocking=True)
+
+    def _bounce_for(self, t: torch.Tensor) -> torch.Tensor:
+        """A symmetric buffer of t's size, kept for reuse (one per size and position in the call)."""
+        n = t.numel() * t.element_size()
+        cache = self.__dict__.setdefault("_bounce", {})
+        key = (n, t.data_ptr())
+        if key not in cache:
+            cache[key] = self.symm_empty(max(n, 1), torch.uint8)[:n]
+        return cache[key]
 
     def max_block_bytes(self, sendcounts, type_size: int) -> int:
         """Largest block of the whole exchange in bytes (host counts; collective over the processes)."""

@@ -7,6 +7,8 @@
     python -m rbruck_alltoallv_b200.utils.profile_case gemm1       # grouped SwiGLU GEMM, 2 experts x 2048 rows, 4096 -> 2 x 14336
     python -m rbruck_alltoallv_b200.utils.profile_case gemm2       # grouped down GEMM, 14336 -> 4096
     python -m rbruck_alltoallv_b200.utils.profile_case transpose   # fused pencil transpose, 384^3 complex64
+    python -m rbruck_alltoallv_b200.utils.profile_case eager       # eager protocol, Zipf blocks <= 64 KB, radix 2
+    python -m rbruck_alltoallv_b200.utils.profile_case moe         # MoE layer, 8192 tokens x 4096, 8 experts, FFN 1024
 """
 from __future__ import annotations
 
@@ -14,6 +16,20 @@ import sys
 
 import numpy as np
 import torch
+
+
+def _moe():
+    from ..ops.moe import MoEExpertParallel
+    from ..parallel.comm import Communicator
+    T, H, I, E = 8192, 4096, 1024, 8
+    comm = Communicator(nranks=1, heap_bytes=1 << 30, arena_bytes=1 << 20)
+    layer = MoEExpertParallel(comm, E, H, I, T, capacity_factor=1.0, seed=1)
+    x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda")
+    for _ in range(3):
+        layer.forward(x, logits)
+    layer.check()
+    comm.close()
 
 
 def _a2av(algo, small=False, **kw):
@@ -25,6 +41,8 @@ def _a2av(algo, small=False, **kw):
     sc, rc = counts.astype(np.int32), counts.T.astype(np.int32).copy()
     send = [torch.zeros(max(int(sc[i].sum()), 1), dtype=torch.float32, device="cuda") for i in range(P)]
     recv = [comm.symm_empty(max(int(rc[i].sum()), 1), torch.float32) for i in range(P)]
+    if kw.pop("eager", False):
+        kw["eager_max_bytes"] = comm.max_block_bytes(sc, 4)
     call = comm.prepare(send, recv, sc, None, rc, None, algo=algo, **kw)
     for _ in range(4):
         call.launch()
@@ -79,6 +97,10 @@ def main() -> int:
         _gemm(2)
     elif case == "transpose":
         _transpose()
+    elif case == "eager":
+        _a2av("rbruck", small=True, r=2, eager=True)
+    elif case == "moe":
+        _moe()
     else:
         raise SystemExit("unknown case")
     print("case", case, "done")

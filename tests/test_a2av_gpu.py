@@ -220,3 +220,18 @@ def test_protocols_can_alternate_on_one_communicator():
     for i in range(6):
         run_case(8, "rbruck", 4, counts, seed=80 + i, r=2, eager_max_bytes=(1200 if i % 2 == 0 else 0))
         run_case(8, "spreadout", 4, counts, seed=90 + i, eager_max_bytes=(0 if i % 3 == 0 else 1200))
+
+
+def test_plain_receive_buffers_go_through_a_bounce_buffer():
+    P, ts = 8, 4
+    comm = get_comm(P)
+    counts = dist.uniform(P, 500, seed=5)
+    prob = oracle.make_problem(counts, ts, 5, packed=False)
+    send_h = oracle.fill_send(prob, 5)
+    want = oracle.expected_recv(prob, send_h)
+    send = [torch.from_numpy(b).cuda() for b in send_h]
+    recv = [torch.full((len(w),), oracle.CANARY, dtype=torch.uint8, device="cuda") for w in want]   # torch allocations
+    for algo, kw in (("spreadout", {}), ("rbruck", dict(r=2))):
+        comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo=algo, type_size=ts, **kw)
+        comm.check()
+        assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
