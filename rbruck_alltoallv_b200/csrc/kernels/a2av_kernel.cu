@@ -1,13 +1,14 @@
 // The alltoallv kernel: one persistent cooperative launch per call and per process that performs
 //   (1) the metadata phase  -- every rank stores its sendcounts / recvcounts / rdispls row and its
-//       receive-buffer offset into every process's metadata table and bumps an arrival counter
+//       receive-buffer offset into every process's metadata table as self-validating 16-byte units
 //       (this replaces the host-side MPI_Alltoall of counts in the reference's drivers, the
 //       MPI_Allreduce(MAX) and the per-round metadata MPI_Sendrecv, e.g. src/tuna2.cpp:45,160),
 //   (2) the data phase      -- an interpreter of the plan's op list: each op copies one block from
 //       the executing rank's send buffer or staging cell straight into the destination rank's
 //       receive buffer or staging cell (a peer mapping over NVLink when the destination lives on
 //       another GPU); rotation, pack, unpack and final placement are folded into the addressing,
-//   (3) completion          -- waits until all P blocks of every local rank have landed.
+//   (3) completion          -- waits until every chunk bound for a local rank's receive buffer has landed
+//       (each chunk of a final hop bumps the receiver's arrival counter; the receiver knows all sizes).
 //
 // Work distribution: ops are cut into chunks of `chunk_bytes`; chunk c of the process-wide
 // sequence is handled by WARP c mod (warps in the grid).  A warp copies its chunk with 16-byte
