@@ -59,6 +59,12 @@ def ensure_built() -> Path | None:
     if out.exists():
         return out
     if not (SRC_COPY / "src").exists():
+        # no copy yet: make one if the reference tree is mounted on this machine
+        for cand in (Path("/root/reference"),):
+            if (cand / "src" / "rbruckv.h").exists():
+                REF.mkdir(exist_ok=True)
+                copy_sources(cand)
+                return build()
         return None
     return build()
 

@@ -192,12 +192,41 @@ def run_ours(args):
         t = time_steps(lambda: step(best), steps=args.steps, warmup=warm, flush=flush, align=align)
         comm.check()
 
-        # end to end through the public API: pinned host -> device, alltoallv, device -> pinned host
-        def e2e_step():
+        # End to end through the public API.  Two ways to move a step's inputs from pinned host memory to the GPUs
+        # and its result back, both timed (the faster one is reported, the other is listed):
+        #  "copy":      cudaMemcpyAsync H2D of every send buffer, the collective, cudaMemcpyAsync D2H of every
+        #               receive buffer;
+        #  "zero_copy": the eager-protocol kernel reads the send blocks straight from the pinned host buffers over
+        #               PCIe and writes the received blocks straight into the pinned host receive buffers (the
+        #               eager protocol accepts any device-accessible memory on both sides).
+        def e2e_copy():
             dev_send.copy_(pin_send, non_blocking=True)
             step(best)
             pin_recv.copy_(dev_recv, non_blocking=True)
-        te = time_steps(e2e_step, steps=args.steps, warmup=warm, flush=flush, align=align)
+
+        pin_send_l = [pin_send[s_off[i]:s_off[i] + max(s_sizes[i], 1)] for i in range(L)]
+        pin_recv_l = [pin_recv[r_off[i]:r_off[i] + max(r_sizes[i], 1)] for i in range(L)]
+        zc_call = comm.prepare(pin_send_l, pin_recv_l, sc, sd, rc, rd, algo="rbruck", r=best[0], type_size=TYPE_SIZE,
+                               eager_max_bytes=emax)
+        e2e_paths = {"copy": e2e_copy, "zero_copy": zc_call.launch}
+        e2e_us = {}
+        for name, fn in e2e_paths.items():
+            pin_recv.fill_(0)
+            e2e_us[name] = float(np.mean(time_steps(fn, steps=20, warmup=3, flush=flush, align=align))) * 1e3
+            comm.check()
+            got = pin_recv.numpy()
+            for i, r in enumerate(mine):
+                if not np.array_equal(got[r_off[i]:r_off[i] + r_sizes[i]], want[r]):
+                    raise SystemExit(f"rank {r}: end-to-end result differs from the expectation ({name})")
+        names = list(e2e_paths)
+        pick = min(range(len(names)), key=lambda i: e2e_us[names[i]])
+        if world > 1:
+            b = torch.tensor([pick], device=dev)
+            dist.broadcast(b, 0)
+            pick = int(b.item())
+        e2e_name = names[pick]
+        pin_recv.fill_(0)
+        te = time_steps(e2e_paths[e2e_name], steps=args.steps, warmup=warm, flush=flush, align=align)
         comm.check()
     got = pin_recv.numpy()
     for i, r in enumerate(mine):
@@ -231,7 +260,8 @@ def run_ours(args):
                     "timing": "CUDA events around each step, per-step max over ranks, summed over the K steps"}),
                 "clocks": clocks.summary(),
                 "e2e": {"value": value_e, "unit": "GB/s", "ms_per_step": ms_e, "h2d_bytes_per_step": h2d,
-                        "d2h_bytes_per_step": d2h},
+                        "d2h_bytes_per_step": d2h, "path": e2e_name,
+                        "us_per_path": {k: round(v, 2) for k, v in e2e_us.items()}},
                 "gpu_launches": args.steps}
         if sweep is not None:
             line["sweep"] = sweep
