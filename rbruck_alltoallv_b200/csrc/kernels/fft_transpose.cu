@@ -1,6 +1,6 @@
 // Pencil transpose for distributed 3-D FFTs: strided gather -> all-to-all -> transposed scatter in ONE kernel.
 // For every destination rank the caller describes a 3-D box of the local array and where (and with which
-// strides) it lands in the destination rank's array; the kernel moves 32 x 32 element tiles through shared
+// strides) it lands in the destination rank's array; the kernel moves 64 x 64 element tiles through shared
 // memory so that both the local reads and the peer writes over NVLink are contiguous runs, then signals all
 // ranks and waits (bounded) until every rank's boxes have landed here.  The reference only generates the
 // count patterns of such an exchange (examples/FFT_distribution.cpp:66-87) and leaves packing to the caller.
@@ -30,9 +30,10 @@ struct TransposeArgs {
   rbv_box box[kMaxProcs];
 };
 
-template <typename T>
-__device__ void move_boxes(const TransposeArgs& a, T (*tile)[TS + 1]) {
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+// TF x TK tile: TF elements along the destination's contiguous dimension, TK along the source's (dimension 2).
+template <typename T, int TF, int TK>
+__device__ void move_boxes(const TransposeArgs& a, T* tile_raw) {
+  T (*tile)[TK + 1] = reinterpret_cast<T(*)[TK + 1]>(tile_raw);
   // tiles are enumerated over all destinations; a CTA takes tile ids blockIdx.x, blockIdx.x + gridDim.x, ...
   long long tile_base = 0;
   for (int d = 0; d < a.nproc; d++) {
@@ -45,10 +46,10 @@ __device__ void move_boxes(const TransposeArgs& a, T (*tile)[TS + 1]) {
     const int nf = fast == 1 ? b.n1 : b.n0;                  // extent of the destination-fastest dim (if != 2)
     const int no = fast == 1 ? b.n0 : b.n1;                  // the remaining ("outer") dim
     const long long sf = fast == 1 ? b.s1 : b.s0, so = fast == 1 ? b.s0 : b.s1;
-    const long long tf = 1, to = fast == 1 ? b.t0 : b.t1;
-    const int W2 = fast == 2 ? kThreadsT : TS;               // elements of dim 2 per tile
+    const long long to = fast == 1 ? b.t0 : b.t1;
+    const int W2 = fast == 2 ? kThreadsT : TK;               // elements of dim 2 per tile
     const int t2n = (b.n2 + W2 - 1) / W2;
-    const int tfn = fast == 2 ? 1 : (nf + TS - 1) / TS;
+    const int tfn = fast == 2 ? 1 : (nf + TF - 1) / TF;
     const long long ntiles = fast == 2 ? (long long)b.n0 * b.n1 * t2n : (long long)no * tfn * t2n;
     const long long first = ((long long)blockIdx.x - (tile_base % (long long)gridDim.x) + gridDim.x) % gridDim.x;
     for (long long t = first; t < ntiles; t += gridDim.x) {
@@ -59,22 +60,30 @@ __device__ void move_boxes(const TransposeArgs& a, T (*tile)[TS + 1]) {
         const int j = (int)(ij % b.n1), i = (int)(ij / b.n1);
         if (k < b.n2) dst[i * b.t0 + j * b.t1 + k] = src[i * b.s0 + j * b.s1 + k];
       } else {
-        const int k0 = (int)(t % t2n) * TS;
+        const int k0 = (int)(t % t2n) * TK;
         const long long r1 = t / t2n;
-        const int f0 = (int)(r1 % tfn) * TS;
+        const int f0 = (int)(r1 % tfn) * TF;
         const int o = (int)(r1 / tfn);
-        // read: rows along dim 2 (contiguous in the source)
-        #pragma unroll
-        for (int r = ty; r < TS; r += 8) {
-          const int f = f0 + r, k = k0 + tx;
-          if (f < nf && k < b.n2) tile[r][tx] = src[o * so + f * sf + k];
+        // read: rows along dim 2 (contiguous in the source); all loads of a thread are issued back to back
+        {
+          const int tx = threadIdx.x % TK, ty = threadIdx.x / TK;
+          constexpr int RS = kThreadsT / TK;
+          #pragma unroll
+          for (int r = 0; r < TF; r += RS) {
+            const int f = f0 + r + ty, k = k0 + tx;
+            if (f < nf && k < b.n2) tile[r + ty][tx] = src[o * so + f * sf + k];
+          }
         }
         __syncthreads();
         // write: rows along the destination-fastest dim (contiguous in the destination)
-        #pragma unroll
-        for (int r = ty; r < TS; r += 8) {
-          const int k = k0 + r, f = f0 + tx;
-          if (f < nf && k < b.n2) dst[o * to + (long long)k * b.t2 + f * tf] = tile[tx][r];
+        {
+          const int tx = threadIdx.x % TF, ty = threadIdx.x / TF;
+          constexpr int RS = kThreadsT / TF;
+          #pragma unroll
+          for (int r = 0; r < TK; r += RS) {
+            const int k = k0 + r + ty, f = f0 + tx;
+            if (f < nf && k < b.n2) dst[o * to + (long long)k * b.t2 + f] = tile[tx][r + ty];
+          }
         }
         __syncthreads();
       }
@@ -84,10 +93,12 @@ __device__ void move_boxes(const TransposeArgs& a, T (*tile)[TS + 1]) {
 }
 
 __global__ void __launch_bounds__(kThreadsT) transpose_exchange_kernel(const __grid_constant__ TransposeArgs a) {
-  __shared__ __align__(16) unsigned char tile_raw[TS * (TS + 1) * 16];
-  if (a.elem_size == 8) move_boxes<unsigned long long>(a, reinterpret_cast<unsigned long long(*)[TS + 1]>(tile_raw));
-  else if (a.elem_size == 4) move_boxes<unsigned>(a, reinterpret_cast<unsigned(*)[TS + 1]>(tile_raw));
-  else move_boxes<uint4>(a, reinterpret_cast<uint4(*)[TS + 1]>(tile_raw));
+  // 64 x 64 tiles (512-byte runs on both sides) for elements up to 8 bytes, 32 x 32 for 16-byte elements
+  __shared__ __align__(16) unsigned char tile_raw[64 * 65 * 8];
+  static_assert(64 * 65 * 8 >= TS * (TS + 1) * 16, "tile buffer");
+  if (a.elem_size == 8) move_boxes<unsigned long long, 64, 64>(a, reinterpret_cast<unsigned long long*>(tile_raw));
+  else if (a.elem_size == 4) move_boxes<unsigned, 64, 64>(a, reinterpret_cast<unsigned*>(tile_raw));
+  else move_boxes<uint4, TS, TS>(a, reinterpret_cast<uint4*>(tile_raw));
   // completion: last CTA signals every process, then waits for all of them (bounded)
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -125,7 +136,7 @@ extern "C" int rbv_transpose_exchange(rbv_ctx_t ctx, const void* src, unsigned l
   a.src = static_cast<const char*>(src);
   a.dst_off = dst_off;
   a.elem_size = elem_size;
-  int grid = max_ctas > 0 ? max_ctas : c.sm_count() * 4;
+  int grid = max_ctas > 0 ? max_ctas : c.sm_count() * 6;
   transpose_exchange_kernel<<<grid, kThreadsT, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return (int)cudaGetLastError();
 }

@@ -235,3 +235,21 @@ def test_plain_receive_buffers_go_through_a_bounce_buffer():
         comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo=algo, type_size=ts, **kw)
         comm.check()
         assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
+
+
+def test_phase_timers_follow_the_reference_names():
+    import ctypes as C
+    comm = get_comm(8)
+    lib = comm._lib
+    comm.enable_trace(True)
+    counts = dist.uniform(8, 2000, seed=9)
+    run_case(8, "ttpl_bt", 8, counts, seed=9, n=4, r=2, b=1)
+    lib.rbv_ctx_set_stream(comm._ctx, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert lib.rbv_update_timers(comm._ctx) == 0
+    names = ["init_time", "findMax_time", "rotateIndex_time", "alcCopy_time", "getBlock_time", "prepData_time",
+             "excgMeta_time", "excgData_time", "replace_time", "orgData_time", "prepSP_time", "SP_time", "intra_time"]
+    vals = {n: C.c_double.in_dll(lib, n).value for n in names}
+    assert all(v >= 0 for v in vals.values())
+    assert vals["excgMeta_time"] > 0 and vals["excgData_time"] + vals["SP_time"] > 0
+    assert vals["replace_time"] == 0 and vals["orgData_time"] == 0      # pack / unpack / organise no longer exist
+    comm.enable_trace(False)
