@@ -51,12 +51,19 @@ class PencilTranspose:
         self.shape_y = (int(self.zsplit[c]), int(self.xsplit[r]), n)
         self.shape_z = (int(self.xsplit[r]), int(self.y2split[c]), n)
         # destination arrays live in the symmetric heap (peers write into them)
-        self.buf_y = comm.symm_empty(self.shape_y, dtype)
-        self.buf_z = comm.symm_empty(self.shape_z, dtype)
+        # Peers address these arrays by their offset inside the heap, so the offset must be the same on every
+        # rank: allocate the largest shape any rank has (the splits are known everywhere) and use a prefix of it.
+        cap_y = int(self.zsplit.max()) * int(self.xsplit.max()) * n
+        cap_z = int(self.xsplit.max()) * int(self.y2split.max()) * n
+        self._store_y = comm.symm_empty(cap_y, dtype)
+        self._store_z = comm.symm_empty(cap_z, dtype)
+        self.buf_y = self._store_y[: int(np.prod(self.shape_y))].view(self.shape_y)
+        self.buf_z = self._store_z[: int(np.prod(self.shape_z))].view(self.shape_z)
         self.error = torch.zeros(2, dtype=torch.int32, device=f"cuda:{comm.device}")
         heap0 = self.lib.rbv_ctx_heap(comm._ctx, comm.proc)
         self.off_y = self.buf_y.data_ptr() - heap0
         self.off_z = self.buf_z.data_ptr() - heap0
+        comm.require_same_offsets(self.off_y, self.off_z)
         self._boxes_xy = self._make_boxes_xy()
         self._boxes_yz = self._make_boxes_yz()
 

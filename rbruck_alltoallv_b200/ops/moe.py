@@ -89,6 +89,7 @@ class MoEExpertParallel:
         heap0 = self.lib.rbv_ctx_heap(comm._ctx, comm.proc)
         self.xrecv_off = self.xrecv.data_ptr() - heap0
         self.y_off = self.y.data_ptr() - heap0
+        comm.require_same_offsets(self.xrecv_off, self.y_off)
         # the histogram all-gather: every rank sends the same E counters to every rank
         cnt = np.full((1, self.P), self.E, dtype=np.int32)
         self._gather = comm.prepare(self.hist, self.hist_all.view(-1), cnt, np.zeros((1, self.P), dtype=np.int64), cnt,

@@ -268,6 +268,17 @@ class Communicator:
             cache[key] = self.symm_empty(max(n, 1), torch.uint8)[:n]
         return cache[key]
 
+    def require_same_offsets(self, *offsets: int) -> None:
+        """Kernels that address a peer's buffer by its heap offset need that offset to be equal on every rank
+        (true when all ranks make the same sequence of equally sized symmetric allocations).  Collective."""
+        if self._side is None:
+            return
+        mine = [int(o) for o in offsets]
+        allv = [None] * self.nproc
+        self._dist.all_gather_object(allv, mine, group=self._side)
+        if any(v != allv[0] for v in allv):
+            raise CommError(f"symmetric buffers sit at different heap offsets on different ranks: {allv}")
+
     def max_block_bytes(self, sendcounts, type_size: int) -> int:
         """Largest block of the whole exchange in bytes (host counts; collective over the processes)."""
         m = int(np.max(np.asarray(sendcounts))) * int(type_size) if np.size(sendcounts) else 0

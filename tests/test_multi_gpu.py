@@ -47,11 +47,12 @@ def test_moe_two_processes_matches_reference():
 
 
 @pytest.mark.skipif(_ngpus() < 2, reason="needs 2 GPUs")
-def test_fft_transposes_two_processes():
+@pytest.mark.parametrize("pr,pc", [(2, 1), (1, 2)])
+def test_fft_transposes_two_processes(pr, pc):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29661", "-m", "rbruck_alltoallv_b200.utils.fft_bench", "--size", "48", "--pr", "2",
-           "--pc", "1", "--check", "--steps", "2", "--warmup", "1"]
+           "127.0.0.1", "--master-port", "29661", "-m", "rbruck_alltoallv_b200.utils.fft_bench", "--size", "48", "--pr", str(pr),
+           "--pc", str(pc), "--check", "--steps", "2", "--warmup", "1"]
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert '"check": "ok"' in res.stdout
