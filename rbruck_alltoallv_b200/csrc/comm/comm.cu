@@ -188,6 +188,7 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
         }
       }
       dp->n_eops = (int)eops.size();
+      dp->h_eops = eops;
       if (dp->n_eops) {
         RBV_CUDA_THROW(cudaMalloc(&dp->d_eops, eops.size() * sizeof(Op)));
         RBV_CUDA_THROW(cudaMemcpy(dp->d_eops, eops.data(), eops.size() * sizeof(Op), cudaMemcpyHostToDevice));
@@ -417,12 +418,27 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
       }
       mx = std::max<long long>(mx, 1);
     }
+    // exact item count for a chunk size: first hops by their own size, unpacks by the receiver's recvcount,
+    // relays by the largest block
+    auto count_items = [&](unsigned long long ch) {
+      double items = 0;
+      for (const Op& o : dp->h_eops) {
+        const int lr = o.src - proc_ * L_;
+        long long bytes = mx;
+        if (!ca.counts_on_device) {
+          if (o.flags & 2u) { if (ca.recvcounts) bytes = (long long)ca.recvcounts[(size_t)lr * P_ + o.origin] * ts; }
+          else if (o.src_cell < 0) bytes = (long long)ca.sendcounts[(size_t)lr * P_ + o.dest] * ts;
+        }
+        items += std::max(1.0, std::ceil((double)bytes / (double)ch));
+      }
+      return items;
+    };
     unsigned long long ech = opt.chunk_bytes ? align_up(opt.chunk_bytes, 16) : 512;
-    double items = (double)dp->n_eops * std::ceil((double)mx / (double)ech);
+    double items = count_items(ech);
     if (!opt.chunk_bytes)
       while (items > (double)max_ctas_ * warps_per_cta && ech < 8192) {
         ech *= 2;
-        items = (double)dp->n_eops * std::ceil((double)mx / (double)ech);
+        items = count_items(ech);
       }
     ka.chunk_bytes = ech;
     int g = opt.grid > 0 ? opt.grid : (int)std::min<double>(max_ctas_, std::max(1.0, std::ceil(items / warps_per_cta)));

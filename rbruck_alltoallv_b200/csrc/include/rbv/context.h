@@ -25,6 +25,7 @@ struct DevPlan {
   // (local rank, source); cell indices: 0..P-1 arrival cell of source s, P + c staging cell c
   Op* d_eops = nullptr;
   int n_eops = 0;
+  std::vector<Op> h_eops;  // host copy (sizing of work items per call)
 };
 
 struct CallOptions {
