@@ -30,6 +30,7 @@ CUDA_SOURCES = [
     "kernels/a2av_eager.cu",
     "kernels/moe_kernels.cu",
     "kernels/grouped_gemm_sm100.cu",
+    "kernels/grouped_gemm_fp8_sm100.cu",
     "kernels/fft_transpose.cu",
     "kernels/noalloc.cu",
     "api/c_api.cu",

@@ -25,6 +25,16 @@ int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void* B, void* 
                           const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
                           int max_ctas, void* cuda_stream);
 
+/* Block-scaled fp8 (e4m3) variant.  A: [a_rows, K] bytes with one fp32 scale per row and 128-wide K block, stored
+ * transposed as a_scale_t [K / 128][a_rows]; B: [G, N, K] bytes with one scale per 128 x 128 block, b_scale
+ * [G][N / 128][K / 128].  N % 128 == 0, K % 128 == 0.  Output bf16, epilogues as above. */
+int rbv_grouped_gemm_fp8(const void* A, const float* a_scale_t, long long a_rows, const void* B, const float* b_scale,
+                         void* C, const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
+                         int epilogue, int* error_flag, int max_ctas, void* cuda_stream);
+/* bf16 [rows, K] (row stride ldx elements) -> e4m3 [rows, K] + scale_t [K / 128][rows], scale = amax / 448. */
+int rbv_quantize_rows_fp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, float* scale_t,
+                          void* cuda_stream);
+
 /* Router: softmax over E logits per token, top-2, weights renormalised to sum to one.
  *   logits [T, E] fp32;  topk_idx [T, 2] int32;  topk_w [T, 2] fp32;  hist [E] int32 (zeroed by the call). */
 int rbv_moe_route(const float* logits, int T, int E, int* topk_idx, float* topk_w, int* hist, void* cuda_stream);

@@ -45,6 +45,64 @@ def grouped_gemm(A: torch.Tensor, B: torch.Tensor, group_start: torch.Tensor, gr
     return out
 
 
+def quantize_rows_fp8(x: torch.Tensor):
+    """bf16 [rows, K] -> (e4m3 bytes [rows, K], scales [K // 128, rows]); one scale per row and 128-wide K block."""
+    lib = _native.cuda_lib()
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 128 == 0
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(K // 128, rows, dtype=torch.float32, device=x.device)
+    st = torch.cuda.current_stream(x.device).cuda_stream
+    rc = lib.rbv_quantize_rows_fp8(_p(x), rows, K, x.stride(0), _p(q), _p(sc), C.c_void_p(st))
+    if rc:
+        raise RuntimeError(f"quantisation launch failed (CUDA error {rc})")
+    return q, sc
+
+
+def quantize_weight_blocks_fp8(w: torch.Tensor):
+    """bf16 / fp32 [G, N, K] -> (e4m3 bytes [G, N, K], scales [G, N // 128, K // 128]); one scale per 128 x 128 block."""
+    G, N, K = w.shape
+    blk = w.float().view(G, N // 128, 128, K // 128, 128)
+    amax = blk.abs().amax(dim=(2, 4))
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    q = (blk / scale[:, :, None, :, None]).to(torch.float8_e4m3fn).view(G, N, K)
+    return q.view(torch.uint8).contiguous(), scale.contiguous()
+
+
+def dequantize_rows_fp8(q: torch.Tensor, scale_t: torch.Tensor) -> torch.Tensor:
+    rows, K = q.shape
+    return (q.view(torch.float8_e4m3fn).float().view(rows, K // 128, 128) * scale_t.t()[:, :, None]).view(rows, K)
+
+
+def dequantize_weight_blocks_fp8(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    G, N, K = q.shape
+    return (q.view(torch.float8_e4m3fn).float().view(G, N // 128, 128, K // 128, 128)
+            * scale[:, :, None, :, None]).view(G, N, K)
+
+
+def grouped_gemm_fp8(Aq: torch.Tensor, a_scale_t: torch.Tensor, Bq: torch.Tensor, b_scale: torch.Tensor,
+                     group_start: torch.Tensor, group_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
+                     swiglu: bool = False, error: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
+    """Block-scaled e4m3 grouped GEMM (see ``csrc/kernels/grouped_gemm_fp8_sm100.cu``); bf16 output."""
+    lib = _native.cuda_lib()
+    G, N, K = Bq.shape
+    M = Aq.shape[0]
+    assert Aq.dtype == torch.uint8 and Bq.dtype == torch.uint8 and Aq.is_contiguous() and Bq.is_contiguous()
+    assert a_scale_t.shape == (K // 128, M) and b_scale.shape == (G, N // 128, K // 128)
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(M, n_out, dtype=torch.bfloat16, device=Aq.device)
+    if error is None:
+        error = torch.zeros(1, dtype=torch.int32, device=Aq.device)
+    st = torch.cuda.current_stream(Aq.device).cuda_stream
+    rc = lib.rbv_grouped_gemm_fp8(_p(Aq), _p(a_scale_t), M, _p(Bq), _p(b_scale), _p(out), _p(group_start),
+                                  _p(group_rows), G, N, K, out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas),
+                                  C.c_void_p(st))
+    if rc:
+        raise RuntimeError(f"fp8 grouped GEMM launch failed (CUDA error {rc})")
+    return out
+
+
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Interleaves [G, I, H] gate and up weights into the [G, 2I, H] layout the SwiGLU epilogue expects."""
     G, I, H = gate.shape
@@ -55,7 +113,7 @@ class MoEExpertParallel:
     """One MoE FFN layer sharded by experts over the ranks of a communicator (one rank per GPU)."""
 
     def __init__(self, comm, num_experts: int, hidden: int, inter: int, tokens: int, capacity_factor: float = 2.0,
-                 seed: int = 0, init_std: float = 0.02):
+                 seed: int = 0, init_std: float = 0.02, fp8: bool = False):
         if comm.L != 1:
             raise ValueError("the MoE path needs one rank per process")
         if num_experts % comm.P:
@@ -70,6 +128,10 @@ class MoEExpertParallel:
         bf = torch.bfloat16
         self.w13 = (torch.randn(self.El, 2 * inter, hidden, device=dev, generator=g) * init_std).to(bf)
         self.w2 = (torch.randn(self.El, hidden, inter, device=dev, generator=g) * init_std).to(bf)
+        self.fp8 = bool(fp8)
+        if self.fp8:   # expert weights as e4m3 with one scale per 128 x 128 block
+            self.w13_q, self.w13_s = quantize_weight_blocks_fp8(self.w13)
+            self.w2_q, self.w2_s = quantize_weight_blocks_fp8(self.w2)
         self.cap = int(np.ceil(capacity_factor * 2 * tokens / 128.0)) * 128
         i32 = torch.int32
         self.xrecv = comm.symm_empty((self.cap, hidden), bf)
@@ -117,10 +179,19 @@ class MoEExpertParallel:
         self._check(lib.rbv_moe_dispatch(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base), _p(self.cursor),
                                          _p(self.slot), self.xrecv_off, self.cap, self.E, _p(self.error[0:1]), st),
                     "dispatch")
-        grouped_gemm(self.xrecv, self.w13, self.group_start, self.group_rows, out=self.h, swiglu=True,
-                     error=self.error[1:2])
-        grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False,
-                     error=self.error[2:3])
+        if self.fp8:
+            # activations are quantised row-wise (1 x 128 blocks) right before each GEMM
+            xq, xs = quantize_rows_fp8(self.xrecv)
+            grouped_gemm_fp8(xq, xs, self.w13_q, self.w13_s, self.group_start, self.group_rows, out=self.h, swiglu=True,
+                             error=self.error[1:2])
+            hq, hs = quantize_rows_fp8(self.h)
+            grouped_gemm_fp8(hq, hs, self.w2_q, self.w2_s, self.group_start, self.group_rows, out=self.y,
+                             error=self.error[2:3])
+        else:
+            grouped_gemm(self.xrecv, self.w13, self.group_start, self.group_rows, out=self.h, swiglu=True,
+                         error=self.error[1:2])
+            grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False,
+                         error=self.error[2:3])
         self._check(lib.rbv_moe_combine(ctx, _p(out), T, H, _p(self.topk_idx), _p(self.topk_w), _p(self.slot),
                                         self.y_off, self.E, _p(self.error[3:4]), st), "combine")
         return out

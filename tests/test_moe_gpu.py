@@ -77,3 +77,49 @@ def test_router_top2():
 def test_moe_layer_single_gpu():
     from rbruck_alltoallv_b200.models.moe_layer import smoke_moe
     smoke_moe()
+
+
+@pytest.mark.parametrize("rows,N,K", [([128], 128, 128), ([100, 37, 0, 300], 256, 256), ([513, 64], 512, 1024)])
+def test_grouped_gemm_fp8_block_scaled(rows, N, K):
+    from rbruck_alltoallv_b200.ops import moe
+    torch.manual_seed(3)
+    G, M = len(rows), int(sum(rows))
+    A = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 3).to(torch.bfloat16)
+    B = (torch.randn(G, N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    Aq, As = moe.quantize_rows_fp8(A)
+    Bq, Bs = moe.quantize_weight_blocks_fp8(B)
+    # the quantiser itself: dequantised values within e4m3 precision of the input
+    assert (moe.dequantize_rows_fp8(Aq, As) - A.float()).abs().max().item() <= 0.07 * A.float().abs().max().item()
+    gs, gr = _groups(rows, "cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    Ad, Bd = moe.dequantize_rows_fp8(Aq, As), moe.dequantize_weight_blocks_fp8(Bq, Bs)
+    r0 = 0
+    for g, n in enumerate(rows):
+        if n:
+            ref = Ad[r0:r0 + n] @ Bd[g].t()          # exact product of the quantised operands, fp32
+            got = out[r0:r0 + n].float()
+            assert (got - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-3, f"group {g}"
+        r0 += n
+
+
+def test_moe_layer_fp8_close_to_bf16():
+    from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    comm = Communicator(nranks=1, heap_bytes=256 << 20, arena_bytes=1 << 20)
+    try:
+        T, H, I, E = 256, 256, 512, 8
+        layer = MoEExpertParallel(comm, E, H, I, T, seed=1, fp8=True)
+        g = torch.Generator(device="cuda")
+        g.manual_seed(7)
+        x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda", generator=g)
+        out = layer.forward(x, logits)
+        layer.check()
+        ref, _, _ = reference_forward(x, logits, layer.w13, layer.w2)
+        rel = (out.float() - ref).norm().item() / ref.norm().item()
+        assert rel < 0.08, f"fp8 layer deviates {rel:.3f} from the bf16 reference"
+    finally:
+        comm.close()
