@@ -6,8 +6,8 @@
 // These blocks do not match the 32-element hardware scaling of the MX instruction kinds, so scaling is done in
 // software: every K block (128 fp8 = one 128-byte swizzle row) is multiplied on its own by four
 // tcgen05.mma.kind::f8f6f4 (K = 32) into one of four 128-column TMEM slots; the four epilogue warps pull each
-// finished slot with tcgen05.ld, scale it and accumulate in registers (128 fp32 per thread = one output row of
-// the 128 x 128 tile), then hand the slot back.  MMA of block kb + 1..3 overlaps the scaling of block kb.
+// finished slot with tcgen05.ld (eight warps: two per TMEM lane quarter, 64 columns each), hand the slot back as
+// soon as it sits in registers, then scale and accumulate (64 fp32 per thread).  MMA of block kb + 1..3 overlaps the scaling of block kb.
 // Same structure as the bf16 kernel otherwise: TMA producer warp (plain tiled loads, no multicast), one MMA
 // thread, persistent static tile schedule over ragged groups, bounded waits.  No counterpart in the reference.
 #include <cuda.h>
@@ -30,7 +30,8 @@ constexpr int BM = 128, BN = 128, BK = 128, STAGES = 6, SLOTS = 4;
 constexpr int A_TILE = BM * BK;          // 16 KB (1 byte per element)
 constexpr int B_TILE = BN * BK;          // 16 KB
 constexpr int STAGE = A_TILE + B_TILE;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;          // TMA warp, MMA warp, 8 scaling / epilogue warps
+constexpr int HN = BN / 2;            // columns per epilogue warp (two warps share a TMEM lane quarter)
 constexpr size_t SMEM = (size_t)STAGES * STAGE + 1024 + 256;
 
 struct Fp8Params {
@@ -83,7 +84,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < SLOTS; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+    for (int b = 0; b < SLOTS; b++) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 8); }
     s_abort = 0;
     mbar_fence_init();
   }
@@ -145,7 +146,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
       if (!ok) { s_abort = 1; atomicExch(p.error, 2); }
     }
   } else {
+    // warps 2..9: lane quarter = warp % 4, column half = (warp - 2) / 4
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     __nv_bfloat16* C = static_cast<__nv_bfloat16*>(p.C);
     const int nkb = num_kb;
@@ -154,9 +157,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     for (int t = blockIdx.x; ok; t += gridDim.x) {
       const Tile tl = tile_of(p, t, s_rows, s_start);
       if (!tl.valid) break;
-      float acc[BN];
+      float acc[HN];
       #pragma unroll
-      for (int j = 0; j < BN; j++) acc[j] = 0.0f;
+      for (int j = 0; j < HN; j++) acc[j] = 0.0f;
       const long long arow = (long long)tl.m0 + row;
       const bool in_a = arow < p.a_rows;
       const float* sb = p.b_scale + ((size_t)tl.g * (p.N / 128) + tl.n0 / 128) * nkb;
@@ -167,26 +170,27 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         if (kb + 1 < nkb) sa_next = in_a ? __ldg(p.a_scale + (size_t)(kb + 1) * p.a_rows + arow) : 0.0f;
         if (!mbar_wait(&tfull_bar[slot], (it / SLOTS) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)slot * BN;
-        #pragma unroll
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr + c, r);
-          tmem_ld_wait();
-          #pragma unroll
-          for (int j = 0; j < 32; j++) acc[c + j] = fmaf(scale, __uint_as_float(r[j]), acc[c + j]);
-        }
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)slot * BN + (uint32_t)half * HN;
+        // both 32-column loads are in flight before the first multiply-add
+        uint32_t r0[32], r1[32];
+        tmem_ld32(taddr, r0);
+        tmem_ld32(taddr + 32, r1);
+        tmem_ld_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty_bar[slot]);
+        if (lane == 0) mbar_arrive(&tempty_bar[slot]);   // the slot is free as soon as it sits in registers
+        #pragma unroll
+        for (int j = 0; j < 32; j++) acc[j] = fmaf(scale, __uint_as_float(r0[j]), acc[j]);
+        #pragma unroll
+        for (int j = 0; j < 32; j++) acc[32 + j] = fmaf(scale, __uint_as_float(r1[j]), acc[32 + j]);
       }
       if (!ok) break;
       if (row < tl.rows_left) {
         __nv_bfloat16* crow = C + (size_t)(tl.m0 + row) * p.ldc;
         if (p.epilogue == 1) {
-          uint4* dst = reinterpret_cast<uint4*>(crow + tl.n0 / 2);
+          uint4* dst = reinterpret_cast<uint4*>(crow + (tl.n0 + half * HN) / 2);
           #pragma unroll
-          for (int v = 0; v < BN / 16; v++) {
+          for (int v = 0; v < HN / 16; v++) {
             uint32_t o[4];
             #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -197,9 +201,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
             dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
           }
         } else {
-          uint4* dst = reinterpret_cast<uint4*>(crow + tl.n0);
+          uint4* dst = reinterpret_cast<uint4*>(crow + tl.n0 + half * HN);
           #pragma unroll
-          for (int v = 0; v < BN / 8; v++) {
+          for (int v = 0; v < HN / 8; v++) {
             uint32_t o[4];
             #pragma unroll
             for (int j = 0; j < 4; j++) {
