@@ -253,3 +253,32 @@ def test_phase_timers_follow_the_reference_names():
     assert vals["excgMeta_time"] > 0 and vals["excgData_time"] + vals["SP_time"] > 0
     assert vals["replace_time"] == 0 and vals["orgData_time"] == 0      # pack / unpack / organise no longer exist
     comm.enable_trace(False)
+
+
+def test_functional_api_with_automatic_choice():
+    from rbruck_alltoallv_b200.ops import alltoallv as A
+    P, ts = 8, 2
+    comm = get_comm(P)
+    for hi in (40, 40000):                      # a latency-class and a bandwidth-class exchange
+        counts = dist.uniform(P, hi, seed=hi)
+        prob = oracle.make_problem(counts, ts, hi, packed=True)
+        send_h = oracle.fill_send(prob, hi)
+        want = oracle.expected_recv(prob, send_h)
+        send = [torch.from_numpy(b).cuda() for b in send_h]
+        recv = [comm.symm_empty(len(w), torch.uint8) for w in want]
+        for t in recv:
+            t.fill_(oracle.CANARY)
+        A.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, comm=comm, algo="auto",
+                    type_size=ts)
+        comm.check()
+        assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
+    # uniform helper
+    n = 100
+    send = [torch.arange(P * n, dtype=torch.int32, device="cuda") + 1000 * r for r in range(P)]
+    recv = [comm.symm_empty(P * n, torch.int32) for _ in range(P)]
+    A.alltoall(send, recv, n, comm=comm)
+    comm.check()
+    for d in range(P):
+        got = recv[d].cpu()
+        for s in range(P):
+            assert torch.equal(got[s * n:(s + 1) * n], torch.arange(d * n, (d + 1) * n, dtype=torch.int32) + 1000 * s)
