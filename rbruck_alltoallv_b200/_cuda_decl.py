@@ -56,6 +56,9 @@ def declare_cuda(lib):
     lib.rbv_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_set_nvls_meta.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+    lib.rbv_ctx_meta_bytes.restype = C.c_size_t
+    lib.rbv_ctx_meta_bytes.argtypes = [C.c_void_p]
     lib.rbv_ctx_set_eager.argtypes = [C.c_void_p, C.c_ulonglong]
     lib.rbv_ctx_set_cooperative.argtypes = [C.c_void_p, C.c_int]
     declare_moe(lib)

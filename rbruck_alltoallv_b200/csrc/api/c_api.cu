@@ -146,6 +146,12 @@ void rbv_prepared_free(rbv_ctx_t ctx, void* prepared) {
   ctx->c->release(*pc);
   delete pc;
 }
+int rbv_ctx_set_nvls_meta(rbv_ctx_t ctx, void* self_ptr, void* mc_ptr, size_t bytes) {
+  int rc = ctx->c->set_nvls_meta(self_ptr, mc_ptr, bytes);
+  if (rc) g_err = ctx->c->last_error();
+  return rc;
+}
+size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx) { return 2 * (size_t)ctx->c->layout().meta_bytes; }
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes) { ctx->eager = max_block_bytes; }
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on) { ctx->c->set_cooperative(on != 0); }

@@ -263,6 +263,8 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
     ka.heap[q] = peer_[q];
   }
   ka.host_status = host_status_dev_;
+  ka.meta_self = nvls_mc_ ? nvls_self_ : heap_ + lay_.meta_off;
+  ka.meta_mc = nvls_mc_;
   for (int lr = 0; lr < L_; lr++) {
     if (!eager && !in_heap(ca.recvbufs[lr], 1)) {
       last_error_ = "recvbuf must be allocated from the symmetric heap";
@@ -447,6 +449,16 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   return 0;
 }
 
+int Context::set_nvls_meta(void* self_ptr, void* mc_ptr, size_t bytes) {
+  if (!self_ptr || !mc_ptr) { nvls_self_ = nvls_mc_ = nullptr; nvls_bytes_ = 0; return 0; }
+  if (bytes < 2 * lay_.meta_bytes || (reinterpret_cast<uintptr_t>(self_ptr) & 15) || (reinterpret_cast<uintptr_t>(mc_ptr) & 15)) {
+    last_error_ = "NVLS metadata buffer too small or misaligned";
+    return RBV_ERR_BAD_ARG;
+  }
+  nvls_self_ = static_cast<char*>(self_ptr); nvls_mc_ = static_cast<char*>(mc_ptr); nvls_bytes_ = bytes;
+  return cudaMemset(nvls_self_, 0, 2 * lay_.meta_bytes) == cudaSuccess ? 0 : RBV_ERR_BAD_ARG;
+}
+
 StatusBlock Context::status(cudaStream_t stream) {
   cudaStreamSynchronize(stream);
   StatusBlock s = *host_status_;
@@ -461,6 +473,7 @@ cudaError_t Context::reset() {
   if (e != cudaSuccess) return e;
   e = cudaMemset(heap_, 0, lay_.stage_off);
   if (e != cudaSuccess) return e;
+  if (nvls_self_) cudaMemset(nvls_self_, 0, 2 * lay_.meta_bytes);
   for (auto& kv : plans_)
     if (kv.second->d_done) cudaMemset(kv.second->d_done, 0, kv.second->nops * sizeof(unsigned));
   std::memset(host_status_, 0, sizeof(StatusBlock));

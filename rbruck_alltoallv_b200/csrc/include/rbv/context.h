@@ -106,6 +106,9 @@ class Context {
   unsigned long long timeout_ns() const { return timeout_ns_; }
   // Fault injection for tests: the given local rank skips its metadata row in the next calls (-1: off).
   void set_absent_rank(int lr) { absent_rank_ = lr; }
+  // NVLS: metadata tables in an externally provided multicast-capable buffer (local address, multicast address,
+  // size).  Every process must set it, or none.  Null pointers switch back to the tables inside the heap.
+  int set_nvls_meta(void* self_ptr, void* mc_ptr, size_t bytes);
   const std::string& last_error() const { return last_error_; }
   const DevPlan* plan_for(const AlgoSpec& spec);
 
@@ -118,6 +121,9 @@ class Context {
   bool cooperative_ = true;
   bool trace_ = false;
   int absent_rank_ = -1;
+  char* nvls_self_ = nullptr;
+  char* nvls_mc_ = nullptr;
+  size_t nvls_bytes_ = 0;
   unsigned long long timeout_ns_ = 2000000000ull;
   int max_ctas_ = 1, sm_count_ = 1;
   StatusBlock* host_status_ = nullptr;

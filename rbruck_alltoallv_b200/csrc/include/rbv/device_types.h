@@ -127,6 +127,8 @@ struct KernelArgs {
   unsigned long long timeout_ns;
   HeapLayout lay;
   char* heap[kMaxProcs];   // heap base of every process as mapped in this process
+  char* meta_self;         // this process's metadata tables (both parities); normally heap[proc] + lay.meta_off
+  char* meta_mc;           // NVLS: multicast address of the same tables on ALL processes (null: peer stores)
   const char* sendbuf[kMaxRanks];         // per local rank (any device memory of this GPU)
   unsigned long long recvoff[kMaxRanks];  // per local rank: recvbuf offset in this process's heap
   unsigned long long sendcopy_off[kMaxRanks];  // CALL_INPLACE: private copy location (heap offset)

@@ -87,6 +87,12 @@ void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
                   int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes);
 int rbv_launch(rbv_ctx_t ctx, void* prepared, void* cuda_stream);
 void rbv_prepared_free(rbv_ctx_t ctx, void* prepared);
+/* NVLS: keep the metadata tables in a caller-provided buffer that is bound to an NVLink multicast object (local
+ * address, multicast address, at least rbv_ctx_meta_bytes() bytes, zero-filled); the metadata phase then publishes
+ * with one multimem.st per unit instead of one store per peer.  Collective: all processes or none. */
+int rbv_ctx_set_nvls_meta(rbv_ctx_t ctx, void* self_ptr, void* mc_ptr, size_t bytes);
+size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx);
+
 /* Protocol of the following calls: 0 = rendezvous (any size); > 0 = eager, for blocks of at most this many bytes
  * (every rank must pass the same value; needs (P + cells) * (16 + 2 * bytes) of staging arena per rank). */
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes);

@@ -54,6 +54,12 @@ __device__ __forceinline__ unsigned* cell_flag_of(const KernelArgs& a, int proc,
 __device__ __forceinline__ char* meta_of(const KernelArgs& a, int proc, int parity) {
   return a.heap[proc] + a.lay.meta_off + (size_t)parity * a.lay.meta_bytes;
 }
+// One store that NVSwitch replicates into the tables of every process (NVLS multicast mapping).
+__device__ __forceinline__ void st_unit_mc(uint4* mc, unsigned w0, unsigned w1, unsigned flag) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(mc), "f"(__uint_as_float(w0)), "f"(__uint_as_float(flag)), "f"(__uint_as_float(w1)),
+                 "f"(__uint_as_float(flag)) : "memory");
+}
 __device__ __forceinline__ char* stage_of(const KernelArgs& a, int proc, int parity, int lr) {
   return a.heap[proc] + a.lay.stage_off + (size_t)(lr * 2 + parity) * a.lay.arena_bytes;
 }
@@ -101,6 +107,27 @@ __device__ void publish_metadata(const KernelArgs& a, int parity, unsigned flag)
   const int P = a.P;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int* rc = in_recvcounts(a);
+  if (a.meta_mc) {
+    // NVLS: each local rank writes its rows once; the switch delivers them to every process
+    for (int lr = warp; lr < a.L; lr += nwarps) {
+      if (lr == a.absent_rank) continue;
+      const int me = a.proc * a.L + lr;
+      char* mt = a.meta_mc + (size_t)parity * a.lay.meta_bytes;
+      uint4* ct = reinterpret_cast<uint4*>(mt + meta_ct_off(P)) + (size_t)me * P;
+      uint4* rt = reinterpret_cast<uint4*>(mt + meta_rt_off(P)) + (size_t)me * P * 2;
+      uint4* ro = reinterpret_cast<uint4*>(mt + meta_ro_off(P)) + me;
+      const int* sc = in_sendcounts(a) + (size_t)lr * P;
+      const long long* rdi = in_rdispls(a) + (size_t)lr * P;
+      for (int i = lane; i < P; i += 32) {
+        const unsigned long long rd = (unsigned long long)rdi[i];
+        st_unit_mc(ct + i, (unsigned)sc[i], (unsigned)a.chunk_bytes, flag);
+        st_unit_mc(rt + 2 * i, rc ? (unsigned)rc[(size_t)lr * P + i] : 0xffffffffu, 0u, flag);
+        st_unit_mc(rt + 2 * i + 1, (unsigned)rd, (unsigned)(rd >> 32), flag);
+      }
+      if (lane == 0) st_unit_mc(ro, (unsigned)a.recvoff[lr], (unsigned)(a.recvoff[lr] >> 32), flag);
+    }
+    return;
+  }
   for (int pair = warp; pair < a.L * a.nproc; pair += nwarps) {
     const int lr = pair / a.nproc, q = pair % a.nproc;
     if (lr == a.absent_rank) continue;  // host-injected fault: the rank "never joins"
@@ -183,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   bool alive = true;
   int mx = 0;
   {
-    const char* mt = meta_of(a, a.proc, parity);
+    const char* mt = a.meta_self + (size_t)parity * a.lay.meta_bytes;
     const uint4* ct = reinterpret_cast<const uint4*>(mt + meta_ct_off(P));
     const uint4* rt = reinterpret_cast<const uint4*>(mt + meta_rt_off(P));
     const uint4* ro = reinterpret_cast<const uint4*>(mt + meta_ro_off(P));

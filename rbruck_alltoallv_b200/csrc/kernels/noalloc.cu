@@ -169,6 +169,8 @@ extern "C" int rbv_alltoallv_noalloc(int nranks, int type_size, const void* cons
   ka.lay.user_off = kTotal; ka.lay.total_bytes = kTotal;
   ka.heap[0] = reinterpret_cast<char*>(ds.base);
   ka.host_status = nullptr;
+  ka.meta_self = reinterpret_cast<char*>(ds.base) + kMetaOff;
+  ka.meta_mc = nullptr;
   for (int r = 0; r < P; r++) {
     ka.sendbuf[r] = static_cast<const char*>(sendbufs[r]);
     // receive buffers are addressed relative to the scratch base; the difference wraps modulo 2^64 and the

@@ -114,10 +114,41 @@ class Communicator:
             if rc:
                 raise CommError("cudaIpcOpenMemHandle failed: " + self._lib.rbv_last_error().decode())
             dist.barrier(group=self._side)
+        self.nvls = False
+        if self.nproc > 1 and os.environ.get("RBV_NVLS", "0") == "1":
+            self._enable_nvls()
         info = (C.c_longlong * 8)()
         self._lib.rbv_ctx_info(self._ctx, info)
         self.max_ctas = int(info[6])
         self.sm_count = int(info[7])
+
+    def _enable_nvls(self) -> None:
+        """Moves the metadata tables into a buffer bound to an NVLink multicast object (allocated and bound by
+        torch's symmetric-memory allocator), so that the metadata phase publishes with ``multimem.st``: NVSwitch
+        replicates one store into the tables of all GPUs.  Opt-in (``RBV_NVLS=1``) and kept off in fault tests: a
+        process that dies while its memory is bound to a multicast object disturbs the other GPUs."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            nbytes = max(int(self._lib.rbv_ctx_meta_bytes(self._ctx)), 4096)
+            buf = symm.empty(nbytes, dtype=torch.uint8, device=f"cuda:{self.device}")
+            hdl = symm.rendezvous(buf, group=self._dist.group.WORLD)
+            mc = int(hdl.multicast_ptr) if hdl.has_multicast_support else 0
+        except Exception:   # no multicast support on this system / build
+            mc, buf, hdl = 0, None, None
+        flag = torch.tensor([1 if mc else 0], dtype=torch.int64)
+        self._dist.all_reduce(flag, op=self._dist.ReduceOp.MIN, group=self._side)
+        if int(flag.item()) == 0:
+            return
+        buf.zero_()
+        torch.cuda.synchronize(self.device)
+        self._dist.barrier(group=self._side)
+        rc = self._lib.rbv_ctx_set_nvls_meta(self._ctx, C.c_void_p(buf.data_ptr()), C.c_void_p(mc), nbytes)
+        if rc:
+            raise CommError("NVLS metadata setup failed: " + self._lib.rbv_last_error().decode())
+        torch.cuda.synchronize(self.device)
+        self._dist.barrier(group=self._side)
+        self._nvls_keep = (buf, hdl)
+        self.nvls = True
 
     # ---- life cycle -------------------------------------------------------------------------
     def close(self):

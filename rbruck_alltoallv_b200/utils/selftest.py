@@ -129,7 +129,8 @@ def main() -> int:
         failures = int(f.item())
     rows = bench(comm) if args.bench and failures == 0 else None
     if comm.proc == 0:
-        line = {"selftest": "ok" if failures == 0 else "FAILED", "failures": failures, "P": comm.P, "gpus": comm.nproc}
+        line = {"selftest": "ok" if failures == 0 else "FAILED", "failures": failures, "P": comm.P, "gpus": comm.nproc,
+                "nvls_metadata": bool(comm.nvls)}
         if rows is not None:
             line["bench"] = rows
         print(json.dumps(line), flush=True)

@@ -56,3 +56,14 @@ def test_fft_transposes_two_processes(pr, pc):
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert '"check": "ok"' in res.stdout
+
+
+@pytest.mark.skipif(_ngpus() < 2 or os.environ.get("RBV_TEST_NVLS") != "1",
+                    reason="needs 2 GPUs and RBV_TEST_NVLS=1 (binds memory to an NVLink multicast object)")
+def test_nvls_metadata_two_processes():
+    env = dict(os.environ, PYTHONPATH=ROOT, RBV_NVLS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29671", "-m", "rbruck_alltoallv_b200.utils.selftest"]
+    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert '"selftest": "ok"' in res.stdout and '"nvls_metadata": true' in res.stdout
