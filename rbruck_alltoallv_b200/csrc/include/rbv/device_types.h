@@ -13,8 +13,8 @@
 //
 // Cross-rank synchronisation uses monotonic counters and sequence-stamped flags only, so nothing
 // has to be reset between calls:
-//   * meta_arrivals[parity]      += 1 per published metadata row      (target: calls_on_parity * P)
-//   * recv_arrivals[local rank]  += 1 per block landed in recvbuf      (target: (seq + 1) * P)
+//   * metadata table units and eager cell units carry the call number in their flag words
+//   * recv_arrivals[local rank]  += 1 per chunk landed in recvbuf; the owner keeps the running target
 //   * cell_flag[parity][lr][c]    = seq + 1 when staging cell c holds this call's block
 // Staging arenas, cell flags and metadata tables alternate by call parity: a peer can run at most
 // one call ahead (it cannot finish call c+1 without data this rank sends in call c+1), so two
@@ -54,7 +54,6 @@ struct StatusBlock {
 
 // Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.
 struct CtrlBlock {
-  unsigned long long meta_arrivals[2];
   unsigned long long recv_arrivals[kMaxRanks];   // += 1 per chunk landed in a local rank's recvbuf
   unsigned long long recv_target[kMaxRanks];     // running total of chunks expected so far (kept by the owner)
   unsigned int abort_flag;       // set locally on error, and by peers that want everyone to stop
