@@ -13,7 +13,7 @@ def __getattr__(name):
     if name in ("Communicator", "init", "get_default_comm"):
         from .parallel import comm as _c
         return getattr(_c, name)
-    if name in ("alltoallv", "alltoall", "nccl_alltoallv"):
+    if name in ("alltoallv", "alltoall", "nccl_alltoallv", "prepare"):
         from .ops import alltoallv as _a
         return getattr(_a, name)
     raise AttributeError(name)

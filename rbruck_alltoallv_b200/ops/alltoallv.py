@@ -17,27 +17,58 @@ from ..parallel import comm as _comm
 from ..parallel import tuner as _tuner
 
 
+def _auto_choice(c, recv, sendcounts, kw, agree_on_max: bool):
+    """Resolves ``algo="auto"`` into keyword arguments for the communicator, using the tuner table."""
+    ts = kw.get("type_size") or (recv.element_size() if isinstance(recv, torch.Tensor) else recv[0].element_size())
+    host_counts = not (isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda)
+    if host_counts:
+        mean_block = float(np.mean(np.asarray(sendcounts))) * ts
+    else:
+        hint = kw.get("bytes_hint", -1)
+        mean_block = hint / (c.L * c.P) if hint and hint > 0 else 64 << 10
+    choice = _tuner.choose(c.P, c.nproc, mean_block)
+    out = dict(kw)
+    out["algo"] = choice.pop("algo")
+    protocol = choice.pop("protocol", "rendezvous")
+    # The eager protocol needs one cell size on all ranks: either the caller promises an upper bound
+    # (``max_block_bytes=``) or, where a collective host reduction is affordable, the ranks agree on the maximum.
+    emax = out.pop("max_block_bytes", 0)
+    if protocol == "eager" and "eager_max_bytes" not in out:
+        if not emax and agree_on_max and host_counts:
+            emax = c.max_block_bytes(sendcounts, ts)
+        if 0 < emax <= (256 << 10) and (c.P + 64) * (2 * emax + 16) <= c.arena_bytes:
+            out["eager_max_bytes"] = int(emax)
+    for k, v in choice.items():
+        out.setdefault(k, v)
+    return out
+
+
 def alltoallv(send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, comm=None,
               algo: str = "auto", **kw) -> None:
+    """One-shot call.  With ``algo="auto"`` the tuner picks algorithm, radix and batch; the low-latency eager
+    protocol is used only when the caller bounds the block size with ``max_block_bytes=`` (a one-shot call does
+    not pay for a host-side reduction; :func:`prepare` does)."""
     c = comm or _comm.get_default_comm()
     if algo == "auto":
-        ts = kw.get("type_size") or (recv.element_size() if isinstance(recv, torch.Tensor) else recv[0].element_size())
-        if isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda:
-            hint = kw.get("bytes_hint", -1)
-            mean_block = hint / (c.L * c.P) if hint and hint > 0 else 64 << 10
-        else:
-            mean_block = float(np.mean(np.asarray(sendcounts))) * ts
-        choice = _tuner.choose(c.P, c.nproc, mean_block)
-        algo = choice.pop("algo")
-        protocol = choice.pop("protocol", "rendezvous")
-        host_counts = not (isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda)
-        if protocol == "eager" and host_counts and "eager_max_bytes" not in kw:
-            emax = c.max_block_bytes(sendcounts, ts)       # collective: agrees on the cell size
-            if 0 < emax <= (256 << 10) and (c.P + 64) * (2 * emax + 16) <= c.arena_bytes:
-                kw["eager_max_bytes"] = emax
-        for k, v in choice.items():
-            kw.setdefault(k, v)
+        kw = _auto_choice(c, recv, sendcounts, kw, agree_on_max=False)
+        algo = kw.pop("algo")
+    else:
+        kw.pop("max_block_bytes", None)
     c.alltoallv(send, recv, sendcounts, sdispls, recvcounts, rdispls, algo=algo, **kw)
+
+
+def prepare(send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, comm=None, algo: str = "auto",
+            **kw):
+    """Persistent call (``.launch()`` repeats it).  ``algo="auto"`` resolves algorithm AND protocol once, including
+    the collective agreement on the eager cell size.  Collective over the processes when counts are on the host."""
+    c = comm or _comm.get_default_comm()
+    if algo == "auto":
+        kw = _auto_choice(c, recv, sendcounts, kw, agree_on_max=True)
+        algo = kw.pop("algo")
+    else:
+        kw.pop("max_block_bytes", None)
+    kw.pop("stream", None)
+    return c.prepare(send, recv, sendcounts, sdispls, recvcounts, rdispls, algo=algo, **kw)
 
 
 def alltoall(send, recv, count: int, *, comm=None, algo: str = "auto", **kw) -> None:

@@ -272,6 +272,14 @@ def test_functional_api_with_automatic_choice():
                     type_size=ts)
         comm.check()
         assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
+        for t in recv:
+            t.fill_(oracle.CANARY)
+        call = A.prepare(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, comm=comm, algo="auto",
+                         type_size=ts)
+        call.launch()
+        call.launch()
+        comm.check()
+        assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
     # uniform helper
     n = 100
     send = [torch.arange(P * n, dtype=torch.int32, device="cuda") + 1000 * r for r in range(P)]
