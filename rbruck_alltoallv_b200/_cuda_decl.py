@@ -17,7 +17,7 @@ class Box(C.Structure):
 
 
 STATUS_NAMES = {0: "ok", 1: "timeout", 2: "bad_argument", 3: "staging_capacity", 4: "truncate", 5: "aborted"}
-SITE_NAMES = {0: "-", 1: "metadata", 2: "staging_cell", 3: "final_arrival"}
+SITE_NAMES = {0: "-", 1: "metadata", 2: "staging_cell", 3: "final_arrival", 4: "bulk_copy"}
 
 
 def declare_cuda(lib):
@@ -56,6 +56,7 @@ def declare_cuda(lib):
     lib.rbv_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_set_bulk.argtypes = [C.c_void_p, C.c_int]
     lib.rbv_ctx_set_nvls_meta.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
     lib.rbv_ctx_meta_bytes.restype = C.c_size_t
     lib.rbv_ctx_meta_bytes.argtypes = [C.c_void_p]

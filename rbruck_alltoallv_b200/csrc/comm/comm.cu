@@ -38,6 +38,8 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   RBV_CUDA_THROW(a2av_configure(P, &per_sm));
   per_sm = std::max(1, std::min(per_sm, 2));
   max_ctas_ = sm_count_ * per_sm;
+  bulk_ctas_ = sm_count_ * std::max(0, std::min(a2av_bulk_ctas_per_sm(P), 1));
+  if (const char* e = std::getenv("RBV_BULK")) bulk_mode_ = std::atoi(e);
   if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_ = std::atoi(e) != 0;
 
   lay_.ctrl_off = 0;
@@ -382,25 +384,48 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   unsigned long long chunk = opt.chunk_bytes;
   int grid = opt.grid;
   const int warps_per_cta = kThreads / 32;
+  // Bulk-copy engine: worth its shared memory (one CTA per SM) once every warp has at least 16 KB to move.  Its
+  // loads must read this GPU's own memory, so send buffers in host memory keep the vector path.
+  bool bulk = false;
+  if (!eager && bulk_mode_ != 0 && bulk_ctas_ > 0) {
+    const bool want = bulk_mode_ > 0 || (work >= 0 && work / (1.0 * bulk_ctas_ * warps_per_cta) >= 16.0 * 1024);
+    if (want) {
+      bulk = true;
+      for (int lr = 0; lr < L_ && bulk && !inplace; lr++) {
+        cudaPointerAttributes at;
+        if (cudaPointerGetAttributes(&at, ca.sendbufs[lr]) != cudaSuccess || at.type != cudaMemoryTypeDevice ||
+            at.device != device_) {
+          (void)cudaGetLastError();
+          bulk = false;
+        }
+      }
+    }
+  }
+  const int max_ctas = bulk ? bulk_ctas_ : max_ctas_;
+  if (bulk) ka.flags |= CALL_BULK;
   if (!chunk) {
     if (work < 0) chunk = 32 << 10;
     else {
-      // a chunk is one warp's unit of work: about one chunk per resident warp, within [2 KB, 64 KB].  Measured
-      // on B200: with fewer, larger chunks most warps idle and a 4 MB exchange takes twice as long.
-      double c = work / (1.0 * max_ctas_ * warps_per_cta);
-      chunk = (unsigned long long)std::min(64.0 * 1024, std::max(2.0 * 1024, c));
-      chunk = align_up(chunk, 1024);
+      // a chunk is one warp's unit of work, at most 64 KB and at least 2 KB.  Chunks are dealt to the resident
+      // warps in turn, so the byte count is cut into a whole number of rounds: with 64 KB chunks and 1.8 rounds,
+      // a tenth of the warps would work alone at the end.  Measured on B200: with fewer, larger chunks most warps
+      // idle and a 4 MB exchange takes twice as long.
+      const double warps = 1.0 * max_ctas * warps_per_cta;
+      const double rounds = std::max(1.0, std::ceil(work / (warps * 64.0 * 1024)));
+      const double c = work / (warps * rounds);
+      chunk = (unsigned long long)std::min(64.0 * 1024, std::max(bulk ? 4.0 * 1024 : 2.0 * 1024, c));
+      chunk = align_up(chunk, bulk ? 4096 : 1024);
     }
   }
   chunk = align_up(chunk, 16);
   if (grid <= 0) {
-    if (work < 0) grid = max_ctas_;
+    if (work < 0) grid = max_ctas;
     else {
       double chunks = work / (double)chunk + dp->nops;
-      grid = (int)std::min<double>(max_ctas_, std::max<double>(1.0, std::ceil(chunks / warps_per_cta)));
+      grid = (int)std::min<double>(max_ctas, std::max<double>(1.0, std::ceil(chunks / warps_per_cta)));
     }
   }
-  grid = std::max(1, std::min(grid, max_ctas_));
+  grid = std::max(1, std::min(grid, max_ctas));
   ka.chunk_bytes = chunk;
   out->grid = grid;
   out->eager = eager;

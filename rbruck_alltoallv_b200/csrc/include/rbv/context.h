@@ -96,6 +96,10 @@ class Context {
   void set_cooperative(bool on) { cooperative_ = on; }
   // Copy the phase time stamps to the host after every call (off: only failing calls report).
   void set_trace(bool on) { trace_ = on; }
+  // Bulk-copy engine for large chunks: 0 = never (default), 1 = whenever the buffers allow it, -1 = by size
+  // (16 KB or more per warp).  Measured on B200 it moves data as fast as the vector path (same HBM copy rate
+  // on one GPU, 0.97x over NVLink at 128 MB blocks), so it is an option rather than the default.
+  void set_bulk(int mode) { bulk_mode_ = mode; }
 
   // First error since the last status() call (0 if none); synchronises `stream` first.
   StatusBlock status(cudaStream_t stream);
@@ -120,6 +124,8 @@ class Context {
   bool opened_[kMaxProcs] = {};
   bool cooperative_ = true;
   bool trace_ = false;
+  int bulk_mode_ = 0;
+  int bulk_ctas_ = 0;
   int absent_rank_ = -1;
   char* nvls_self_ = nullptr;
   char* nvls_mc_ = nullptr;
@@ -147,6 +153,8 @@ class Context {
 
 // implemented in kernels/a2av_kernel.cu
 size_t a2av_smem_bytes(int P);
+size_t a2av_smem_bytes_bulk(int P);
+int a2av_bulk_ctas_per_sm(int P);
 cudaError_t a2av_configure(int P, int* max_ctas_per_sm);
 cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream);
 // implemented in kernels/a2av_eager.cu

@@ -41,7 +41,7 @@ enum Status : int {
   RBV_ERR_ABORTED = 5,    // another rank reported an error and asked everyone to stop
 };
 
-enum WaitSite : int { WAIT_META = 1, WAIT_CELL = 2, WAIT_RECV = 3 };
+enum WaitSite : int { WAIT_META = 1, WAIT_CELL = 2, WAIT_RECV = 3, WAIT_BULK = 4 };
 
 struct StatusBlock {
   int code;        // Status of the first error of the most recent call, 0 if none
@@ -49,7 +49,8 @@ struct StatusBlock {
   int detail0;     // op index / local rank / cell, depending on site
   int detail1;     // peer rank or expected count
   unsigned long long trace[8];  // %globaltimer stamps of CTA 0: 0 start, 1 metadata published,
-                                // 2 metadata complete, 3 own ops issued, 4 all blocks received
+                                // 2 metadata complete, 3 own ops issued, 4 all blocks received,
+                                // 5 / 6 before and after the fence that precedes the arrival report, 7 arrivals reported
 };
 
 // Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.
@@ -103,6 +104,7 @@ enum CallFlags : unsigned {
   CALL_META_INLINE = 2u,  // counts/displacements are in KernelArgs::inl, not behind the pointers
   CALL_TRACE = 4u,        // copy the status block (with the phase time stamps) to the host after every call,
                           // not only after a failing one
+  CALL_BULK = 8u,         // large aligned chunks go through the bulk-copy engine (shared-memory ring per warp)
 };
 
 struct InlineMeta {

@@ -97,6 +97,7 @@ size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx);
  * (every rank must pass the same value; needs (P + cells) * (16 + 2 * bytes) of staging arena per rank). */
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes);
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on);       /* report phase time stamps after every call */
+void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode);      /* bulk-copy engine for large chunks: 0 off (default), 1 on, -1 by size */
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on); /* cooperative (default) or plain kernel launches */
 
 /* Phase timers of the most recent call, filled by rbv_update_timers() (which synchronises;

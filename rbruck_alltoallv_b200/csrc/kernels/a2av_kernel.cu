@@ -24,6 +24,7 @@
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
+#include "kernels/bulk_copy.cuh"
 #include "kernels/primitives.cuh"
 #include "rbv/device_types.h"
 
@@ -34,6 +35,9 @@ namespace rbv {
 namespace {
 
 constexpr int kOpTile = 1024;
+
+// Tiles per warp of the bulk-copy ring: three where the tables of the communicator leave room in shared memory.
+__host__ __device__ constexpr int a2av_bulk_stages(int P) { return P <= 16 ? 3 : 2; }
 
 struct Smem {
   int* counts;
@@ -159,6 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   __shared__ int s_flag;
   __shared__ unsigned s_total;
   __shared__ unsigned s_seq;
+  __shared__ unsigned s_arrived[kMaxRanks];   // chunks this CTA delivered to each rank's receive buffer, not yet reported
   const int P = a.P, L = a.L, ts = a.type_size;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned warps_per_cta = blockDim.x >> 5;
@@ -168,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   dev::WaitCfg wc{&my->abort_flag, a.timeout_ns};
 
   Smem sm;
+  unsigned char* bulk_region;
   {
     unsigned char* p = smem_raw;
     sm.rdispl = reinterpret_cast<long long*>(p); p += 8ull * P * P;
@@ -175,9 +181,14 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     sm.counts = reinterpret_cast<int*>(p); p += 4ull * P * P;
     sm.caps = reinterpret_cast<int*>(p); p += 4ull * P * P;
     sm.schunk = reinterpret_cast<unsigned*>(p); p += 4ull * P;
-    sm.prefix = reinterpret_cast<unsigned*>(p);
+    sm.prefix = reinterpret_cast<unsigned*>(p); p += 4ull * (kOpTile + 1);
+    bulk_region = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(p) + 127) & ~uintptr_t(127));
   }
+  const bool bulk = (a.flags & CALL_BULK) != 0;
+  dev::BulkPipe bp{0u, 0u, 0u, 2u};
+  if (bulk) dev::bulk_pipe_init(bp, bulk_region, warp, (int)warps_per_cta, lane, a2av_bulk_stages(P));   // published by the barrier below
 
+  if (tid < kMaxRanks) s_arrived[tid] = 0;
   if (tid == 0) {
     s_seq = __ldcg(&my->call_seq);
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
@@ -360,14 +371,30 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
           dst = a.heap[dproc] + sm.recvoff[o.dst] + (size_t)sm.rdispl[(size_t)o.dst * P + o.origin] * ts;
         else
           dst = stage_of(a, dproc, parity, ldst) + (size_t)o.dst_cell * stride;
-        dev::group_copy(dst + off, src + off, len, lane, 32);
+        if (bulk && len >= dev::kBulkMinBytes &&
+            ((reinterpret_cast<uintptr_t>(dst + off) | reinterpret_cast<uintptr_t>(src + off)) & 15u) == 0) {
+          // one thread drives the copy engine; a tail shorter than 16 bytes goes through the vector path
+          const size_t body = len & ~(size_t)15;
+          int r = 0;
+          if (lane == 0) {
+            r = dev::bulk_copy(dst + off, src + off, body, bp, wc);
+            if (r == dev::WAIT_TIMEOUT) report_error(a, RBV_ERR_TIMEOUT, WAIT_BULK, t0 + oi, (int)k);
+          }
+          r = __shfl_sync(0xffffffffu, r, 0);
+          if (r != dev::WAIT_OK) { ok = false; alive = false; }
+          else if (len > body) dev::group_copy(dst + off + body, src + off + body, len - body, lane, 32);
+        } else {
+          dev::group_copy(dst + off, src + off, len, lane, 32);
+        }
       }
       __syncwarp();
-      // completion.  Final hops: every chunk reports to the receiver, which knows how many to expect.
-      // Staging cells: the warp that finishes the last chunk of the op raises the cell's flag.
+      // completion.  Final hops: every chunk counts towards the receiver's arrival counter (the receiver knows
+      // how many to expect); nobody looks at that counter before the end of the call, so the chunks are tallied
+      // per CTA and reported once per op tile, which spares a fence and a remote atomic per chunk.
+      // Staging cells: the warp that finishes the last chunk of the op raises the cell's flag at once.
       if (lane == 0) {
         if (o.dst_cell < 0) {
-          dev::signal_add(&ctrl_of(a, dproc)->recv_arrivals[ldst], 1ull, remote);
+          atomicAdd(&s_arrived[o.dst], 1u);
         } else {
           bool last = true;
           if (nch > 1) {
@@ -380,8 +407,21 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
         }
       }
     }
+    // this warp's stores are performed before the CTA reports them
+    __syncwarp();
     base += total;
     __syncthreads();
+    if (blockIdx.x == 0 && tid == 0) my->status.trace[5] = dev::globaltimer();
+    if (tid < P) {
+      const unsigned n = atomicExch(&s_arrived[tid], 0u);
+      const int dproc = tid / L;
+      const bool far = dproc != a.proc;
+      // the barrier above orders every warp's stores before this fence, which publishes them (cumulativity)
+      if (n) dev::fence_acq_rel(far);
+      if (blockIdx.x == 0 && tid == 0) my->status.trace[6] = dev::globaltimer();
+      if (n) dev::red_relaxed_add(&ctrl_of(a, dproc)->recv_arrivals[tid - dproc * L], (unsigned long long)n, far);
+    }
+    if (blockIdx.x == 0 && tid == 0) my->status.trace[7] = dev::globaltimer();
   }
 
   // ---- (3) completion ----
@@ -415,12 +455,17 @@ size_t a2av_smem_bytes(int P) {
   return 8ull * P * P + 8ull * P + 4ull * P * P * 2 + 4ull * P + 4ull * (kOpTile + 1) + 16;
 }
 
+// Dynamic shared memory of a launch that uses the bulk-copy engine: the tables plus one tile ring per warp.
+size_t a2av_smem_bytes_bulk(int P) {
+  return a2av_smem_bytes(P) + 128 + dev::bulk_smem_bytes(kThreads / 32, a2av_bulk_stages(P));
+}
+
 cudaError_t a2av_configure(int P, int* max_ctas_per_sm) {
   size_t smem = a2av_smem_bytes(P);
   // The attribute belongs to the kernel, not to a context: size it for the largest communicator so
   // that contexts with different rank counts can coexist in one process.
   cudaError_t e = cudaFuncSetAttribute(a2av_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)a2av_smem_bytes(kMaxRanks));
+                                       (int)a2av_smem_bytes_bulk(kMaxRanks));
   if (e != cudaSuccess) return e;
   int nb = 0;
   e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, a2av_kernel, kThreads, smem);
@@ -428,13 +473,21 @@ cudaError_t a2av_configure(int P, int* max_ctas_per_sm) {
   return e;
 }
 
+int a2av_bulk_ctas_per_sm(int P) {
+  int nb = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, a2av_kernel, kThreads, a2av_smem_bytes_bulk(P)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return nb;
+}
+
 cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream) {
   void* params[] = {(void*)&args};
+  const size_t smem = (args.flags & CALL_BULK) ? a2av_smem_bytes_bulk(args.P) : a2av_smem_bytes(args.P);
   if (cooperative)
-    return cudaLaunchCooperativeKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params,
-                                       a2av_smem_bytes(args.P), stream);
-  return cudaLaunchKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params, a2av_smem_bytes(args.P),
-                          stream);
+    return cudaLaunchCooperativeKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params, smem, stream);
+  return cudaLaunchKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params, smem, stream);
 }
 
 }  // namespace rbv

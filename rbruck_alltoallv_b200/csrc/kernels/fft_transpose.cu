@@ -107,8 +107,9 @@ __global__ void __launch_bounds__(kThreadsT) transpose_exchange_kernel(const __g
     if (atomicAdd(&my->aux_exit[2], 1u) == gridDim.x - 1) {
       my->aux_exit[2] = 0;
       const unsigned seq = my->aux_seq[2];
+      dev::fence_acq_rel(a.nproc > 1);   // one fence publishes every CTA's tiles (each fenced before its exit count)
       for (int q = 0; q < a.nproc; q++)
-        dev::signal_add(&reinterpret_cast<CtrlBlock*>(a.heap[q] + a.ctrl_off)->aux_arrivals[2], 1ull, q != a.proc);
+        dev::red_relaxed_add(&reinterpret_cast<CtrlBlock*>(a.heap[q] + a.ctrl_off)->aux_arrivals[2], 1ull, q != a.proc);
       dev::WaitCfg wc{&my->abort_flag, a.timeout_ns};
       const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)a.nproc;
       if (dev::wait_ge(&my->aux_arrivals[2], target, wc, a.nproc > 1) != dev::WAIT_OK) atomicCAS(a.error, 0, 1);

@@ -6,8 +6,9 @@
 // These blocks do not match the 32-element hardware scaling of the MX instruction kinds, so scaling is done in
 // software: every K block (128 fp8 = one 128-byte swizzle row) is multiplied on its own by four
 // tcgen05.mma.kind::f8f6f4 (K = 32) into one of four 128-column TMEM slots; the four epilogue warps pull each
-// finished slot with tcgen05.ld (eight warps: two per TMEM lane quarter, 64 columns each), hand the slot back as
-// soon as it sits in registers, then scale and accumulate (64 fp32 per thread).  MMA of block kb + 1..3 overlaps the scaling of block kb.
+// finished slot with tcgen05.ld (eight warps: two per TMEM lane quarter, 64 columns each, loaded as two pipelined
+// halves), hand the slot back as soon as it sits in registers, and scale and accumulate with packed fp32 FMAs
+// (64 fp32 per thread; scales prefetched four K blocks ahead).  MMA of block kb + 1..3 overlaps the scaling of block kb.
 // Same structure as the bf16 kernel otherwise: TMA producer warp (plain tiled loads, no multicast), one MMA
 // thread, persistent static tile schedule over ragged groups, bounded waits.  No counterpart in the reference.
 #include <cuda.h>
@@ -157,33 +158,63 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
     for (int t = blockIdx.x; ok; t += gridDim.x) {
       const Tile tl = tile_of(p, t, s_rows, s_start);
       if (!tl.valid) break;
-      float acc[HN];
+      float2 acc2[HN / 2];
       #pragma unroll
-      for (int j = 0; j < HN; j++) acc[j] = 0.0f;
+      for (int j = 0; j < HN / 2; j++) acc2[j] = make_float2(0.0f, 0.0f);
       const long long arow = (long long)tl.m0 + row;
       const bool in_a = arow < p.a_rows;
       const float* sb = p.b_scale + ((size_t)tl.g * (p.N / 128) + tl.n0 / 128) * nkb;
-      float sa_next = in_a ? __ldg(p.a_scale + arow) : 0.0f;
-      for (int kb = 0; kb < nkb && ok; kb++, it++) {
-        const int slot = it % SLOTS;
-        const float scale = sa_next * __ldg(sb + kb);
-        if (kb + 1 < nkb) sa_next = in_a ? __ldg(p.a_scale + (size_t)(kb + 1) * p.a_rows + arow) : 0.0f;
-        if (!mbar_wait(&tfull_bar[slot], (it / SLOTS) & 1u, abort_flag)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)slot * BN + (uint32_t)half * HN;
-        // both 32-column loads are in flight before the first multiply-add
-        uint32_t r0[32], r1[32];
-        tmem_ld32(taddr, r0);
-        tmem_ld32(taddr + 32, r1);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty_bar[slot]);   // the slot is free as soon as it sits in registers
-        #pragma unroll
-        for (int j = 0; j < 32; j++) acc[j] = fmaf(scale, __uint_as_float(r0[j]), acc[j]);
-        #pragma unroll
-        for (int j = 0; j < 32; j++) acc[32 + j] = fmaf(scale, __uint_as_float(r1[j]), acc[32 + j]);
+      const float* sa = p.a_scale + (in_a ? arow : 0);
+      // Scales are fetched kDepth K blocks ahead, so that their L2 latency never sits between a finished MMA
+      // and its scaling.
+      constexpr int kDepth = 4;
+      float sa_q[kDepth], sb_q[kDepth];
+      #pragma unroll
+      for (int j = 0; j < kDepth; j++) {
+        sa_q[j] = (j < nkb) ? __ldg(sa + (size_t)j * p.a_rows) : 0.0f;
+        sb_q[j] = (j < nkb) ? __ldg(sb + j) : 0.0f;
       }
+      // Two 32-column loads per K block, software-pipelined: while one half is multiplied, the other half (or
+      // the first half of the next K block) is in flight from TMEM.
+      uint32_t r0[32], r1[32];
+      const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)half * HN;
+      if (!mbar_wait(&tfull_bar[it % SLOTS], (it / SLOTS) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      tmem_ld32(tbase + (uint32_t)(it % SLOTS) * BN, r0);
+      for (int kb0 = 0; kb0 < nkb && ok; kb0 += kDepth) {
+        #pragma unroll
+        for (int j = 0; j < kDepth; j++) {
+          const int kb = kb0 + j;
+          if (kb >= nkb) break;
+          const int slot = it % SLOTS;
+          const float scale = in_a ? sa_q[j] * sb_q[j] : 0.0f;
+          const float2 s2 = make_float2(scale, scale);
+          if (kb + kDepth < nkb) {
+            sa_q[j] = __ldg(sa + (size_t)(kb + kDepth) * p.a_rows);
+            sb_q[j] = __ldg(sb + kb + kDepth);
+          }
+          tmem_ld_wait();                                            // first half of this K block has landed
+          tmem_ld32(tbase + (uint32_t)slot * BN + 32, r1);
+          #pragma unroll
+          for (int c = 0; c < 16; c++)
+            acc2[c] = __ffma2_rn(s2, make_float2(__uint_as_float(r0[2 * c]), __uint_as_float(r0[2 * c + 1])), acc2[c]);
+          tmem_ld_wait();                                            // second half has landed
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[slot]);             // the slot is free once it sits in registers
+          it++;
+          if (kb + 1 < nkb) {
+            if (!mbar_wait(&tfull_bar[it % SLOTS], (it / SLOTS) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            tmem_ld32(tbase + (uint32_t)(it % SLOTS) * BN, r0);
+          }
+          #pragma unroll
+          for (int c = 0; c < 16; c++)
+            acc2[16 + c] =
+                __ffma2_rn(s2, make_float2(__uint_as_float(r1[2 * c]), __uint_as_float(r1[2 * c + 1])), acc2[16 + c]);
+        }
+      }
+      const float* acc = reinterpret_cast<const float*>(acc2);
       if (!ok) break;
       if (row < tl.rows_left) {
         __nv_bfloat16* crow = C + (size_t)(tl.m0 + row) * p.ldc;

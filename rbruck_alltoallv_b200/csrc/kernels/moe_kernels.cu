@@ -170,7 +170,8 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
     if (atomicAdd(&my->aux_exit[0], 1u) == gridDim.x - 1) {
       my->aux_exit[0] = 0;
       const unsigned seq = my->aux_seq[0];
-      for (int q = 0; q < c.nproc; q++) dev::signal_add(&ctrl_of(c, q)->aux_arrivals[0], 1ull, q != c.proc);
+      dev::fence_acq_rel(c.nproc > 1);   // one fence publishes every CTA's rows (each fenced before its exit count)
+      for (int q = 0; q < c.nproc; q++) dev::red_relaxed_add(&ctrl_of(c, q)->aux_arrivals[0], 1ull, q != c.proc);
       dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
       const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
       if (dev::wait_ge(&my->aux_arrivals[0], target, wc, c.nproc > 1) != dev::WAIT_OK) moe_fail(c, 1, 0);
@@ -208,8 +209,10 @@ __global__ void __launch_bounds__(kMoeThreads) moe_combine_kernel(const __grid_c
   CtrlBlock* my = ctrl_of(c, c.proc);
   if (threadIdx.x == 0) {
     const unsigned seq = __ldcg(&my->aux_seq[1]);
-    if (blockIdx.x == 0)
-      for (int q = 0; q < c.nproc; q++) dev::signal_add(&ctrl_of(c, q)->aux_arrivals[1], 1ull, q != c.proc);
+    if (blockIdx.x == 0) {
+      dev::fence_acq_rel(c.nproc > 1);
+      for (int q = 0; q < c.nproc; q++) dev::red_relaxed_add(&ctrl_of(c, q)->aux_arrivals[1], 1ull, q != c.proc);
+    }
     dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
     const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
     int r = dev::wait_ge(&my->aux_arrivals[1], target, wc, c.nproc > 1);

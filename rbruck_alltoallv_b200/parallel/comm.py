@@ -100,6 +100,7 @@ class Communicator:
         if not self._ctx:
             raise CommError("context creation failed: " + self._lib.rbv_last_error().decode())
         self._lib.rbv_ctx_set_timeout_ms(self._ctx, float(timeout_ms))
+        self._bulk = int(os.environ.get("RBV_BULK", "0"))
         self._side = None
         if self.nproc > 1:
             self._side = dist.new_group(backend="gloo")
@@ -241,7 +242,8 @@ class Communicator:
                   sendcounts, sdispls=None, recvcounts=None, rdispls=None, *, algo: str = "spreadout",
                   n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0, type_size: Optional[int] = None,
                   inplace: bool = False, grid: int = 0, chunk_bytes: int = 0, bytes_hint: int = -1,
-                  eager_max_bytes: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+                  eager_max_bytes: int = 0, bulk: Optional[int] = None,
+                  stream: Optional[torch.cuda.Stream] = None) -> None:
         """Non-uniform all-to-all of the L local ranks (asynchronous on the current stream).
 
         ``send`` / ``recv`` are one tensor per local rank (a bare tensor when L == 1); ``recv`` must come
@@ -280,6 +282,7 @@ class Communicator:
         st = stream or torch.cuda.current_stream(self.device)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
         self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
+        self._lib.rbv_ctx_set_bulk(self._ctx, int(self._bulk if bulk is None else bulk))
         rcode = self._lib.rbv_alltoallv(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
                                         1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
                                         int(chunk_bytes), C.c_void_p(st.cuda_stream))
@@ -322,7 +325,7 @@ class Communicator:
     def prepare(self, send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None, *,
                 algo: str = "spreadout", n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0,
                 type_size: Optional[int] = None, inplace: bool = False, grid: int = 0, chunk_bytes: int = 0,
-                bytes_hint: int = -1, eager_max_bytes: int = 0) -> "PreparedCall":
+                bytes_hint: int = -1, eager_max_bytes: int = 0, bulk: Optional[int] = None) -> "PreparedCall":
         """Persistent form of :meth:`alltoallv` (compare ``MPI_Alltoallv_init``): everything is resolved once;
         ``.launch()`` then costs one kernel launch.  Buffers and counts are fixed (device-resident counts are
         re-read by every launch, so a router may still change their values)."""
@@ -330,6 +333,7 @@ class Communicator:
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
         self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
+        self._lib.rbv_ctx_set_bulk(self._ctx, int(self._bulk if bulk is None else bulk))
         h = self._lib.rbv_prepare(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
                                   1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
                                   int(chunk_bytes))
@@ -347,7 +351,8 @@ class Communicator:
         return {"code": st.code, "name": STATUS_NAMES.get(st.code, "?"), "site": SITE_NAMES.get(st.site, "?"),
                 "detail": (st.detail0, st.detail1), "trace_ns": tr,
                 "phases_us": {"publish": (tr[1] - tr[0]) / 1e3, "metadata": (tr[2] - tr[1]) / 1e3,
-                              "issue": (tr[3] - tr[2]) / 1e3, "drain": (tr[4] - tr[3]) / 1e3}}
+                              "issue": (tr[3] - tr[2]) / 1e3, "drain": (tr[4] - tr[3]) / 1e3,
+                              "fence": (tr[6] - tr[5]) / 1e3, "copy": (tr[5] - tr[2]) / 1e3, "report": (tr[7] - tr[6]) / 1e3}}
 
     def check(self) -> None:
         s = self.status()
@@ -360,6 +365,13 @@ class Communicator:
         self.host_barrier()
         self._lib.rbv_ctx_reset(self._ctx)
         self.host_barrier()
+
+    def set_bulk(self, mode: int) -> None:
+        """Bulk-copy engine (``cp.async.bulk`` through a shared-memory ring per warp) for large 16-byte aligned
+        chunks of the rendezvous protocol: 0 = never (default; the vector path measured as fast), 1 = whenever the
+        buffers allow, -1 = chosen by size."""
+        self._bulk = int(mode)
+        self._lib.rbv_ctx_set_bulk(self._ctx, self._bulk)
 
     def enable_trace(self, on: bool = True) -> None:
         """Have every following call report its phase time stamps (``status()['phases_us']``)."""

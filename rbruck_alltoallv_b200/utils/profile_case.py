@@ -70,6 +70,21 @@ def _gemm(which):
     assert err.item() == 0
 
 
+def _gemm_fp8():
+    from ..ops.moe import grouped_gemm_fp8, quantize_rows_fp8, quantize_weight_blocks_fp8
+    G, rows, H, I = 2, 2048, 4096, 14336
+    gs = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    gr = torch.tensor([rows, rows], dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    Aq, a_sc = quantize_rows_fp8(torch.randn(G * rows, H, device="cuda").to(torch.bfloat16))
+    Bq, b_sc = quantize_weight_blocks_fp8((torch.randn(G, 2 * I, H, device="cuda") * 0.02).to(torch.bfloat16))
+    out = torch.empty(G * rows, I, dtype=torch.bfloat16, device="cuda")
+    for _ in range(4):
+        grouped_gemm_fp8(Aq, a_sc, Bq, b_sc, gs, gr, out=out, swiglu=True, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+
+
 def _transpose():
     from ..ops.fft import PencilTranspose
     from ..parallel.comm import Communicator
@@ -95,6 +110,8 @@ def main() -> int:
         _gemm(1)
     elif case == "gemm2":
         _gemm(2)
+    elif case == "gemm_fp8":
+        _gemm_fp8()
     elif case == "transpose":
         _transpose()
     elif case == "eager":

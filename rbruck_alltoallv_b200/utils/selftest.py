@@ -66,7 +66,7 @@ def check_all(comm: Communicator, ts: int = 4, seed: int = 3) -> int:
     return failures
 
 
-def bench(comm: Communicator, sizes=(16, 1024, 65536, 1 << 20, 4 << 20)) -> list:
+def bench(comm: Communicator, sizes=(16, 1024, 65536, 1 << 20, 4 << 20), aligned: bool = False) -> list:
     P, L, mine = comm.P, comm.L, comm.local_ranks
     dev = f"cuda:{comm.device}"
     flush, align = L2Flusher(dev), RankAligner(comm)
@@ -74,6 +74,8 @@ def bench(comm: Communicator, sizes=(16, 1024, 65536, 1 << 20, 4 << 20)) -> list
     for nbytes in sizes:
         elems = max(1, nbytes // 2)
         counts = D.normal(P, elems, 0.25, seed=nbytes)
+        if aligned:   # every block starts on a 16-byte boundary (8 bf16 elements)
+            counts = (counts // 8) * 8
         sc = counts[mine].astype(np.int32)
         rc = counts.T[mine].astype(np.int32)
         send = [torch.zeros(max(int(sc[i].sum()), 1), dtype=torch.bfloat16, device=dev) for i in range(L)]
@@ -82,6 +84,11 @@ def bench(comm: Communicator, sizes=(16, 1024, 65536, 1 << 20, 4 << 20)) -> list
         emax = comm.max_block_bytes(sc, 2)
         cases = [("spreadout", dict(algo="spreadout")), ("rbruck_r2", dict(algo="rbruck", r=2)),
                  ("tuna2_r2", dict(algo="tuna2", r=2)), ("pairwise", dict(algo="pairwise"))]
+        if nbytes >= (64 << 10):   # the two copy engines of the rendezvous protocol, side by side
+            cases += [("spreadout_vector", dict(algo="spreadout", bulk=0)), ("spreadout_bulk", dict(algo="spreadout", bulk=1))]
+            if comm.nproc == 1:
+                cases += [("rbruck_r2_vector", dict(algo="rbruck", r=2, bulk=0)),
+                          ("rbruck_r2_bulk", dict(algo="rbruck", r=2, bulk=1))]
         if emax <= (256 << 10):
             cases += [("spreadout_eager", dict(algo="spreadout", eager_max_bytes=emax)),
                       ("rbruck_r2_eager", dict(algo="rbruck", r=2, eager_max_bytes=emax))]
@@ -115,19 +122,25 @@ def main() -> int:
     ap.add_argument("--nranks", type=int, default=0)
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--out", default="")
+    ap.add_argument("--sizes", default="", help="comma-separated mean block sizes in bytes for --bench")
+    ap.add_argument("--heap-mb", type=int, default=1024)
+    ap.add_argument("--aligned", action="store_true", help="--bench with block sizes that are multiples of 16 bytes")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         local = int(os.environ.get("LOCAL_RANK", "0"))
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    comm = Communicator(nranks=args.nranks or max(world, 1), heap_bytes=1 << 30, arena_bytes=64 << 20)
+    comm = Communicator(nranks=args.nranks or max(world, 1), heap_bytes=args.heap_mb << 20, arena_bytes=64 << 20)
     failures = check_all(comm)
     if world > 1:
         f = torch.tensor([failures], device="cuda")
         dist.all_reduce(f)
         failures = int(f.item())
-    rows = bench(comm) if args.bench and failures == 0 else None
+    sizes = tuple(int(x) for x in args.sizes.split(",")) if args.sizes else None
+    rows = None
+    if args.bench and failures == 0:
+        rows = bench(comm, sizes, args.aligned) if sizes else bench(comm, aligned=args.aligned)
     if comm.proc == 0:
         line = {"selftest": "ok" if failures == 0 else "FAILED", "failures": failures, "P": comm.P, "gpus": comm.nproc,
                 "nvls_metadata": bool(comm.nvls)}

@@ -78,6 +78,21 @@ def test_large_blocks_multi_chunk():
     run_case(4, "rbruck", 4, counts, seed=2, r=2, chunk_bytes=96 << 10, grid=37)
 
 
+BULK = [("spreadout", {}), ("rbruck", dict(r=2)), ("tuna2", dict(r=2, b=2)), ("ttpl_bt_s1", dict(n=2, r=2))]
+
+
+@pytest.mark.parametrize("algo,kw", BULK, ids=[a for a, _ in BULK])
+def test_bulk_copy_engine(algo, kw):
+    # 16-byte elements keep every block aligned: blocks of up to 80 KB span many 4 KB tiles with ragged last tiles
+    run_case(4, algo, 16, dist.uniform(4, 5000, seed=7), seed=7, bulk=1, **kw)
+    # 4-byte elements with gaps between blocks: unaligned chunks fall back to the vector path, aligned ones
+    # end in tails shorter than 16 bytes; several chunks per block
+    run_case(4, algo, 4, dist.uniform(4, 9000, seed=8), packed=False, seed=8, bulk=1, chunk_bytes=8 << 10, **kw)
+    if algo == "spreadout":
+        # the size-based choice: 2.8 MB blocks give every warp more than 16 KB
+        run_case(4, algo, 4, dist.normal(4, 700_000, seed=9), seed=9, bulk=-1, **kw)
+
+
 def test_zipf_and_empty():
     counts = dist.zipf(8, 16384, seed=11)
     run_case(8, "rbruck", 4, counts, seed=11, r=2)
