@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
       if (tid == 0) s_total = carry;
     }
     __syncthreads();
+    if (t0 == 0 && blockIdx.x == 0 && tid == 0) my->status.trace[1] = dev::globaltimer();   // work items sized
     const unsigned total = s_total;
     unsigned c = (gwarp + nwarps - (base % nwarps)) % nwarps;
     int oi = 0;
@@ -280,6 +281,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         alive = __all_sync(0xffffffffu, alive);
       }
     }
+    if (blockIdx.x == 0 && tid == 0) my->status.trace[2] = dev::globaltimer();   // first warp's items done
     base += total;
     __syncthreads();
   }
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   // The last CTA to leave advances the call number and publishes the status.
   __syncthreads();
   if (tid == 0) {
+    if (blockIdx.x == 0) my->status.trace[3] = dev::globaltimer();               // first CTA done
     __threadfence();
     if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
       my->exit_count = 0;

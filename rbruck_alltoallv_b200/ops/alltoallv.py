@@ -8,6 +8,7 @@ baseline only: it stands where ``MPI_Alltoallv`` stands in the reference's drive
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import numpy as np
@@ -15,6 +16,28 @@ import torch
 
 from ..parallel import comm as _comm
 from ..parallel import tuner as _tuner
+
+
+_ENV_INT = {"RBV_RADIX": "r", "RBV_RADIX2": "r2", "RBV_BATCH": "b", "RBV_BATCH2": "b2", "RBV_GROUP": "n"}
+
+
+def env_overrides() -> dict:
+    """Choices forced from the environment: ``RBV_ALGO`` (any algorithm name), ``RBV_RADIX`` / ``RBV_RADIX2``,
+    ``RBV_BATCH`` / ``RBV_BATCH2``, ``RBV_GROUP`` (ranks per group of the two-layer algorithms) and ``RBV_PROTOCOL``
+    (``eager`` or ``rendezvous``).  They take precedence over the tuner table in ``algo="auto"`` calls.  The
+    reference's drivers take the same knobs as positional arguments (examples/rbruckv_example.cpp:23-44)."""
+    out = {}
+    if os.environ.get("RBV_ALGO"):
+        out["algo"] = os.environ["RBV_ALGO"]
+    for var, key in _ENV_INT.items():
+        if os.environ.get(var):
+            out[key] = int(os.environ[var])
+    proto = os.environ.get("RBV_PROTOCOL", "")
+    if proto:
+        if proto not in ("eager", "rendezvous"):
+            raise ValueError("RBV_PROTOCOL must be 'eager' or 'rendezvous'")
+        out["protocol"] = proto
+    return out
 
 
 def _auto_choice(c, recv, sendcounts, kw, agree_on_max: bool):
@@ -27,6 +50,10 @@ def _auto_choice(c, recv, sendcounts, kw, agree_on_max: bool):
         hint = kw.get("bytes_hint", -1)
         mean_block = hint / (c.L * c.P) if hint and hint > 0 else 64 << 10
     choice = _tuner.choose(c.P, c.nproc, mean_block)
+    forced = env_overrides()
+    if "algo" in forced and forced["algo"] != choice.get("algo"):
+        choice = {"algo": forced["algo"], "protocol": choice.get("protocol", "rendezvous")}   # drop the other algorithm's knobs
+    choice.update(forced)
     out = dict(kw)
     out["algo"] = choice.pop("algo")
     protocol = choice.pop("protocol", "rendezvous")

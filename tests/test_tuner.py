@@ -1,6 +1,8 @@
 """Tuner table logic (no GPU)."""
 import json
 
+import pytest
+
 from rbruck_alltoallv_b200.parallel import tuner
 
 
@@ -29,3 +31,37 @@ def test_candidates_are_valid_plans():
 
 def test_size_class():
     assert tuner.size_class(1) == 0 and tuner.size_class(1024) == 10 and tuner.size_class(1500) == 10
+
+
+def test_environment_overrides_take_precedence(monkeypatch):
+    """RBV_ALGO / RBV_RADIX / RBV_PROTOCOL win over the tuner table in automatic calls (no GPU needed: the
+    choice is resolved against a stand-in communicator)."""
+    from types import SimpleNamespace
+
+    import numpy as np
+    import torch
+
+    from rbruck_alltoallv_b200.ops import alltoallv as A
+
+    comm = SimpleNamespace(P=8, L=8, nproc=1, arena_bytes=8 << 20, max_block_bytes=lambda sc, ts: int(np.max(sc)) * ts)
+    recv = [torch.empty(4, dtype=torch.float32)]
+    sc = np.full((8, 8), 100, dtype=np.int32)
+    for var in ("RBV_ALGO", "RBV_RADIX", "RBV_BATCH", "RBV_GROUP", "RBV_PROTOCOL"):
+        monkeypatch.delenv(var, raising=False)
+    base = A._auto_choice(comm, recv, sc, {}, agree_on_max=True)
+    assert "algo" in base
+    monkeypatch.setenv("RBV_ALGO", "tuna2")
+    monkeypatch.setenv("RBV_RADIX", "3")
+    monkeypatch.setenv("RBV_BATCH", "2")
+    monkeypatch.setenv("RBV_PROTOCOL", "rendezvous")
+    got = A._auto_choice(comm, recv, sc, {}, agree_on_max=True)
+    assert got["algo"] == "tuna2" and got["r"] == 3 and got["b"] == 2 and "eager_max_bytes" not in got
+    monkeypatch.setenv("RBV_PROTOCOL", "eager")
+    got = A._auto_choice(comm, recv, sc, {}, agree_on_max=True)
+    assert got["eager_max_bytes"] == 400
+    # a keyword given by the caller still wins over the environment
+    got = A._auto_choice(comm, recv, sc, {"r": 4}, agree_on_max=True)
+    assert got["r"] == 4
+    monkeypatch.setenv("RBV_PROTOCOL", "carrier-pigeon")
+    with pytest.raises(ValueError):
+        A._auto_choice(comm, recv, sc, {}, agree_on_max=True)
