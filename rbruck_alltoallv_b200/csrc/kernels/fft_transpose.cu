@@ -35,8 +35,11 @@ template <typename T, int TF, int TK>
 __device__ void move_boxes(const TransposeArgs& a, T* tile_raw) {
   T (*tile)[TK + 1] = reinterpret_cast<T(*)[TK + 1]>(tile_raw);
   // tiles are enumerated over all destinations; a CTA takes tile ids blockIdx.x, blockIdx.x + gridDim.x, ...
+  // Destinations are visited starting with this rank and going upwards (the spread-out order): at any moment the
+  // ranks of a group write to different peers, so no GPU's NVLink ingress is shared by the whole group.
   long long tile_base = 0;
-  for (int d = 0; d < a.nproc; d++) {
+  for (int dd = 0; dd < a.nproc; dd++) {
+    const int d = (a.proc + dd) % a.nproc;
     const rbv_box& b = a.box[d];
     if (b.n0 <= 0 || b.n1 <= 0 || b.n2 <= 0) continue;
     const T* src = reinterpret_cast<const T*>(a.src) + b.src_off;
