@@ -305,3 +305,21 @@ def test_functional_api_with_automatic_choice():
         got = recv[d].cpu()
         for s in range(P):
             assert torch.equal(got[s * n:(s + 1) * n], torch.arange(d * n, (d + 1) * n, dtype=torch.int32) + 1000 * s)
+
+
+def test_ulysses_sequence_head_exchange_round_trip():
+    from rbruck_alltoallv_b200.ops.ulysses import UlyssesExchange
+    P, s_l, H, D = 4, 24, 8, 16
+    comm = get_comm(P)
+    ex = UlyssesExchange(comm, s_l, H, D, dtype=torch.float32)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    full = torch.randn(P * s_l, H, D, device="cuda", generator=g)                 # [S, H, D]
+    x = [full[r * s_l:(r + 1) * s_l].contiguous() for r in range(P)]
+    y = ex.seq_to_head(x)
+    comm.check()
+    for r in range(P):
+        assert torch.equal(y[r], full[:, r * (H // P):(r + 1) * (H // P), :])
+    back = ex.head_to_seq([t.clone() for t in y])
+    comm.check()
+    for r in range(P):
+        assert torch.equal(back[r], x[r])
