@@ -211,10 +211,28 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         const size_t nunits = ((size_t)bytes + 7) / 8;
         char* dst = a.heap[a.proc] + a.recvoff[lsrc] + (size_t)rdispls[(size_t)lsrc * P + o.origin] * ts;
         const size_t uend = min(nunits, u0 + cu);
-        for (size_t u = u0 + lane; u < uend; u += 32) {
-          uint4 v;
-          if (!poll_unit(cell + 1 + u, ec, v)) { eager_error(a, RBV_ERR_TIMEOUT, WAIT_CELL, t0 + oi, (int)u); alive = false; break; }
-          store_words(dst, u, v.x, v.z, bytes);
+        if (((reinterpret_cast<uintptr_t>(dst) & 15) | (u0 & 1)) == 0) {
+          // two units per lane, written as one 16-byte vector (full 32-byte sectors; larger packets when the
+          // receive buffer is pinned host memory)
+          for (size_t u = u0 + 2 * lane; u < uend; u += 64) {
+            uint4 v0, v1 = make_uint4(0u, 0u, 0u, 0u);
+            bool got = poll_unit(cell + 1 + u, ec, v0);
+            const bool two = u + 1 < uend;
+            if (got && two) got = poll_unit(cell + 2 + u, ec, v1);
+            if (!got) { eager_error(a, RBV_ERR_TIMEOUT, WAIT_CELL, t0 + oi, (int)u); alive = false; break; }
+            if (two && (u + 2) * 8 <= bytes) {
+              *reinterpret_cast<uint4*>(dst + u * 8) = make_uint4(v0.x, v0.z, v1.x, v1.z);
+            } else {
+              store_words(dst, u, v0.x, v0.z, bytes);
+              if (two) store_words(dst, u + 1, v1.x, v1.z, bytes);
+            }
+          }
+        } else {
+          for (size_t u = u0 + lane; u < uend; u += 32) {
+            uint4 v;
+            if (!poll_unit(cell + 1 + u, ec, v)) { eager_error(a, RBV_ERR_TIMEOUT, WAIT_CELL, t0 + oi, (int)u); alive = false; break; }
+            store_words(dst, u, v.x, v.z, bytes);
+          }
         }
         alive = __all_sync(0xffffffffu, alive);
         continue;

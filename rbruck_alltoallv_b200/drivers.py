@@ -104,7 +104,18 @@ def main(argv=None) -> int:
     P = comm.P
     _timed.flush = L2Flusher(f"cuda:{comm.device}")
     _timed.align = RankAligner(comm)
-    drv = args.driver
+    # the reference's CMake target and file names are accepted too
+    aliases = {"merge_benckmark": "merge", "merge_benchmark": "merge", "simple_merge_benchmark": "merge",
+               "simply_merge": "merge", "split_benchmark": "split", "balanced_benchmark": "balance",
+               "gather_benchmark": "gather", "mpich_twolayer_alltoall": "twolayer", "ms_benchmark": "twolayer",
+               "rbruckv_example": "rbruckv", "twolayer_example": "twolayer", "twophaseLayer_example": "combAlltoallv",
+               "twophaseLayer_example2": "LTRNA", "twophaseLayer_example3": "TTPL", "twophaseLayer_example4": "TLLiner_S2",
+               "twophaseLayer_example5": "TLLiner_S3", "MLinputs_example": "MLinputs", "FFT_distribution": "FFT",
+               "other_distributions": "otherDis"}
+    drv = aliases.get(args.driver, args.driver)
+    if args.driver in ("mpich_twolayer_alltoall", "ms_benchmark"):
+        p = [p[0] if p else "10", "1"] + list(p[1:])       # toy programs of the reference: one rank per group
+        args.nmax = min(args.nmax, 2)
     ints = [int(v) for v in p[1:] if v.lstrip("-").isdigit()]
     fails = 0
     if drv == "rbruckv":                       # <loop> <bases...>
