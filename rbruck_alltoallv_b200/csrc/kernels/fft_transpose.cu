@@ -52,7 +52,14 @@ __device__ void move_boxes(const TransposeArgs& a, T* tile_raw) {
     const long long to = fast == 1 ? b.t0 : b.t1;
     const int W2 = fast == 2 ? kThreadsT : TK;               // elements of dim 2 per tile
     const int t2n = (b.n2 + W2 - 1) / W2;
-    const int tfn = fast == 2 ? 1 : (nf + TF - 1) / TF;
+    // Tiles start `lead` elements before the box along the destination-fastest dimension, so that every run a
+    // tile writes begins on a 128-byte line of the destination (whole lines over NVLink instead of a ragged head
+    // and tail per run).  Possible when all rows of the box share their alignment.
+    constexpr int kLine = 128 / (int)sizeof(T);
+    int lead = 0;
+    if (fast != 2 && to % kLine == 0 && b.t2 % kLine == 0)
+      lead = (int)((reinterpret_cast<uintptr_t>(dst) / sizeof(T)) % kLine);
+    const int tfn = fast == 2 ? 1 : (nf + lead + TF - 1) / TF;
     const long long ntiles = fast == 2 ? (long long)b.n0 * b.n1 * t2n : (long long)no * tfn * t2n;
     const long long first = ((long long)blockIdx.x - (tile_base % (long long)gridDim.x) + gridDim.x) % gridDim.x;
     for (long long t = first; t < ntiles; t += gridDim.x) {
@@ -65,17 +72,23 @@ __device__ void move_boxes(const TransposeArgs& a, T* tile_raw) {
       } else {
         const int k0 = (int)(t % t2n) * TK;
         const long long r1 = t / t2n;
-        const int f0 = (int)(r1 % tfn) * TF;
+        const int f0 = (int)(r1 % tfn) * TF - lead;
         const int o = (int)(r1 / tfn);
         // read: rows along dim 2 (contiguous in the source); all loads of a thread are issued back to back
         {
           const int tx = threadIdx.x % TK, ty = threadIdx.x / TK;
           constexpr int RS = kThreadsT / TK;
+          T v[TF / RS];
+          const int k = k0 + tx;
+          const T* p = src + o * so + (long long)(f0 + ty) * sf + k;
+          const long long step = (long long)RS * sf;
           #pragma unroll
-          for (int r = 0; r < TF; r += RS) {
-            const int f = f0 + r + ty, k = k0 + tx;
-            if (f < nf && k < b.n2) tile[r + ty][tx] = src[o * so + f * sf + k];
+          for (int i = 0; i < TF / RS; i++, p += step) {
+            const int f = f0 + i * RS + ty;
+            if (f >= 0 && f < nf && k < b.n2) v[i] = *p;
           }
+          #pragma unroll
+          for (int i = 0; i < TF / RS; i++) tile[i * RS + ty][tx] = v[i];
         }
         __syncthreads();
         // write: rows along the destination-fastest dim (contiguous in the destination)
@@ -85,7 +98,7 @@ __device__ void move_boxes(const TransposeArgs& a, T* tile_raw) {
           #pragma unroll
           for (int r = 0; r < TK; r += RS) {
             const int k = k0 + r + ty, f = f0 + tx;
-            if (f < nf && k < b.n2) dst[o * to + (long long)k * b.t2 + f] = tile[tx][r + ty];
+            if (f >= 0 && f < nf && k < b.n2) dst[o * to + (long long)k * b.t2 + f] = tile[tx][r + ty];
           }
         }
         __syncthreads();
