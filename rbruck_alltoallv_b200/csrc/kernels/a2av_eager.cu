@@ -144,6 +144,12 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         b = cap >= 0 ? min((size_t)cap * ts, emax) : emax;
       } else if (o.src_cell < 0) {            // first hop (or self copy): size known locally
         b = (size_t)sendcounts[(size_t)lsrc * P + o.dest] * ts;
+        // Small blocks: start fetching the block now.  By the time a warp picks the item up (two barriers and a
+        // scan later) the lines are in L2, which takes one DRAM round trip off the path of a small call.
+        if (b != 0 && b <= 1024) {
+          const char* src = a.sendbuf[lsrc] + (size_t)sdispls[(size_t)lsrc * P + o.dest] * ts;
+          for (size_t off = 0; off < b; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
+        }
       } else {
         b = emax;                             // relay: size arrives with the block
       }
