@@ -8,12 +8,13 @@
 //       receive buffer or staging cell (a peer mapping over NVLink when the destination lives on
 //       another GPU); rotation, pack, unpack and final placement are folded into the addressing,
 //   (3) completion          -- waits until every chunk bound for a local rank's receive buffer has landed
-//       (each chunk of a final hop bumps the receiver's arrival counter; the receiver knows all sizes).
+//       (chunks of final hops are tallied per CTA in shared memory and added to the receivers' arrival counters
+//       once per op tile, behind one fence; the receiver knows all sizes and therefore the count to wait for).
 //
 // Work distribution: ops are cut into chunks of `chunk_bytes`; chunk c of the process-wide
 // sequence is handled by WARP c mod (warps in the grid).  A warp copies its chunk with 16-byte
-// vectors (512 contiguous bytes per warp instruction) and, when it completes an op, signals the
-// destination.  Small blocks thus proceed in parallel, one warp each, and large blocks are spread
+// vectors (512 contiguous bytes per warp instruction; optionally with cp.async.bulk through a
+// shared-memory ring, see bulk_copy.cuh) and, when it completes a staging op, signals the destination.  Small blocks thus proceed in parallel, one warp each, and large blocks are spread
 // over all warps of all SMs.  Warps walk their chunks in plan order, so a wait on a staging cell
 // only ever depends on chunks of an earlier plan key, which rules out cycles as long as all CTAs
 // are resident (cooperative launch).
