@@ -151,7 +151,7 @@ int rbv_ctx_set_nvls_meta(rbv_ctx_t ctx, void* self_ptr, void* mc_ptr, size_t by
   if (rc) g_err = ctx->c->last_error();
   return rc;
 }
-size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx) { return 2 * (size_t)ctx->c->layout().meta_bytes; }
+size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx) { return ctx->c->nvls_bytes_needed(); }
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes) { ctx->eager = max_block_bytes; }
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
 void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode) { ctx->c->set_bulk(mode); }

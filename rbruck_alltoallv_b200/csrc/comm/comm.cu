@@ -476,12 +476,12 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
 
 int Context::set_nvls_meta(void* self_ptr, void* mc_ptr, size_t bytes) {
   if (!self_ptr || !mc_ptr) { nvls_self_ = nvls_mc_ = nullptr; nvls_bytes_ = 0; return 0; }
-  if (bytes < 2 * lay_.meta_bytes || (reinterpret_cast<uintptr_t>(self_ptr) & 15) || (reinterpret_cast<uintptr_t>(mc_ptr) & 15)) {
+  if (bytes < nvls_bytes_needed() || (reinterpret_cast<uintptr_t>(self_ptr) & 15) || (reinterpret_cast<uintptr_t>(mc_ptr) & 15)) {
     last_error_ = "NVLS metadata buffer too small or misaligned";
     return RBV_ERR_BAD_ARG;
   }
   nvls_self_ = static_cast<char*>(self_ptr); nvls_mc_ = static_cast<char*>(mc_ptr); nvls_bytes_ = bytes;
-  return cudaMemset(nvls_self_, 0, 2 * lay_.meta_bytes) == cudaSuccess ? 0 : RBV_ERR_BAD_ARG;
+  return cudaMemset(nvls_self_, 0, nvls_bytes_needed()) == cudaSuccess ? 0 : RBV_ERR_BAD_ARG;
 }
 
 StatusBlock Context::status(cudaStream_t stream) {
@@ -498,7 +498,7 @@ cudaError_t Context::reset() {
   if (e != cudaSuccess) return e;
   e = cudaMemset(heap_, 0, lay_.stage_off);
   if (e != cudaSuccess) return e;
-  if (nvls_self_) cudaMemset(nvls_self_, 0, 2 * lay_.meta_bytes);
+  if (nvls_self_) cudaMemset(nvls_self_, 0, nvls_bytes_needed());
   for (auto& kv : plans_)
     if (kv.second->d_done) cudaMemset(kv.second->d_done, 0, kv.second->nops * sizeof(unsigned));
   std::memset(host_status_, 0, sizeof(StatusBlock));

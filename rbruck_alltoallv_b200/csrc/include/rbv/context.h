@@ -113,6 +113,17 @@ class Context {
   // NVLS: metadata tables in an externally provided multicast-capable buffer (local address, multicast address,
   // size).  Every process must set it, or none.  Null pointers switch back to the tables inside the heap.
   int set_nvls_meta(void* self_ptr, void* mc_ptr, size_t bytes);
+  // Bytes an NVLS buffer must have: two metadata tables and the arrival counters of the auxiliary barriers.
+  size_t nvls_bytes_needed() const { return nvls_aux_off() + 256; }
+  size_t nvls_aux_off() const { return (2 * (size_t)lay_.meta_bytes + 255) & ~(size_t)255; }
+  // Arrival counters of the auxiliary barriers (MoE dispatch / combine, transpose) inside the NVLS buffer: this
+  // GPU's copy and the multicast address that reaches every GPU's copy; null when NVLS is off.
+  unsigned long long* nvls_aux_self() const {
+    return nvls_mc_ ? reinterpret_cast<unsigned long long*>(nvls_self_ + nvls_aux_off()) : nullptr;
+  }
+  unsigned long long* nvls_aux_mc() const {
+    return nvls_mc_ ? reinterpret_cast<unsigned long long*>(nvls_mc_ + nvls_aux_off()) : nullptr;
+  }
   const std::string& last_error() const { return last_error_; }
   const DevPlan* plan_for(const AlgoSpec& spec);
 

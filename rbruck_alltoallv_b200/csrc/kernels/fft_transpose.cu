@@ -23,6 +23,8 @@ struct TransposeArgs {
   int nproc, proc;
   unsigned long long ctrl_off, timeout_ns;
   int* error;
+  unsigned long long* aux_self;   // arrival counter copies in the NVLS buffer and their multicast address
+  unsigned long long* aux_mc;     // (null: the counters of the control blocks are used)
   char* heap[kMaxProcs];
   const char* src;
   unsigned long long dst_off;   // byte offset of the destination array inside every heap
@@ -124,11 +126,16 @@ __global__ void __launch_bounds__(kThreadsT) transpose_exchange_kernel(const __g
       my->aux_exit[2] = 0;
       const unsigned seq = my->aux_seq[2];
       dev::fence_acq_rel(a.nproc > 1);   // one fence publishes every CTA's tiles (each fenced before its exit count)
-      for (int q = 0; q < a.nproc; q++)
-        dev::red_relaxed_add(&reinterpret_cast<CtrlBlock*>(a.heap[q] + a.ctrl_off)->aux_arrivals[2], 1ull, q != a.proc);
+      if (a.aux_mc) {
+        dev::multimem_red_add(a.aux_mc + 2, 1ull);   // NVSwitch bumps the counter on every GPU
+      } else {
+        for (int q = 0; q < a.nproc; q++)
+          dev::red_relaxed_add(&reinterpret_cast<CtrlBlock*>(a.heap[q] + a.ctrl_off)->aux_arrivals[2], 1ull, q != a.proc);
+      }
       dev::WaitCfg wc{&my->abort_flag, a.timeout_ns};
       const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)a.nproc;
-      if (dev::wait_ge(&my->aux_arrivals[2], target, wc, a.nproc > 1) != dev::WAIT_OK) atomicCAS(a.error, 0, 1);
+      const unsigned long long* arrivals = a.aux_mc ? a.aux_self + 2 : &my->aux_arrivals[2];
+      if (dev::wait_ge(arrivals, target, wc, a.nproc > 1) != dev::WAIT_OK) atomicCAS(a.error, 0, 1);
       my->aux_seq[2] = seq + 1u;
     }
   }
@@ -146,6 +153,8 @@ extern "C" int rbv_transpose_exchange(rbv_ctx_t ctx, const void* src, unsigned l
   a.nproc = c.nproc(); a.proc = c.proc();
   a.ctrl_off = c.layout().ctrl_off; a.timeout_ns = c.timeout_ns();
   a.error = error_flag;
+  a.aux_self = c.nvls_aux_self();
+  a.aux_mc = c.nvls_aux_mc();
   for (int q = 0; q < kMaxProcs; q++) {
     a.heap[q] = q < c.nproc() ? c.peer_heap(q) : nullptr;
     if (q < c.nproc()) a.box[q] = boxes[q]; else a.box[q] = rbv_box{};

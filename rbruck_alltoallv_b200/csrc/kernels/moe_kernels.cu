@@ -114,8 +114,21 @@ struct MoeComm {
   unsigned long long ctrl_off;
   unsigned long long timeout_ns;
   int* error;               // device flag: 0 ok, else (site << 8 | detail)
+  unsigned long long* aux_self;   // arrival counters of the auxiliary barriers in the NVLS buffer (null: in the
+  unsigned long long* aux_mc;     // control blocks); aux_mc is the multicast address that reaches every GPU's copy
   char* heap[kMaxProcs];
 };
+
+// This process has reached auxiliary barrier `slot`: one multimem.red through NVSwitch, or one relaxed reduction
+// per process.  The caller has fenced.
+__device__ __forceinline__ void aux_arrive(const MoeComm& c, int slot) {
+  if (c.aux_mc) { dev::multimem_red_add(c.aux_mc + slot, 1ull); return; }
+  for (int q = 0; q < c.nproc; q++)
+    dev::red_relaxed_add(&reinterpret_cast<CtrlBlock*>(c.heap[q] + c.ctrl_off)->aux_arrivals[slot], 1ull, q != c.proc);
+}
+__device__ __forceinline__ const unsigned long long* aux_counter(const MoeComm& c, int slot) {
+  return c.aux_mc ? c.aux_self + slot : &reinterpret_cast<CtrlBlock*>(c.heap[c.proc] + c.ctrl_off)->aux_arrivals[slot];
+}
 
 __device__ __forceinline__ CtrlBlock* ctrl_of(const MoeComm& c, int q) {
   return reinterpret_cast<CtrlBlock*>(c.heap[q] + c.ctrl_off);
@@ -171,10 +184,10 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
       my->aux_exit[0] = 0;
       const unsigned seq = my->aux_seq[0];
       dev::fence_acq_rel(c.nproc > 1);   // one fence publishes every CTA's rows (each fenced before its exit count)
-      for (int q = 0; q < c.nproc; q++) dev::red_relaxed_add(&ctrl_of(c, q)->aux_arrivals[0], 1ull, q != c.proc);
+      aux_arrive(c, 0);
       dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
       const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
-      if (dev::wait_ge(&my->aux_arrivals[0], target, wc, c.nproc > 1) != dev::WAIT_OK) moe_fail(c, 1, 0);
+      if (dev::wait_ge(aux_counter(c, 0), target, wc, c.nproc > 1) != dev::WAIT_OK) moe_fail(c, 1, 0);
       my->aux_seq[0] = seq + 1u;
     }
   }
@@ -211,11 +224,11 @@ __global__ void __launch_bounds__(kMoeThreads) moe_combine_kernel(const __grid_c
     const unsigned seq = __ldcg(&my->aux_seq[1]);
     if (blockIdx.x == 0) {
       dev::fence_acq_rel(c.nproc > 1);
-      for (int q = 0; q < c.nproc; q++) dev::red_relaxed_add(&ctrl_of(c, q)->aux_arrivals[1], 1ull, q != c.proc);
+      aux_arrive(c, 1);
     }
     dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
     const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
-    int r = dev::wait_ge(&my->aux_arrivals[1], target, wc, c.nproc > 1);
+    int r = dev::wait_ge(aux_counter(c, 1), target, wc, c.nproc > 1);
     if (r != dev::WAIT_OK) moe_fail(c, 2, 0);
     s_ok = (r == dev::WAIT_OK);
   }
@@ -258,6 +271,8 @@ MoeComm make_comm(rbv_ctx_t ctx, int* error) {
   m.ctrl_off = c.layout().ctrl_off;
   m.timeout_ns = c.timeout_ns();
   m.error = error;
+  m.aux_self = c.nvls_aux_self();
+  m.aux_mc = c.nvls_aux_mc();
   for (int q = 0; q < kMaxProcs; q++) m.heap[q] = q < c.nproc() ? c.peer_heap(q) : nullptr;
   return m;
 }

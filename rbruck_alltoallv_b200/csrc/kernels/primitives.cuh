@@ -198,6 +198,10 @@ __device__ __forceinline__ void red_relaxed_add(unsigned long long* p, unsigned 
   if (sys) asm volatile("red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
   else asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// One reduction that NVSwitch applies to the copy of the counter on every GPU of the multicast group (NVLS).
+__device__ __forceinline__ void multimem_red_add(unsigned long long* mc, unsigned long long v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u64 [%0], %1;" ::"l"(mc), "l"(v) : "memory");
+}
 __device__ __forceinline__ void st_relaxed(unsigned* p, unsigned v, bool sys) {
   if (sys) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
   else asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -67,3 +67,18 @@ def test_nvls_metadata_two_processes():
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert '"selftest": "ok"' in res.stdout and '"nvls_metadata": true' in res.stdout
+
+
+@pytest.mark.skipif(_ngpus() < 2 or os.environ.get("RBV_TEST_NVLS") != "1",
+                    reason="needs 2 GPUs and RBV_TEST_NVLS=1 (binds memory to an NVLink multicast object)")
+@pytest.mark.parametrize("module,args", [
+    ("moe_bench", ["--tokens", "512", "--hidden", "512", "--inter", "1024", "--experts-per-rank", "4", "--check", "--steps", "3"]),
+    ("fft_bench", ["--size", "48", "--pr", "1", "--pc", "2", "--check", "--steps", "2", "--warmup", "1"])])
+def test_nvls_arrivals_of_the_auxiliary_barriers(module, args):
+    """MoE dispatch / combine and the transpose report their arrival with one multimem.red when NVLS is on."""
+    env = dict(os.environ, PYTHONPATH=ROOT, RBV_NVLS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29681", "-m", f"rbruck_alltoallv_b200.utils.{module}", *args]
+    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert '"check": "ok"' in res.stdout
