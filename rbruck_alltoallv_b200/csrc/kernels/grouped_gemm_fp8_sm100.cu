@@ -44,7 +44,8 @@ struct Fp8Params {
   const float* b_scale;        // [G][N / 128][K / 128]
   void* C;
   int* error;
-  int epilogue;                // 0 plain, 1 SwiGLU over interleaved gate / up columns
+  int epilogue;                // bit 0: SwiGLU over interleaved gate / up columns; bit 1: coarse scales (the
+                               // scales of K block 0 hold for the whole row / weight block: one TMEM read per tile)
 };
 
 struct Tile { int g, m0, n0, rows_left; bool valid; };
@@ -121,15 +122,18 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
   } else if (warp == 1) {
     if (elect_one()) {
       const uint32_t idesc = umma_idesc(BM, BN, 0 /*e4m3*/);
+      const bool coarse = (p.epilogue & 2) != 0;
       int stage = 0; uint32_t phase = 0;
       unsigned it = 0;   // running K-block count -> TMEM slot ring
       bool ok = true;
       for (int t = blockIdx.x; ok; t += gridDim.x) {
         const Tile tl = tile_of(p, t, s_rows, s_start);
         if (!tl.valid) break;
-        for (int kb = 0; kb < num_kb && ok; kb++, it++) {
+        for (int kb = 0; kb < num_kb && ok; kb++) {
+          // fine scales: one TMEM slot per K block; coarse scales: one per tile, accumulated over all K blocks
           const int slot = it % SLOTS;
-          if (!mbar_wait(&tempty_bar[slot], ((it / SLOTS) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          if (!coarse || kb == 0)
+            if (!mbar_wait(&tempty_bar[slot], ((it / SLOTS) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint8_t* sa = tiles + (size_t)stage * STAGE;
@@ -138,9 +142,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
           const uint32_t d_tmem = tmem_base + (uint32_t)slot * BN;
           #pragma unroll
           for (int kk = 0; kk < BK / 32; kk++)
-            umma_f8(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (uint32_t)(kk != 0));
+            umma_f8(d_tmem, adesc + 2u * kk, bdesc + 2u * kk, idesc, (uint32_t)(coarse ? (kb | kk) != 0 : kk != 0));
           umma_commit(&empty_bar[stage]);
-          umma_commit(&tfull_bar[slot]);
+          if (!coarse || kb == num_kb - 1) { umma_commit(&tfull_bar[slot]); it++; }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -174,6 +178,27 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
         sa_q[j] = (j < nkb) ? __ldg(sa + (size_t)j * p.a_rows) : 0.0f;
         sb_q[j] = (j < nkb) ? __ldg(sb + j) : 0.0f;
       }
+      if (p.epilogue & 2) {
+        // coarse scales: the tile was accumulated over all K blocks in one TMEM slot; read it once and scale
+        const int slot = it % SLOTS;
+        const float scale = in_a ? sa_q[0] * sb_q[0] : 0.0f;
+        uint32_t t0[32], t1[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)half * HN + (uint32_t)slot * BN;
+        if (!mbar_wait(&tfull_bar[slot], (it / SLOTS) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        tmem_ld32(taddr, t0);
+        tmem_ld32(taddr + 32, t1);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[slot]);
+        it++;
+        #pragma unroll
+        for (int c = 0; c < 16; c++) {
+          acc2[c] = make_float2(scale * __uint_as_float(t0[2 * c]), scale * __uint_as_float(t0[2 * c + 1]));
+          acc2[16 + c] = make_float2(scale * __uint_as_float(t1[2 * c]), scale * __uint_as_float(t1[2 * c + 1]));
+        }
+      } else {
       // Two 32-column loads per K block, software-pipelined: while one half is multiplied, the other half (or
       // the first half of the next K block) is in flight from TMEM.
       uint32_t r0[32], r1[32];
@@ -214,11 +239,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
                 __ffma2_rn(s2, make_float2(__uint_as_float(r1[2 * c]), __uint_as_float(r1[2 * c + 1])), acc2[16 + c]);
         }
       }
+      }
       const float* acc = reinterpret_cast<const float*>(acc2);
       if (!ok) break;
       if (row < tl.rows_left) {
         __nv_bfloat16* crow = C + (size_t)(tl.m0 + row) * p.ldc;
-        if (p.epilogue == 1) {
+        if (p.epilogue & 1) {
           uint4* dst = reinterpret_cast<uint4*>(crow + (tl.n0 + half * HN) / 2);
           #pragma unroll
           for (int v = 0; v < HN / 16; v++) {

@@ -82,8 +82,12 @@ def dequantize_weight_blocks_fp8(q: torch.Tensor, scale: torch.Tensor) -> torch.
 
 def grouped_gemm_fp8(Aq: torch.Tensor, a_scale_t: torch.Tensor, Bq: torch.Tensor, b_scale: torch.Tensor,
                      group_start: torch.Tensor, group_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
-                     swiglu: bool = False, error: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
-    """Block-scaled e4m3 grouped GEMM (see ``csrc/kernels/grouped_gemm_fp8_sm100.cu``); bf16 output."""
+                     swiglu: bool = False, error: Optional[torch.Tensor] = None, max_ctas: int = 0,
+                     coarse: bool = False) -> torch.Tensor:
+    """Block-scaled e4m3 grouped GEMM (see ``csrc/kernels/grouped_gemm_fp8_sm100.cu``); bf16 output.
+
+    ``coarse=True`` promises that the scales do not change along K (one per activation row, one per 128 weight
+    rows): the kernel then accumulates a whole tile in TMEM and applies ``a_scale_t[0] * b_scale[..., 0]`` once."""
     lib = _native.cuda_lib()
     G, N, K = Bq.shape
     M = Aq.shape[0]
@@ -96,7 +100,7 @@ def grouped_gemm_fp8(Aq: torch.Tensor, a_scale_t: torch.Tensor, Bq: torch.Tensor
         error = torch.zeros(1, dtype=torch.int32, device=Aq.device)
     st = torch.cuda.current_stream(Aq.device).cuda_stream
     rc = lib.rbv_grouped_gemm_fp8(_p(Aq), _p(a_scale_t), M, _p(Bq), _p(b_scale), _p(out), _p(group_start),
-                                  _p(group_rows), G, N, K, out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas),
+                                  _p(group_rows), G, N, K, out.stride(0), (1 if swiglu else 0) | (2 if coarse else 0), _p(error), int(max_ctas),
                                   C.c_void_p(st))
     if rc:
         raise RuntimeError(f"fp8 grouped GEMM launch failed (CUDA error {rc})")

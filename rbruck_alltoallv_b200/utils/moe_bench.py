@@ -108,6 +108,11 @@ def main() -> int:
                                               out=layer.h, swiglu=True, error=layer.error[1:2]), a.steps, a.warmup)
         t_g2 = _time(lambda: grouped_gemm_fp8(hq, hs, layer.w2_q, layer.w2_s, layer.group_start, layer.group_rows,
                                               out=layer.y, error=layer.error[2:3]), a.steps, a.warmup)
+        # the same operands with scales taken as constant along K: what the tile shape allows without the
+        # per-K-block rescaling (timing only; the layer itself uses the block scales)
+        t_c = _time(lambda: grouped_gemm_fp8(xq, xs, layer.w13_q, layer.w13_s, layer.group_start, layer.group_rows,
+                                             out=layer.h, swiglu=True, error=layer.error[1:2], coarse=True), a.steps, a.warmup)
+        res["ms_gemm1_coarse_scales"] = float(np.median(t_c))
     else:
         t_g1 = _time(lambda: grouped_gemm(layer.xrecv, layer.w13, layer.group_start, layer.group_rows, out=layer.h,
                                           swiglu=True, error=layer.error[1:2]), a.steps, a.warmup)

@@ -105,6 +105,32 @@ def test_grouped_gemm_fp8_block_scaled(rows, N, K):
         r0 += n
 
 
+def test_grouped_gemm_fp8_coarse_scales():
+    """Scales that are constant along K: the whole tile is accumulated in TMEM and scaled once."""
+    from rbruck_alltoallv_b200.ops import moe
+    torch.manual_seed(5)
+    rows, N, K = [200, 0, 131], 256, 512
+    G, M = len(rows), int(sum(rows))
+    Aq = torch.randn(M, K, device="cuda").clamp(-3, 3).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+    Bq = torch.randn(G, N, K, device="cuda").clamp(-3, 3).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+    As = (torch.rand(1, M, device="cuda") + 0.5).expand(K // 128, M).contiguous()
+    Bs = (torch.rand(G, N // 128, 1, device="cuda") * 0.1 + 0.01).expand(G, N // 128, K // 128).contiguous()
+    gs, gr = _groups(rows, "cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fine = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err)
+    coarse = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err, coarse=True)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    Ad, Bd = moe.dequantize_rows_fp8(Aq, As), moe.dequantize_weight_blocks_fp8(Bq, Bs)
+    r0 = 0
+    for g, n in enumerate(rows):
+        if n:
+            ref = Ad[r0:r0 + n] @ Bd[g].t()
+            for got in (fine[r0:r0 + n].float(), coarse[r0:r0 + n].float()):
+                assert (got - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-3, f"group {g}"
+        r0 += n
+
+
 def test_moe_layer_fp8_close_to_bf16():
     from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
     from rbruck_alltoallv_b200.parallel.comm import Communicator
