@@ -383,6 +383,43 @@ class Communicator:
     def set_timeout_ms(self, ms: float) -> None:
         self._lib.rbv_ctx_set_timeout_ms(self._ctx, float(ms))
 
+    # ---- liveness on the host ------------------------------------------------------------------
+    # A process that stops taking part (between calls, with nothing of its own in flight) says so in the job's
+    # key-value store; the others look before they launch, so that nobody spins on the device for a peer that
+    # will not come.  A process that vanishes without a word is caught by the device-side deadline instead.
+    def _store(self):
+        if self._dist is None:
+            return None
+        from torch.distributed import distributed_c10d as c10d
+        return c10d._get_default_store()
+
+    def announce_leave(self) -> None:
+        st = self._store()
+        if st is not None:
+            st.set(f"rbv/left/{self.proc}", "1")
+
+    def announce_return(self) -> None:
+        st = self._store()
+        if st is not None:
+            st.set(f"rbv/left/{self.proc}", "0")
+
+    def departed(self) -> list:
+        """Processes that have announced that they left (and not that they returned)."""
+        st = self._store()
+        if st is None:
+            return []
+        out = []
+        for q in range(self.nproc):
+            key = f"rbv/left/{q}"
+            if st.check([key]) and st.get(key) == b"1":
+                out.append(q)
+        return out
+
+    def require_peers(self) -> None:
+        gone = self.departed()
+        if gone:
+            raise CommError(f"processes {gone} have left the communicator; not launching")
+
     def inject_absent_rank(self, local_rank: int) -> None:
         """Test hook: the given local rank skips the metadata phase of the following calls (-1 switches it off).
         The other ranks then run into their bounded wait and report a time-out."""

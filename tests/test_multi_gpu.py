@@ -82,3 +82,16 @@ def test_nvls_arrivals_of_the_auxiliary_barriers(module, args):
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert '"check": "ok"' in res.stdout
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs 2 GPUs")
+def test_a_process_that_does_not_join_is_a_timeout_and_the_communicator_recovers():
+    """Failures are made on the host (a process skips a call, then announces a departure); no GPU is faulted.
+    NVLS stays off: a process that fails while bound to a multicast object would disturb the other GPUs."""
+    env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
+    env.pop("RBV_NVLS", None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29691", "-m", "rbruck_alltoallv_b200.utils.fault_case"]
+    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert '"fault_case": "ok"' in res.stdout
