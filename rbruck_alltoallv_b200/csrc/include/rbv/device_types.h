@@ -51,7 +51,8 @@ struct StatusBlock {
   unsigned long long trace[8];  // %globaltimer stamps of CTA 0: 0 start, 1 metadata published,
                                 // 2 metadata complete, 3 own ops issued, 4 all blocks received,
                                 // 5 / 6 before and after the fence that precedes the arrival report, 7 arrivals reported.
-                                // Eager protocol: 1 work items sized, 2 first warp done, 3 first CTA done, 4 last CTA out
+                                // Eager protocol: 1 work items sized, 2 first warp done, 3 first CTA done, 4 last CTA out,
+                                // and with CALL_TRACE 5 latest CTA start, 6 latest CTA done
 };
 
 // Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.

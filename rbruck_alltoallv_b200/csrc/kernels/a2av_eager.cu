@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   if (tid == 0) {
     seq_early = __ldcg(&my->call_seq);
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
+    if (a.flags & CALL_TRACE) atomicMax(&my->status.trace[5], dev::globaltimer());   // latest CTA start
   }
   unsigned seq = 0;
   int parity = 0;
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
     unsigned c = (gwarp + nwarps - (base % nwarps)) % nwarps;
     int oi = 0;
     for (; c < total && alive; c += nwarps) {
-      while (s_prefix[oi + 1] <= c) oi++;
+      oi = dev::find_op(s_prefix, oi, tn, c);
       const Op o = a.ops[t0 + oi];
       const unsigned k = c - s_prefix[oi];
       const int lsrc = o.src - a.proc * L;
@@ -314,6 +315,10 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   __syncthreads();
   if (tid == 0) {
     if (blockIdx.x == 0) my->status.trace[3] = dev::globaltimer();               // first CTA done
+    if (a.flags & CALL_TRACE) {                                                  // latest CTA done, and which one
+      const unsigned long long now = dev::globaltimer();
+      if (atomicMax(&my->status.trace[6], now) < now) my->status.trace[7] = blockIdx.x;
+    }
     __threadfence();
     if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
       my->exit_count = 0;

@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     unsigned c = (gwarp + nwarps - (base % nwarps)) % nwarps;
     int oi = 0;
     for (; c < total; c += nwarps) {
-      while (sm.prefix[oi + 1] <= c) oi++;   // chunks are visited in order: monotone search
+      oi = dev::find_op(sm.prefix, oi, tn, c);   // chunks are visited in order: the search resumes at the last op
       const Op o = a.ops[t0 + oi];
       const unsigned k = c - sm.prefix[oi];
       const unsigned nch = sm.prefix[oi + 1] - sm.prefix[oi];
