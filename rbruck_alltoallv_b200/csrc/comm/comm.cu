@@ -223,6 +223,8 @@ int Context::launch(const Prepared& pc, cudaStream_t stream) {
 void Context::release(Prepared& pc) {
   if (pc.owned_meta) cudaFree(pc.owned_meta);
   pc.owned_meta = nullptr;
+  if (pc.owned_items) cudaFree(pc.owned_items);
+  pc.owned_items = nullptr;
 }
 
 int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const CallOptions& opt,
@@ -250,6 +252,7 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   KernelArgs& ka = out->ka;
   std::memset(&ka, 0, sizeof ka);
   out->owned_meta = nullptr;
+  out->owned_items = nullptr;
   ka.P = P_; ka.L = L_; ka.nproc = nproc_; ka.proc = proc_;
   ka.type_size = ts;
   ka.flags = (opt.flags & CALL_INPLACE) | (trace_ ? (unsigned)CALL_TRACE : 0u);
@@ -468,6 +471,36 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
         items = count_items(ech);
       }
     ka.chunk_bytes = ech;
+    // A persistent call with host-side counts knows every item in advance: the table spares the kernel its sizing
+    // pass (two block-wide barriers and a scan before the first byte moves).  Same rule as the kernel's own pass.
+    if (persistent && !ca.counts_on_device && items < 4e6) {
+      std::vector<unsigned> tab;
+      tab.reserve((size_t)items);
+      bool fits = dp->h_eops.size() < 65536;
+      for (size_t oi = 0; fits && oi < dp->h_eops.size(); oi++) {
+        const Op& o = dp->h_eops[oi];
+        const int lr = o.src - proc_ * L_;
+        unsigned long long b;
+        if (o.flags & 2u) {
+          const long long cap = ca.recvcounts ? (long long)ca.recvcounts[(size_t)lr * P_ + o.origin] : -1;
+          b = cap >= 0 ? std::min<unsigned long long>((unsigned long long)cap * ts, emax) : emax;
+        } else if (o.src_cell < 0) {
+          b = (unsigned long long)ca.sendcounts[(size_t)lr * P_ + o.dest] * ts;
+        } else {
+          b = emax;
+        }
+        const unsigned long long nch = std::max<unsigned long long>(1, (b + ech - 1) / ech);
+        if (nch > 65535) { fits = false; break; }
+        for (unsigned long long k = 0; k < nch; k++) tab.push_back((unsigned)(oi << 16) | (unsigned)k);
+      }
+      if (fits && !tab.empty()) {
+        RBV_CUDA_THROW(cudaMalloc(&out->owned_items, tab.size() * sizeof(unsigned)));
+        RBV_CUDA_THROW(cudaMemcpy(out->owned_items, tab.data(), tab.size() * sizeof(unsigned), cudaMemcpyHostToDevice));
+        ka.items = static_cast<const unsigned*>(out->owned_items);
+        ka.nitems = (unsigned)tab.size();
+        items = (double)tab.size();
+      }
+    }
     int g = opt.grid > 0 ? opt.grid : (int)std::min<double>(max_ctas_, std::max(1.0, std::ceil(items / warps_per_cta)));
     out->grid = std::max(1, std::min(g, max_ctas_));
   }

@@ -54,6 +54,7 @@ struct Prepared {
   int grid = 1;
   bool eager = false;
   void* owned_meta = nullptr;   // device copy of host count arrays that did not fit the kernel parameters
+  void* owned_items = nullptr;  // device copy of the precomputed work-item table (eager protocol)
 };
 
 class Context {

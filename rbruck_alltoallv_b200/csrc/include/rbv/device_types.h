@@ -127,6 +127,8 @@ struct KernelArgs {
   unsigned* op_done;       // [nops] completion counters of multi-chunk ops (zero between calls)
   unsigned long long chunk_bytes;
   unsigned long long eager_payload;  // eager protocol: payload bytes a cell can hold (0: rendezvous protocol)
+  const unsigned* items;             // eager protocol, persistent calls with host-side counts: work item c is
+  unsigned nitems;                   // chunk (items[c] & 0xffff) of op (items[c] >> 16); null: sized in the kernel
   unsigned long long timeout_ns;
   HeapLayout lay;
   char* heap[kMaxProcs];   // heap base of every process as mapped in this process

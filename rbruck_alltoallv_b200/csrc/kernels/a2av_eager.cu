@@ -133,9 +133,22 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   EagerCtx ec{&my->abort_flag, a.timeout_ns, 0u};
   bool alive = true;
 
+  // Persistent calls with host-side counts bring a table of their work items: no sizing pass, no block-wide
+  // barrier before the first byte moves; every warp fetches the call number itself.
+  const bool pre = a.items != nullptr;
+  if (pre) {
+    unsigned sq = 0;
+    if (lane == 0) sq = (tid == 0) ? seq_early : __ldcg(&my->call_seq);
+    seq = __shfl_sync(0xffffffffu, sq, 0);
+    parity = seq & 1;
+    ec.flag = seq + 1u;
+    if (blockIdx.x == 0 && tid == 0) my->status.trace[1] = dev::globaltimer();
+  }
+
   unsigned base = 0;
-  for (int t0 = 0; t0 < a.nops; t0 += kOpTileE) {
+  for (int t0 = 0; t0 < (pre ? 1 : a.nops); t0 += kOpTileE) {
     const int tn = min(kOpTileE, a.nops - t0);
+    if (!pre) {
     for (int i = tid; i < tn; i += blockDim.x) {
       const Op o = a.ops[t0 + i];
       const int lsrc = o.src - a.proc * L;
@@ -178,13 +191,21 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
     }
     __syncthreads();
     if (t0 == 0 && blockIdx.x == 0 && tid == 0) my->status.trace[1] = dev::globaltimer();   // work items sized
-    const unsigned total = s_total;
+    }
+    const unsigned total = pre ? a.nitems : s_total;
     unsigned c = (gwarp + nwarps - (base % nwarps)) % nwarps;
     int oi = 0;
     for (; c < total && alive; c += nwarps) {
-      oi = dev::find_op(s_prefix, oi, tn, c);
+      unsigned k;
+      if (pre) {
+        const unsigned it = __ldg(a.items + c);
+        oi = (int)(it >> 16);
+        k = it & 0xffffu;
+      } else {
+        oi = dev::find_op(s_prefix, oi, tn, c);
+        k = c - s_prefix[oi];
+      }
       const Op o = a.ops[t0 + oi];
-      const unsigned k = c - s_prefix[oi];
       const int lsrc = o.src - a.proc * L;
       const size_t u0 = (size_t)k * (chunk / 8);           // first payload unit of this item
       const size_t cu = chunk / 8;
