@@ -473,10 +473,10 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
     ka.chunk_bytes = ech;
     // A persistent call with host-side counts knows every item in advance: the table spares the kernel its sizing
     // pass (two block-wide barriers and a scan before the first byte moves).  Same rule as the kernel's own pass.
-    if (persistent && !ca.counts_on_device && items < 4e6) {
-      std::vector<unsigned> tab;
+    if (persistent && !ca.counts_on_device && items < 1e6) {
+      std::vector<EagerItem> tab;
       tab.reserve((size_t)items);
-      bool fits = dp->h_eops.size() < 65536;
+      bool fits = true;
       for (size_t oi = 0; fits && oi < dp->h_eops.size(); oi++) {
         const Op& o = dp->h_eops[oi];
         const int lr = o.src - proc_ * L_;
@@ -490,13 +490,12 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
           b = emax;
         }
         const unsigned long long nch = std::max<unsigned long long>(1, (b + ech - 1) / ech);
-        if (nch > 65535) { fits = false; break; }
-        for (unsigned long long k = 0; k < nch; k++) tab.push_back((unsigned)(oi << 16) | (unsigned)k);
+          for (unsigned long long k = 0; k < nch; k++) tab.push_back(EagerItem{o, (unsigned)k, (unsigned)oi});
       }
       if (fits && !tab.empty()) {
-        RBV_CUDA_THROW(cudaMalloc(&out->owned_items, tab.size() * sizeof(unsigned)));
-        RBV_CUDA_THROW(cudaMemcpy(out->owned_items, tab.data(), tab.size() * sizeof(unsigned), cudaMemcpyHostToDevice));
-        ka.items = static_cast<const unsigned*>(out->owned_items);
+        RBV_CUDA_THROW(cudaMalloc(&out->owned_items, tab.size() * sizeof(EagerItem)));
+        RBV_CUDA_THROW(cudaMemcpy(out->owned_items, tab.data(), tab.size() * sizeof(EagerItem), cudaMemcpyHostToDevice));
+        ka.items = static_cast<const EagerItem*>(out->owned_items);
         ka.nitems = (unsigned)tab.size();
         items = (double)tab.size();
       }

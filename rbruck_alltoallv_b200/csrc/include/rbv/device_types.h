@@ -116,6 +116,14 @@ struct InlineMeta {
   long long rdispls[kInlineMeta];
 };
 
+// One precomputed work item of the eager protocol: chunk `k` of op number `index`, with the op itself.
+struct alignas(16) EagerItem {
+  Op op;
+  unsigned k;
+  unsigned index;
+};
+static_assert(sizeof(EagerItem) == 32, "two 16-byte loads per item");
+
 struct KernelArgs {
   int P, L, nproc, proc;
   int type_size;
@@ -127,8 +135,8 @@ struct KernelArgs {
   unsigned* op_done;       // [nops] completion counters of multi-chunk ops (zero between calls)
   unsigned long long chunk_bytes;
   unsigned long long eager_payload;  // eager protocol: payload bytes a cell can hold (0: rendezvous protocol)
-  const unsigned* items;             // eager protocol, persistent calls with host-side counts: work item c is
-  unsigned nitems;                   // chunk (items[c] & 0xffff) of op (items[c] >> 16); null: sized in the kernel
+  const EagerItem* items;            // eager protocol, persistent calls with host-side counts: the work items,
+  unsigned nitems;                   // each with a copy of its op (one load instead of two); null: sized in the kernel
   unsigned long long timeout_ns;
   HeapLayout lay;
   char* heap[kMaxProcs];   // heap base of every process as mapped in this process

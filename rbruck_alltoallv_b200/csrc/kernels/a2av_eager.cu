@@ -197,15 +197,21 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
     int oi = 0;
     for (; c < total && alive; c += nwarps) {
       unsigned k;
+      Op o;
       if (pre) {
-        const unsigned it = __ldg(a.items + c);
-        oi = (int)(it >> 16);
-        k = it & 0xffffu;
+        // the item brings its op along: one 32-byte fetch, nothing that depends on it but the data itself
+        const uint4* ip = reinterpret_cast<const uint4*>(a.items + c);
+        union { uint4 q[2]; EagerItem it; } u;
+        u.q[0] = __ldg(ip);
+        u.q[1] = __ldg(ip + 1);
+        o = u.it.op;
+        k = u.it.k;
+        oi = (int)u.it.index;
       } else {
         oi = dev::find_op(s_prefix, oi, tn, c);
         k = c - s_prefix[oi];
+        o = a.ops[t0 + oi];
       }
-      const Op o = a.ops[t0 + oi];
       const int lsrc = o.src - a.proc * L;
       const size_t u0 = (size_t)k * (chunk / 8);           // first payload unit of this item
       const size_t cu = chunk / 8;
