@@ -38,7 +38,7 @@ namespace {
 constexpr int kOpTile = 1024;
 
 // Tiles per warp of the bulk-copy ring: three where the tables of the communicator leave room in shared memory.
-__host__ __device__ constexpr int a2av_bulk_stages(int P) { return P <= 16 ? 3 : 2; }
+__host__ __device__ constexpr int a2av_bulk_stages(int P) { return P <= 16 ? dev::kBulkMaxStages : 2; }
 
 struct Smem {
   int* counts;
