@@ -16,4 +16,13 @@ def __getattr__(name):
     if name in ("alltoallv", "alltoall", "nccl_alltoallv", "prepare"):
         from .ops import alltoallv as _a
         return getattr(_a, name)
+    if name in ("MoEExpertParallel", "grouped_gemm", "grouped_gemm_fp8"):
+        from .ops import moe as _m
+        return getattr(_m, name)
+    if name == "PencilTranspose":
+        from .ops.fft import PencilTranspose
+        return PencilTranspose
+    if name == "UlyssesExchange":
+        from .ops.ulysses import UlyssesExchange
+        return UlyssesExchange
     raise AttributeError(name)
