@@ -16,6 +16,15 @@ def __getattr__(name):
     if name in ("alltoallv", "alltoall", "nccl_alltoallv", "prepare"):
         from .ops import alltoallv as _a
         return getattr(_a, name)
+    if name == "symm_empty":
+        # receive buffers of the default communicator (peers write into them): rbv.symm_empty(n, dtype)
+        from .parallel import comm as _c
+        return lambda *a, **k: _c.get_default_comm().symm_empty(*a, **k)
+    if name == "bench":
+        # latency table of the default communicator: rbv.bench(sizes=(16, 65536, ...)) -> list of rows
+        from .parallel import comm as _c
+        from .utils import selftest as _s
+        return lambda *a, **k: _s.bench(_c.get_default_comm(), *a, **k)
     if name in ("MoEExpertParallel", "grouped_gemm", "grouped_gemm_fp8"):
         from .ops import moe as _m
         return getattr(_m, name)
