@@ -65,3 +65,10 @@ def test_environment_overrides_take_precedence(monkeypatch):
     monkeypatch.setenv("RBV_PROTOCOL", "carrier-pigeon")
     with pytest.raises(ValueError):
         A._auto_choice(comm, recv, sc, {}, agree_on_max=True)
+
+
+def test_default_choice_for_unmeasured_configurations():
+    small = tuner.default_choice(16, 16, 1024)
+    large = tuner.default_choice(16, 16, 4 << 20)
+    assert small == {"algo": "spreadout", "protocol": "eager"}
+    assert large == {"algo": "spreadout", "protocol": "rendezvous"}
