@@ -28,6 +28,7 @@ CUDA_SOURCES = [
     "comm/comm.cu",
     "kernels/a2av_kernel.cu",
     "kernels/a2av_eager.cu",
+    "kernels/a2av_static.cu",
     "kernels/moe_kernels.cu",
     "kernels/grouped_gemm_sm100.cu",
     "kernels/grouped_gemm_fp8_sm100.cu",
@@ -97,21 +98,45 @@ def cuda_sources():
     return [CSRC / s for s in CUDA_SOURCES if (CSRC / s).exists()]
 
 
+def _compile_one(args):
+    src, obj, flags, verbose = args
+    return _run([_nvcc(), *flags, "-c", f"-I{INCLUDE}", f"-I{CSRC}", str(src), "-o", str(obj)], verbose)
+
+
 def build_cuda(force: bool = False, verbose: bool = False, ptxas_verbose: bool = False) -> Path:
+    """Compiles every source to an object of its own (in parallel; an object is kept while its source, the headers
+    and the flags are unchanged) and links them into ``librbv_cuda.so``."""
+    from concurrent.futures import ThreadPoolExecutor
+
     lib = PKG / "librbv_cuda.so"
     srcs = cuda_sources()
-    flags = list(NVCC_FLAGS)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
     if ptxas_verbose:
         flags += ["-Xptxas", "-v"]
     digest = _hash(srcs + _headers(), flags)
     if force or _needs_build(lib, digest):
+        objdir = PKG / "_obj"
+        objdir.mkdir(exist_ok=True)
+        heads = _headers()
+        jobs, objs = [], []
+        for src in srcs:
+            obj = objdir / (src.stem + ".o")
+            d = _hash([src] + heads, flags)
+            stamp = obj.with_suffix(".stamp")
+            objs.append(obj)
+            if force or not (obj.exists() and stamp.exists() and stamp.read_text().strip() == d):
+                jobs.append((src, obj, flags, verbose, stamp, d))
+        with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+            outs = list(pool.map(_compile_one, [j[:4] for j in jobs]))
+        for j in jobs:
+            j[4].write_text(j[5])
         tmp = lib.with_suffix(f".tmp{os.getpid()}.so")
-        out = _run([_nvcc(), *flags, f"-I{INCLUDE}", f"-I{CSRC}", *map(str, srcs), "-o", str(tmp),
-                    "-lcuda"], verbose)
+        _run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *map(str, objs), "-o", str(tmp), "-lcuda"],
+             verbose)
         os.replace(tmp, lib)
         lib.with_suffix(".stamp").write_text(digest)
         if ptxas_verbose:
-            print(out)
+            print("".join(outs))
     return lib
 
 

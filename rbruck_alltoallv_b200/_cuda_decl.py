@@ -53,6 +53,13 @@ def declare_cuda(lib):
     lib.rbv_prepare.argtypes = [C.c_void_p] + [C.c_int] * 7 + [
         C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
         C.c_int, C.c_longlong, C.c_uint, C.c_int, C.c_size_t]
+    lib.rbv_prepare_global.restype = C.c_void_p
+    lib.rbv_prepare_global.argtypes = lib.rbv_prepare.argtypes + [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.rbv_prepared_info.argtypes = [C.c_void_p, c_ll_p]
+    lib.rbv_ctx_set_static.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_last_trace.argtypes = [C.c_void_p, C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong),
+                                       C.POINTER(C.c_ulonglong), C.c_int]
+    lib.rbv_iteration_count.argtypes = [C.c_void_p]
     lib.rbv_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]

@@ -1,4 +1,6 @@
 // C API: context management and the reference-shaped collective entry points (rbv/rbruckv.h).
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <stdexcept>
@@ -43,7 +45,11 @@ rbv_ctx_t rbv_ctx_create(int nranks, int nproc, int proc, int device, size_t use
   }
 }
 
-void rbv_ctx_destroy(rbv_ctx_t ctx) { delete ctx; }
+void rbv_ctx_destroy(rbv_ctx_t ctx) {
+  if (!ctx) return;
+  if (ctx->cached) rbv_prepared_free(ctx, ctx->cached);
+  delete ctx;
+}
 
 int rbv_ctx_ipc_handle(rbv_ctx_t ctx, void* out64) {
   cudaError_t e = ctx->c->ipc_handle(out64);
@@ -111,10 +117,12 @@ int rbv_alltoallv(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
   }
 }
 
-void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
-                  const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
-                  const int* recvcounts, const long long* sdispls, const long long* rdispls,
-                  int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes) {
+void* rbv_prepare_global(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
+                         const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
+                         const int* recvcounts, const long long* sdispls, const long long* rdispls,
+                         int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes,
+                         const int* g_counts, const int* g_caps, const long long* g_rdispls,
+                         const unsigned long long* g_recvoff) {
   try {
     AlgoSpec s;
     s.algo = algo; s.P = ctx->c->P(); s.n = n; s.r = r; s.r2 = r2; s.b = b; s.b2 = b2;
@@ -123,17 +131,35 @@ void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
     ca.sendcounts = sendcounts; ca.recvcounts = recvcounts; ca.sdispls = sdispls; ca.rdispls = rdispls;
     ca.counts_on_device = counts_on_device != 0;
     ca.bytes_hint = bytes_hint;
+    ca.g_counts = g_counts; ca.g_caps = g_caps; ca.g_rdispls = g_rdispls; ca.g_recvoff = g_recvoff;
     CallOptions opt;
-    opt.grid = grid; opt.chunk_bytes = chunk_bytes; opt.flags = flags;
+    opt.grid = grid; opt.chunk_bytes = chunk_bytes; opt.flags = flags & CALL_INPLACE;
+    opt.allow_static = ctx->allow_static && !(flags & 0x100u);
     opt.eager_max_bytes = ctx->eager;
     auto pc = std::make_unique<Prepared>();
     int rc = ctx->c->prepare(s, type_size, ca, opt, nullptr, true, pc.get());
+    ctx->last_rc = rc;
     if (rc) { g_err = ctx->c->last_error(); return nullptr; }
     return pc.release();
   } catch (const std::exception& e) {
     g_err = e.what();
+    ctx->last_rc = RBV_ERR_BAD_ARG;
     return nullptr;
   }
+}
+void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
+                  const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
+                  const int* recvcounts, const long long* sdispls, const long long* rdispls,
+                  int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes) {
+  return rbv_prepare_global(ctx, algo, n, r, r2, b, b2, type_size, sendbufs, recvbufs, sendcounts, recvcounts, sdispls,
+                            rdispls, counts_on_device, bytes_hint, flags, grid, chunk_bytes, nullptr, nullptr, nullptr,
+                            nullptr);
+}
+// 0 dynamic rendezvous kernel, 1 eager kernel, 2 static rendezvous kernel; out3 = grid, cooperative launch needed, items
+int rbv_prepared_info(void* prepared, long long* out3) {
+  const Prepared* pc = static_cast<Prepared*>(prepared);
+  if (out3) { out3[0] = pc->grid; out3[1] = pc->cooperative ? 1 : 0; out3[2] = pc->is_static ? pc->sa.nitems : pc->ka.nitems; }
+  return pc->is_static ? 2 : (pc->eager ? 1 : 0);
 }
 int rbv_launch(rbv_ctx_t ctx, void* prepared, void* cuda_stream) {
   int rc = ctx->c->launch(*static_cast<Prepared*>(prepared), static_cast<cudaStream_t>(cuda_stream));
@@ -155,20 +181,91 @@ size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx) { return ctx->c->nvls_bytes_needed(); }
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes) { ctx->eager = max_block_bytes; }
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
 void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode) { ctx->c->set_bulk(mode); }
-void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on) { ctx->c->set_cooperative(on != 0); }
+void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int mode) { ctx->c->set_cooperative(mode < 0 ? -1 : (mode ? 1 : 0)); }
+void rbv_ctx_set_static(rbv_ctx_t ctx, int on) { ctx->allow_static = on != 0; }
 
+// Per-key time stamps of the most recent traced call: fills keys[i] (plan key: phase << 24 | step), start_ns[i],
+// end_ns[i] for up to `max` keys and returns the number of keys of the plan (the eager protocol adds one more entry
+// for unpacking, with key 0xffffffff).  Synchronises the context's stream.
+int rbv_ctx_last_trace(rbv_ctx_t ctx, unsigned* keys, unsigned long long* start_ns, unsigned long long* end_ns, int max) {
+  cudaStreamSynchronize(ctx->stream);
+  const DevPlan* dp = ctx->c->last_plan();
+  if (!dp) return 0;
+  const TraceBlock& tb = ctx->c->last_trace();
+  const int nk = (int)dp->plan.keys.size();
+  int n = 0;
+  for (int i = 0; i <= nk && i < kMaxTraceKeys && n < max; i++) {
+    if (i == nk && (tb.kstart[i] == ~0ull || tb.kend[i] == 0)) break;
+    keys[n] = i < nk ? dp->plan.keys[i] : 0xffffffffu;
+    start_ns[n] = tb.kstart[i];
+    end_ns[n] = tb.kend[i];
+    n++;
+  }
+  return n;
+}
+
+// Fills the reference's timer globals (src/twophase_twolayer_rbruck.cpp:10-12, src/twolayer_communicator_linear.cpp:
+// 10-11) from the device stamps of the most recent traced call.  What each name means here:
+//   init_time        kernel start until the first item of the call starts (launch ramp, call number, tables)
+//   findMax_time     metadata publish (the reference's max-count MPI_Allreduce happens in the same exchange)
+//   rotateIndex_time host time spent compiling the schedule (the reference's index-rotation arrays; 0 when cached)
+//   alcCopy_time     self copies (the reference times its allocations and the self memcpy under this name)
+//   getBlock_time    0: block lists are part of the compiled schedule
+//   prepData_time    0: nothing is packed, blocks are read in place
+//   excgMeta_time    waiting for the peers' metadata (or, in the static kernel, for the peers to enter the call)
+//   excgData_time    first to last item of the intra-group / flat Bruck rounds (phase 1 keys)
+//   replace_time     eager protocol: unpacking arrival cells into the receive buffer; otherwise 0
+//   orgData_time     hand-out stage of the leader-routed exchanges (phase 3 keys); otherwise 0
+//   prepSP_time      0: the inter-group displacement tables are part of the compiled schedule
+//   SP_time          first to last item of the inter-group phase (phase 2 keys)
+//   intra_time       same span as excgData_time
+//   iteration_time   one entry per inter-group batch (phase 2 key), malloc'ed here; like in the reference the
+//                    caller frees it (the previous array is not freed by the library)
+// Returns the status code of that call.
 int rbv_update_timers(rbv_ctx_t ctx) {
   StatusBlock s = ctx->c->status(ctx->stream);
   auto sec = [&](int a, int b) { return s.trace[b] > s.trace[a] ? (double)(s.trace[b] - s.trace[a]) * 1e-9 : 0.0; };
-  init_time = 0;
-  // metadata phase = what the reference spends in its max-count allreduce and per-round count exchanges
-  findMax_time = sec(0, 1);
-  excgMeta_time = sec(1, 2);
-  rotateIndex_time = alcCopy_time = getBlock_time = prepData_time = replace_time = orgData_time = prepSP_time = 0;
-  excgData_time = sec(2, 3);
-  SP_time = sec(3, 4);
-  intra_time = sec(2, 3);
+  init_time = findMax_time = rotateIndex_time = alcCopy_time = getBlock_time = prepData_time = excgMeta_time =
+      excgData_time = replace_time = orgData_time = prepSP_time = SP_time = intra_time = 0;
+  iteration_time = nullptr;
+  const DevPlan* dp = ctx->c->last_plan();
+  if (!dp) return s.code;
+  rotateIndex_time = ctx->plan_build_s;
+  const TraceBlock& tb = ctx->c->last_trace();
+  const int nk = std::min<int>((int)dp->plan.keys.size(), kMaxTraceKeys - 1);
+  unsigned long long lo[4] = {~0ull, ~0ull, ~0ull, ~0ull}, hi[4] = {0, 0, 0, 0}, first = ~0ull;
+  std::vector<double> batches;
+  for (int i = 0; i < nk; i++) {
+    if (tb.kstart[i] == ~0ull || tb.kend[i] < tb.kstart[i]) continue;
+    const unsigned ph = std::min(3u, dp->plan.keys[i] >> 24);
+    lo[ph] = std::min(lo[ph], tb.kstart[i]);
+    hi[ph] = std::max(hi[ph], tb.kend[i]);
+    first = std::min(first, tb.kstart[i]);
+    if (ph == 2) batches.push_back((double)(tb.kend[i] - tb.kstart[i]) * 1e-9);
+  }
+  auto span = [&](int ph) { return hi[ph] > lo[ph] && lo[ph] != ~0ull ? (double)(hi[ph] - lo[ph]) * 1e-9 : 0.0; };
+  if (first != ~0ull && first > s.trace[0]) init_time = (double)(first - s.trace[0]) * 1e-9;
+  alcCopy_time = span(0);
+  excgData_time = intra_time = span(1);
+  SP_time = span(2);
+  orgData_time = span(3);
+  if (s.trace[2] > s.trace[1] && s.trace[1] > s.trace[0] && s.trace[2] - s.trace[0] < 1000000000ull) {
+    findMax_time = sec(0, 1);      // dynamic kernel: publish, then wait for the peers' rows
+    excgMeta_time = sec(1, 2);
+  }
+  if (nk < kMaxTraceKeys - 1 && tb.kstart[nk] != ~0ull && tb.kend[nk] > tb.kstart[nk])
+    replace_time = (double)(tb.kend[nk] - tb.kstart[nk]) * 1e-9;
+  if (!batches.empty()) {
+    iteration_time = static_cast<double*>(std::malloc(batches.size() * sizeof(double)));
+    if (iteration_time) std::memcpy(iteration_time, batches.data(), batches.size() * sizeof(double));
+  }
   return s.code;
+}
+int rbv_iteration_count(rbv_ctx_t ctx) {
+  const DevPlan* dp = ctx->c->last_plan();
+  int n = 0;
+  if (dp) for (unsigned k : dp->plan.keys) if ((k >> 24) == 2) n++;
+  return n;
 }
 
 int myPow(int x, unsigned int p) { return ipow(x, p); }
@@ -202,6 +299,7 @@ int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbu
   // argument validation happens in the plan compiler; evaluate it now so that every rank gets the code
   try {
     const DevPlan* dp = c.plan_for(spec);
+    if (c.last_plan_build_s() > 0) ctx->plan_build_s = c.last_plan_build_s();
     if (dp->plan.err) { g_err = dp->plan.errmsg; return dp->plan.err; }
   } catch (const std::exception& e) { g_err = e.what(); return RBV_ERR_BAD_ARG; }
   if (ctx->pend == 0) {
@@ -225,10 +323,28 @@ int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbu
   std::fill(ctx->seen.begin(), ctx->seen.end(), 0);
   bool have_rc = true;
   for (int v : ctx->rc) if (v < 0) have_rc = false;
-  int rc = rbv_alltoallv(ctx, spec.algo, spec.n, spec.r, spec.r2, spec.b, spec.b2, ts, ctx->sendbufs.data(),
-                         ctx->recvbufs.data(), ctx->sc.data(), have_rc ? ctx->rc.data() : nullptr, ctx->sd.data(),
-                         ctx->rd.data(), 0, -1, flags, ctx->grid, ctx->chunk, ctx->stream);
-  return rc;
+  // The call is resolved once and kept: a loop that repeats the same collective (same buffers, counts and
+  // parameters) pays for the resolution once and then for one kernel launch per iteration.
+  std::vector<char> key;
+  auto put = [&](const void* p, size_t n) { key.insert(key.end(), static_cast<const char*>(p), static_cast<const char*>(p) + n); };
+  put(&spec, sizeof spec); put(&ts, sizeof ts); put(&flags, sizeof flags); put(&ctx->eager, sizeof ctx->eager);
+  put(&ctx->grid, sizeof ctx->grid); put(&ctx->chunk, sizeof ctx->chunk); put(&have_rc, sizeof have_rc);
+  put(ctx->sendbufs.data(), ctx->sendbufs.size() * sizeof(void*));
+  put(ctx->recvbufs.data(), ctx->recvbufs.size() * sizeof(void*));
+  put(ctx->sc.data(), ctx->sc.size() * sizeof(int)); put(ctx->rc.data(), ctx->rc.size() * sizeof(int));
+  put(ctx->sd.data(), ctx->sd.size() * sizeof(long long)); put(ctx->rd.data(), ctx->rd.size() * sizeof(long long));
+  if (!ctx->cached || key != ctx->cached_key) {
+    if (ctx->cached) { cudaStreamSynchronize(ctx->stream); rbv_prepared_free(ctx, ctx->cached); ctx->cached = nullptr; }
+    ctx->cached = rbv_prepare(ctx, spec.algo, spec.n, spec.r, spec.r2, spec.b, spec.b2, ts, ctx->sendbufs.data(),
+                              ctx->recvbufs.data(), ctx->sc.data(), have_rc ? ctx->rc.data() : nullptr, ctx->sd.data(),
+                              ctx->rd.data(), 0, -1, flags, ctx->grid, ctx->chunk);
+    if (!ctx->cached) {
+      ctx->cached_key.clear();
+      return ctx->last_rc ? ctx->last_rc : (int)RBV_ERR_BAD_ARG;
+    }
+    ctx->cached_key.swap(key);
+  }
+  return rbv_launch(ctx, ctx->cached, ctx->stream);
 }
 
 AlgoSpec mk(int algo, int n = 0, int r = 2, int r2 = 0, int b = 0, int b2 = 0) {
@@ -284,6 +400,11 @@ int twolayer_communicator_linear_s3(int n, int bblock1, int bblock2, RBV_V_ARGS)
 int twolayer_communicator_linear_s4(int n, int bblock1, int bblock2, RBV_V_ARGS) {
   return RBV_V_PASS(mk(ALG_TWOLAYER_LINEAR_S4, n, 2, 0, bblock1, bblock2), 0);
 }
+// benchmarks/merge_benchmark.cpp:155-332, benchmarks/simple_merge_benchmark.cpp:138-210,
+// benchmarks/split_benchmark.cpp:147-205 (functions of the reference's benchmark programs, same argument order)
+int merge_alltoallv(int ncores, RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_MERGE, ncores), 0); }
+int simply_merge_alltoallv(int ncores, RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_SIMPLE_MERGE, ncores), 0); }
+int split_alltoallv(RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_SPLIT), 0); }
 int ML_benchmark(RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_SPREADOUT), 0); }
 void spreadout_alltoallv(RBV_V_ARGS) { (void)RBV_V_PASS(mk(ALG_SPREADOUT), 0); }
 

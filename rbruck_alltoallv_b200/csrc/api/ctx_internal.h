@@ -20,6 +20,13 @@ struct rbv_ctx_s {
   int grid = 0;
   size_t chunk = 0;
   unsigned long long eager = 0;   // cell payload bytes of the eager protocol for the following calls (0: off)
+  bool allow_static = true;       // persistent calls with host-side counts may run the static kernel
+  double plan_build_s = 0;        // host time spent compiling the schedule of the latest call (0: it was cached)
+  // per-rank entry points: the resolved call of the previous collective, reused when the next one has the same
+  // arguments (a loop over one collective then costs one kernel launch per iteration)
+  void* cached = nullptr;
+  int last_rc = 0;                // return code of the latest rbv_prepare*
+  std::vector<char> cached_key;
   std::vector<rbv_comm_s> comms;
   // calls of the local ranks collected until all L have arrived
   int pend = 0;

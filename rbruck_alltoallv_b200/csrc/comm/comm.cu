@@ -1,6 +1,7 @@
 // Context implementation: heap layout, CUDA IPC peer mapping, symmetric allocator, plan cache and
 // the launch path of the alltoallv kernel.
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -40,19 +41,26 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   max_ctas_ = sm_count_ * per_sm;
   bulk_ctas_ = sm_count_ * std::max(0, std::min(a2av_bulk_ctas_per_sm(P), 1));
   if (const char* e = std::getenv("RBV_BULK")) bulk_mode_ = std::atoi(e);
-  if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_ = std::atoi(e) != 0;
+  if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_mode_ = std::atoi(e) != 0 ? 1 : 0;
+  if (const char* e = std::getenv("RBV_STATIC_OCC")) static_occ_ = std::atoi(e) >= 2 ? 2 : 1;
+  int st_per_sm = 1;
+  RBV_CUDA_THROW(a2av_static_configure(static_occ_, &st_per_sm));
+  static_max_ctas_ = sm_count_ * std::max(1, std::min(st_per_sm, 2));
 
   lay_.ctrl_off = 0;
-  lay_.flags_off = align_up(sizeof(CtrlBlock), 256);
-  lay_.meta_off = lay_.flags_off + align_up(sizeof(unsigned) * 2ull * L_ * kMaxCellsPerRank, 256);
+  lay_.trace_off = align_up(sizeof(CtrlBlock), 256);
+  lay_.flags_off = lay_.trace_off + align_up(sizeof(TraceBlock), 256);
+  lay_.flags_per_rank = kMaxFlagsPerRank;
+  lay_.meta_off = lay_.flags_off + align_up(sizeof(unsigned) * 2ull * L_ * lay_.flags_per_rank, 256);
   lay_.meta_bytes = meta_table_bytes(P);
   lay_.stage_off = align_up(lay_.meta_off + 2 * lay_.meta_bytes, 4096);
   lay_.arena_bytes = align_up(arena_bytes, 4096);
-  lay_.user_off = lay_.stage_off + 2ull * L_ * lay_.arena_bytes;
+  lay_.eager_off = lay_.stage_off + 2ull * L_ * lay_.arena_bytes;
+  lay_.user_off = lay_.eager_off + 2ull * L_ * lay_.arena_bytes;
   lay_.total_bytes = lay_.user_off + align_up(user_bytes, 4096);
 
   RBV_CUDA_THROW(cudaMalloc(&heap_, lay_.total_bytes));
-  RBV_CUDA_THROW(cudaMemset(heap_, 0, lay_.stage_off));
+  RBV_CUDA_THROW(clear_library_regions());
   peer_[proc] = heap_;
   opened_[proc] = false;
   free_[lay_.user_off] = lay_.total_bytes - lay_.user_off;
@@ -60,7 +68,19 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   RBV_CUDA_THROW(cudaHostAlloc(&host_status_, sizeof(StatusBlock), cudaHostAllocMapped));
   std::memset(host_status_, 0, sizeof(StatusBlock));
   RBV_CUDA_THROW(cudaHostGetDevicePointer(&host_status_dev_, host_status_, 0));
+  RBV_CUDA_THROW(cudaHostAlloc(&host_trace_, sizeof(TraceBlock), cudaHostAllocMapped));
+  std::memset(host_trace_, 0, sizeof(TraceBlock));
+  RBV_CUDA_THROW(cudaHostGetDevicePointer(&host_trace_dev_, host_trace_, 0));
   RBV_CUDA_THROW(cudaDeviceSynchronize());
+}
+
+// Everything in front of the user region starts at zero: counters, chunk flags, metadata tables, and both kinds of
+// arena.  The eager cells in particular must not show flag words of an earlier life of this memory (a heap from
+// cudaMalloc can be the memory of a context that was destroyed, and reset() restarts the call numbers).
+cudaError_t Context::clear_library_regions() {
+  cudaError_t e = cudaMemset(heap_, 0, lay_.user_off);
+  if (e != cudaSuccess) return e;
+  return cudaMemset(heap_ + lay_.trace_off + offsetof(TraceBlock, kstart), 0xff, sizeof(TraceBlock::kstart));
 }
 
 Context::~Context() {
@@ -79,6 +99,7 @@ Context::~Context() {
     if (ring_ev_[i]) cudaEventDestroy(ring_ev_[i]);
   }
   if (host_status_) cudaFreeHost(host_status_);
+  if (host_trace_) cudaFreeHost(host_trace_);
   if (heap_) cudaFree(heap_);
 }
 
@@ -151,9 +172,12 @@ bool Context::in_heap(const void* p, size_t bytes) const {
 const DevPlan* Context::plan_for(const AlgoSpec& s) {
   auto key = std::make_tuple(s.algo, s.P, s.n, s.r, s.r2, s.b, s.b2);
   auto it = plans_.find(key);
+  last_plan_build_s_ = 0;
   if (it != plans_.end()) return it->second.get();
   auto dp = std::make_unique<DevPlan>();
+  const auto t_build = std::chrono::steady_clock::now();
   dp->plan = build_plan(s);
+  last_plan_build_s_ = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_build).count();
   if (!dp->plan.err) {
     if (dp->plan.ncells > kMaxCellsPerRank) {
       dp->plan.err = -3;
@@ -163,6 +187,8 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
       for (int i = 0; i < L_; i++) mine[i] = proc_ * L_ + i;
       std::vector<Op> ops = ops_for_ranks(dp->plan, mine);
       dp->nops = (int)ops.size();
+      dp->h_ops = ops;
+      for (const Op& o : dp->plan.ops) if (op_nparts(o)) dp->has_parts = true;
       if (dp->nops) {
         RBV_CUDA_THROW(cudaMalloc(&dp->d_ops, ops.size() * sizeof(Op)));
         RBV_CUDA_THROW(cudaMemcpy(dp->d_ops, ops.data(), ops.size() * sizeof(Op), cudaMemcpyHostToDevice));
@@ -185,7 +211,8 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
           if (s == d) continue;
           Op u{};
           u.src = u.dst = u.dest = (uint16_t)d; u.origin = (uint16_t)s;
-          u.src_cell = s; u.dst_cell = -1; u.key = 0xffffffffu; u.flags = 2u;
+          u.src_cell = s; u.dst_cell = -1; u.key = 0xffffffffu;
+          u.flags = kOpUnpack | ((uint32_t)dp->plan.keys.size() << 16);   // unpacking is timed as a key of its own
           eops.push_back(u);
         }
       }
@@ -211,8 +238,11 @@ int Context::alltoallv(const AlgoSpec& spec, int ts, const CallArgs& ca, const C
 }
 
 int Context::launch(const Prepared& pc, cudaStream_t stream) {
-  cudaError_t e = pc.eager ? a2av_eager_launch(pc.ka, pc.grid, cooperative_, stream)
-                           : a2av_launch(pc.ka, pc.grid, cooperative_, stream);
+  // cooperative_mode_: 1 always cooperative, 0 never (in-place calls excepted), -1 only for calls that need it
+  const bool coop = cooperative_mode_ > 0 || (cooperative_mode_ < 0 && pc.cooperative);
+  cudaError_t e = pc.is_static ? a2av_static_launch(pc.sa, pc.grid, static_occ_, coop, stream)
+                  : pc.eager   ? a2av_eager_launch(pc.ka, pc.grid, coop, stream)
+                               : a2av_launch(pc.ka, pc.grid, coop, stream);
   if (e != cudaSuccess) {
     last_error_ = std::string("kernel launch failed: ") + cudaGetErrorString(e);
     return RBV_ERR_BAD_ARG;
@@ -233,12 +263,16 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   spec.P = P_;
   const DevPlan* dp = plan_for(spec);
   if (dp->plan.err) { last_error_ = dp->plan.errmsg; return dp->plan.err; }
+  last_plan_ = dp;
   if (ts < 1) { last_error_ = "type size must be positive"; return RBV_ERR_BAD_ARG; }
   const bool inplace = (opt.flags & CALL_INPLACE) != 0;
   const bool eager = opt.eager_max_bytes > 0;
   const unsigned long long emax = (opt.eager_max_bytes + 7) & ~7ull;
+  out->is_static = false;
+  out->cooperative = true;
   if (eager) {
     if (inplace) { last_error_ = "the eager protocol does not take in-place calls"; return RBV_ERR_BAD_ARG; }
+    if (dp->has_parts) { last_error_ = "a schedule that sends a block in slices needs the rendezvous protocol"; return RBV_ERR_BAD_ARG; }
     if ((unsigned long long)(P_ + dp->plan.ncells) * (16 + 2 * emax) > lay_.arena_bytes) {
       last_error_ = "staging arena too small for the eager cells of this plan";
       return RBV_ERR_CAPACITY;
@@ -249,10 +283,36 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
     last_error_ = "null argument"; return RBV_ERR_BAD_ARG;
   }
 
-  KernelArgs& ka = out->ka;
-  std::memset(&ka, 0, sizeof ka);
   out->owned_meta = nullptr;
   out->owned_items = nullptr;
+  for (int q = 0; q < nproc_; q++)
+    if (!peer_[q]) { last_error_ = "peer heaps are not connected"; return RBV_ERR_BAD_ARG; }
+  // With host-side counts the receive extents are known: a buffer that ends beyond the heap is refused here
+  // instead of letting peers store outside their mapping of it.
+  if (!ca.counts_on_device && !eager) {
+    for (int lr = 0; lr < L_; lr++) {
+      long long ext = 0;
+      for (int s2 = 0; s2 < P_; s2++) {
+        long long cnt = 0;
+        if (ca.recvcounts) cnt = ca.recvcounts[(size_t)lr * P_ + s2];
+        else if (ca.g_counts) cnt = ca.g_counts[(size_t)s2 * P_ + (proc_ * L_ + lr)];
+        else if (L_ == P_) cnt = ca.sendcounts[(size_t)s2 * P_ + lr];
+        ext = std::max(ext, (ca.rdispls[(size_t)lr * P_ + s2] + std::max(cnt, 0ll)) * ts);
+      }
+      if (!in_heap(ca.recvbufs[lr], (size_t)std::max(ext, 1ll))) {
+        last_error_ = "recvbuf must lie inside the symmetric heap with room for every block (displacement + count)";
+        return RBV_ERR_BAD_ARG;
+      }
+    }
+  }
+  // A persistent call whose counts are all on the host (own ranks only when this process hosts every rank, or the
+  // gathered tables) is resolved into copy descriptors here and runs the static kernel.
+  if (persistent && opt.allow_static && !ca.counts_on_device && !eager && !inplace && absent_rank_ < 0 &&
+      (nproc_ == 1 || (ca.g_counts && ca.g_rdispls && ca.g_recvoff)))
+    return prepare_static(dp, ts, ca, opt, out);
+
+  KernelArgs& ka = out->ka;
+  std::memset(&ka, 0, sizeof ka);
   ka.P = P_; ka.L = L_; ka.nproc = nproc_; ka.proc = proc_;
   ka.type_size = ts;
   ka.flags = (opt.flags & CALL_INPLACE) | (trace_ ? (unsigned)CALL_TRACE : 0u);
@@ -263,11 +323,9 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   ka.op_done = dp->d_done;
   ka.timeout_ns = timeout_ns_;
   ka.lay = lay_;
-  for (int q = 0; q < nproc_; q++) {
-    if (!peer_[q]) { last_error_ = "peer heaps are not connected"; return RBV_ERR_BAD_ARG; }
-    ka.heap[q] = peer_[q];
-  }
+  for (int q = 0; q < nproc_; q++) ka.heap[q] = peer_[q];
   ka.host_status = host_status_dev_;
+  ka.host_trace = host_trace_dev_;
   ka.meta_self = nvls_mc_ ? nvls_self_ : heap_ + lay_.meta_off;
   ka.meta_mc = nvls_mc_;
   for (int lr = 0; lr < L_; lr++) {
@@ -432,6 +490,9 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   ka.chunk_bytes = chunk;
   out->grid = grid;
   out->eager = eager;
+  // A direct schedule has no CTA that waits for another CTA of the same grid (the final wait of CTA 0 holds no one
+  // up), so it does not need the residency guarantee of a cooperative launch.
+  out->cooperative = dp->plan.ncells > 0 || inplace;
   if (eager) {
     ka.ops = dp->d_eops;
     ka.nops = dp->n_eops;
@@ -502,7 +563,189 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
     }
     int g = opt.grid > 0 ? opt.grid : (int)std::min<double>(max_ctas_, std::max(1.0, std::ceil(items / warps_per_cta)));
     out->grid = std::max(1, std::min(g, max_ctas_));
+    // Items wait for units that other items send.  A sender never waits, and items are listed senders first, so a
+    // grid that covers all items in one round cannot block itself as long as CTAs start in index order; with one
+    // rank per GPU and no relay hops every wait is for another GPU anyway.  Everything else is launched cooperatively.
+    out->cooperative = !((L_ == 1 && dp->plan.ncells == 0) || items <= (double)out->grid * warps_per_cta);
   }
+  return 0;
+}
+
+namespace {
+// Chunk size of the rendezvous copy loops for `work` bytes moved by one process (forwarded hops included): a chunk
+// is one warp's unit of work, at most 64 KB and at least 2 KB.  Chunks are dealt to the resident warps in turn, so
+// the byte count is cut into a whole number of rounds: with 64 KB chunks and 1.8 rounds a tenth of the warps would
+// work alone at the end.  Measured on B200: with fewer, larger chunks most warps idle and a 4 MB exchange takes
+// twice as long.
+unsigned long long chunk_for(double work, int max_ctas) {
+  const double warps = 1.0 * max_ctas * (kThreads / 32);
+  const double rounds = std::max(1.0, std::ceil(work / (warps * 64.0 * 1024)));
+  const double c = work / (warps * rounds);
+  unsigned long long chunk = (unsigned long long)std::min(64.0 * 1024, std::max(2.0 * 1024, c));
+  return align_up(chunk, 1024);
+}
+}  // namespace
+
+int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const CallOptions& opt, Prepared* out) {
+  const int P = P_, L = L_, first = proc_ * L_;
+  // ---- the communicator-wide tables ----
+  std::vector<int> own_counts, own_caps;
+  std::vector<long long> own_rd;
+  std::vector<unsigned long long> own_ro;
+  const int* gc = ca.g_counts;
+  const int* gcap = ca.g_caps;
+  const long long* grd = ca.g_rdispls;
+  const unsigned long long* gro = ca.g_recvoff;
+  if (!gc) {   // this process hosts every rank
+    own_counts.assign(ca.sendcounts, ca.sendcounts + (size_t)P * P);
+    own_rd.assign(ca.rdispls, ca.rdispls + (size_t)P * P);
+    own_ro.resize(P);
+    for (int d = 0; d < P; d++) own_ro[d] = (unsigned long long)(static_cast<char*>(ca.recvbufs[d]) - heap_);
+    if (ca.recvcounts) { own_caps.assign(ca.recvcounts, ca.recvcounts + (size_t)P * P); gcap = own_caps.data(); }
+    gc = own_counts.data(); grd = own_rd.data(); gro = own_ro.data();
+  }
+  long long maxcount = 0;
+  for (size_t i = 0; i < (size_t)P * P; i++) {
+    if (gc[i] < 0 || grd[i] < 0) { last_error_ = "negative count or displacement"; return RBV_ERR_BAD_ARG; }
+    maxcount = std::max<long long>(maxcount, gc[i]);
+  }
+  for (size_t i = 0; i < (size_t)L * P; i++)
+    if (ca.sdispls[i] < 0) { last_error_ = "negative count or displacement"; return RBV_ERR_BAD_ARG; }
+  if (gcap)
+    for (int s = 0; s < P; s++)
+      for (int d = 0; d < P; d++)
+        if (gcap[(size_t)d * P + s] >= 0 && gc[(size_t)s * P + d] > gcap[(size_t)d * P + s]) {
+          last_error_ = "block " + std::to_string(s) + " -> " + std::to_string(d) + " is larger than the receiver's recvcount";
+          return RBV_ERR_TRUNCATE;
+        }
+  for (int d = 0; d < P; d++) {
+    unsigned long long ext = 0;
+    for (int s = 0; s < P; s++)
+      ext = std::max(ext, (unsigned long long)(grd[(size_t)d * P + s] + gc[(size_t)s * P + d]) * ts);
+    if (gro[d] < lay_.user_off || gro[d] + ext > lay_.total_bytes) {
+      last_error_ = "receive buffer of rank " + std::to_string(d) + " does not fit inside the symmetric heap";
+      return RBV_ERR_BAD_ARG;
+    }
+  }
+  const size_t stride = align_up((size_t)maxcount * ts, 16);
+  const int ncells = dp->plan.ncells;
+  if (ncells > 0 && stride * (size_t)ncells > lay_.arena_bytes) {
+    last_error_ = "staging arena too small: " + std::to_string(ncells) + " cells of " + std::to_string(stride) + " bytes";
+    return RBV_ERR_CAPACITY;
+  }
+  auto slice_bytes = [&](const Op& o, long long* first_el) {
+    long long f = 0, n = 0;
+    op_slice(o, gc[(size_t)o.origin * P + o.dest], &f, &n);
+    if (first_el) *first_el = f;
+    return (unsigned long long)n * ts;
+  };
+  // ---- chunk size: the same on every process (receivers count chunks), so it is derived from the busiest process ----
+  unsigned long long chunk = opt.chunk_bytes;
+  if (!chunk) {
+    std::vector<double> work(nproc_, 0.0);
+    for (const Op& o : dp->plan.ops) work[o.src / L] += (double)slice_bytes(o, nullptr);
+    chunk = chunk_for(*std::max_element(work.begin(), work.end()), static_max_ctas_);
+  }
+  chunk = align_up(chunk, 16);
+  const unsigned long long fpc = ncells > 0 ? lay_.flags_per_rank / (unsigned long long)ncells : 0;
+  if (ncells > 0) chunk = std::max<unsigned long long>(chunk, align_up((stride + fpc - 1) / fpc, 16));
+  if (chunk > 0xffffffffull) chunk = 0xfffffff0ull;
+  auto nchunks = [&](unsigned long long bytes) { return (bytes + chunk - 1) / chunk; };
+
+  // ---- items of this process: plan order.  Across GPUs the chunks of the ops of one key alternate, so that a rank
+  // writes to all peers of a round at once (with one block after the other, two senders meet at one receiver while
+  // another receiver idles as soon as block sizes differ).  Inside one GPU the copies are bound by HBM, where
+  // walking block after block measured 4-8 % faster than alternating (better DRAM page locality). ----
+  const bool alternate = nproc_ > 1;
+  std::vector<StaticItem> items;
+  const std::vector<Op>& ops = dp->h_ops;
+  auto stage_addr = [&](int proc, int lr, int cell) {
+    return reinterpret_cast<unsigned long long>(peer_[proc]) + lay_.stage_off + (unsigned long long)(lr * 2) * lay_.arena_bytes +
+           (unsigned long long)cell * stride;
+  };
+  for (size_t g0 = 0; g0 < ops.size();) {
+    size_t g1 = g0;
+    while (g1 < ops.size() && ops[g1].key == ops[g0].key) g1++;
+    unsigned long long maxn = 0;
+    for (size_t i = g0; i < g1; i++) maxn = std::max(maxn, nchunks(slice_bytes(ops[i], nullptr)));
+    // (outer, inner) = (chunk, op) when alternating, (op, chunk) otherwise
+    const unsigned long long n_outer = alternate ? maxn : (unsigned long long)(g1 - g0);
+    const unsigned long long n_inner = alternate ? (unsigned long long)(g1 - g0) : maxn;
+    for (unsigned long long outer = 0; outer < n_outer; outer++)
+      for (unsigned long long inner = 0; inner < n_inner; inner++) {
+        const unsigned long long k = alternate ? outer : inner;
+        const size_t i = g0 + (size_t)(alternate ? inner : outer);
+        const Op& o = ops[i];
+        long long f = 0;
+        const unsigned long long bytes = slice_bytes(o, &f);
+        if (k >= nchunks(bytes)) continue;
+        const int lsrc = o.src - first, dproc = o.dst / L, ldst = o.dst - dproc * L;
+        const unsigned long long off = k * chunk;
+        StaticItem it{};
+        it.len = (unsigned)std::min<unsigned long long>(chunk, bytes - off);
+        it.dst_rank = o.dst;
+        unsigned fl = 0;
+        if (o.src_cell < 0) {
+          it.src = reinterpret_cast<unsigned long long>(ca.sendbufs[lsrc]) +
+                   (unsigned long long)(ca.sdispls[(size_t)lsrc * P + o.dest] + f) * ts + off;
+          it.wait_flag = kNoFlag;
+        } else {
+          it.src = stage_addr(proc_, lsrc, o.src_cell) + off;
+          it.wait_flag = (unsigned)((unsigned long long)lsrc * lay_.flags_per_rank + (unsigned long long)o.src_cell * fpc + k);
+          fl |= ITEM_SRC_STAGE;
+        }
+        if (o.dst_cell < 0) {
+          it.dst = reinterpret_cast<unsigned long long>(peer_[dproc]) + gro[o.dst] +
+                   (unsigned long long)(grd[(size_t)o.dst * P + o.origin] + f) * ts + off;
+          it.signal_flag = kNoFlag;
+        } else {
+          it.dst = stage_addr(dproc, ldst, o.dst_cell) + off;
+          it.signal_flag = (unsigned)((unsigned long long)ldst * lay_.flags_per_rank + (unsigned long long)o.dst_cell * fpc + k);
+          fl |= ITEM_DST_STAGE;
+        }
+        if (dproc != proc_) fl |= ITEM_REMOTE;
+        if (o.flags & kOpSelf) fl |= ITEM_SELF;
+        it.flags = (unsigned short)(fl | (std::min<unsigned>(op_key_index(o), 255u) << 8));
+        items.push_back(it);
+      }
+    g0 = g1;
+  }
+  // chunks that land in the receive buffers of this process's ranks, from every process
+  std::vector<unsigned long long> expect(L, 0);
+  for (const Op& o : dp->plan.ops)
+    if (o.dst_cell < 0 && o.dst / L == proc_) expect[o.dst - first] += nchunks(slice_bytes(o, nullptr));
+
+  // ---- device copy: [expect[L] | items] ----
+  const size_t head = align_up(sizeof(unsigned long long) * L, 32);
+  const size_t bytes = head + std::max<size_t>(items.size(), 1) * sizeof(StaticItem);
+  std::vector<char> blob(bytes, 0);
+  std::memcpy(blob.data(), expect.data(), sizeof(unsigned long long) * L);
+  if (!items.empty()) std::memcpy(blob.data() + head, items.data(), items.size() * sizeof(StaticItem));
+  RBV_CUDA_THROW(cudaMalloc(&out->owned_items, bytes));
+  RBV_CUDA_THROW(cudaMemcpy(out->owned_items, blob.data(), bytes, cudaMemcpyHostToDevice));
+
+  StaticArgs& sa = out->sa;
+  std::memset(&sa, 0, sizeof sa);
+  sa.P = P; sa.L = L; sa.nproc = nproc_; sa.proc = proc_;
+  sa.flags = trace_ ? (unsigned)CALL_TRACE : 0u;
+  sa.nitems = (unsigned)items.size();
+  sa.expect = static_cast<const unsigned long long*>(out->owned_items);
+  sa.items = reinterpret_cast<const StaticItem*>(static_cast<char*>(out->owned_items) + head);
+  sa.timeout_ns = timeout_ns_;
+  sa.lay = lay_;
+  for (int q = 0; q < nproc_; q++) sa.heap[q] = peer_[q];
+  sa.host_status = host_status_dev_;
+  sa.host_trace = host_trace_dev_;
+  if (items.size() <= (size_t)kInlineItems) std::memcpy(sa.inl, items.data(), items.size() * sizeof(StaticItem));
+  const int warps_per_cta = kThreads / 32;
+  int grid = opt.grid > 0 ? opt.grid : (int)((items.size() + warps_per_cta - 1) / warps_per_cta);
+  out->grid = std::max(1, std::min(grid, static_max_ctas_));
+  out->is_static = true;
+  out->eager = false;
+  // Only items that forward a staged chunk wait for other items; those come later in the list than what they wait
+  // for, on every process.  With one round of items per warp that order cannot block as long as CTAs start in index
+  // order; several rounds per warp need all CTAs resident.
+  out->cooperative = ncells > 0 && items.size() > (size_t)out->grid * warps_per_cta;
   return 0;
 }
 
@@ -528,12 +771,13 @@ cudaError_t Context::reset() {
   if (e != cudaSuccess) return e;
   e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return e;
-  e = cudaMemset(heap_, 0, lay_.stage_off);
+  e = clear_library_regions();
   if (e != cudaSuccess) return e;
   if (nvls_self_) cudaMemset(nvls_self_, 0, nvls_bytes_needed());
   for (auto& kv : plans_)
     if (kv.second->d_done) cudaMemset(kv.second->d_done, 0, kv.second->nops * sizeof(unsigned));
   std::memset(host_status_, 0, sizeof(StatusBlock));
+  std::memset(host_trace_, 0, sizeof(TraceBlock));
   return cudaDeviceSynchronize();
 }
 

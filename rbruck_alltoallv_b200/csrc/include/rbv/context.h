@@ -19,6 +19,8 @@ namespace rbv {
 struct DevPlan {
   Plan plan;               // host copy (all ranks)
   Op* d_ops = nullptr;     // ops of this process's ranks
+  std::vector<Op> h_ops;   // host copy of the same list
+  bool has_parts = false;  // some block travels in slices (split_alltoallv)
   unsigned* d_done = nullptr;
   int nops = 0;
   // eager protocol: the same ops retargeted at arrival / staging cells, followed by one unpack op per
@@ -33,6 +35,7 @@ struct CallOptions {
   unsigned long long chunk_bytes = 0; // 0 = choose
   unsigned flags = 0;                 // CALL_INPLACE
   unsigned long long eager_max_bytes = 0;  // > 0: eager protocol with cells of this payload size (same on all ranks)
+  bool allow_static = true;           // persistent calls with host-side counts may resolve everything on the host
 };
 
 // Arguments of one collective call for all L local ranks.  Count arrays are [L][P].
@@ -45,6 +48,14 @@ struct CallArgs {
   const long long* rdispls = nullptr;
   bool counts_on_device = false;           // the four arrays are device memory
   long long bytes_hint = -1;               // total bytes sent by this process, if known (device counts)
+  // The whole communicator's arguments, when the caller has gathered them on the host (all null otherwise):
+  // g_counts[s * P + d] = sendcounts of rank s, g_caps[d * P + s] = recvcounts of rank d (-1: unchecked; the array
+  // may be null), g_rdispls[d * P + s], g_recvoff[d] = offset of rank d's receive buffer in its process's heap.
+  // A process that hosts every rank needs none of them: its own arguments are the whole picture.
+  const int* g_counts = nullptr;
+  const int* g_caps = nullptr;
+  const long long* g_rdispls = nullptr;
+  const unsigned long long* g_recvoff = nullptr;
 };
 
 // A fully resolved call: launching it again repeats the collective with the same buffers and counts
@@ -53,6 +64,9 @@ struct Prepared {
   KernelArgs ka;
   int grid = 1;
   bool eager = false;
+  bool is_static = false;       // runs the static kernel with `sa`; `ka` is unused then
+  bool cooperative = true;      // launch mode this call needs (false: a plain launch is safe)
+  StaticArgs sa;
   void* owned_meta = nullptr;   // device copy of host count arrays that did not fit the kernel parameters
   void* owned_items = nullptr;  // device copy of the precomputed work-item table (eager protocol)
 };
@@ -92,9 +106,11 @@ class Context {
               cudaStream_t stream, bool persistent, Prepared* out);
   int launch(const Prepared& pc, cudaStream_t stream);
   void release(Prepared& pc);
-  // Cooperative launches guarantee that all CTAs are resident (needed when other kernels share the GPU);
-  // a plain launch is a little cheaper.  Default: cooperative; RBV_COOPERATIVE=0 switches it off.
-  void set_cooperative(bool on) { cooperative_ = on; }
+  // Cooperative launches guarantee that all CTAs are resident; a plain launch is a little cheaper.  Default (-1):
+  // cooperative only for calls in which a CTA may wait for work of a later CTA of the same grid (store-and-forward
+  // schedules with more items than resident warps); 1: always; 0: never, except for in-place calls, whose grid-wide
+  // barrier needs it.  RBV_COOPERATIVE=0/1 sets the same.
+  void set_cooperative(int mode) { cooperative_mode_ = mode; }
   // Copy the phase time stamps to the host after every call (off: only failing calls report).
   void set_trace(bool on) { trace_ = on; }
   // Bulk-copy engine for large chunks: 0 = never (default), 1 = whenever the buffers allow it, -1 = by size
@@ -104,6 +120,11 @@ class Context {
 
   // First error since the last status() call (0 if none); synchronises `stream` first.
   StatusBlock status(cudaStream_t stream);
+  // Per-key time stamps of the most recent traced call (valid after status() has synchronised), and the plan
+  // that call ran (null before the first call).
+  const TraceBlock& last_trace() const { return *host_trace_; }
+  const DevPlan* last_plan() const { return last_plan_; }
+  double last_plan_build_s() const { return last_plan_build_s_; }
   // Clears all synchronisation state.  Every process must call it between the same two calls,
   // with a host barrier before and after.
   cudaError_t reset();
@@ -134,7 +155,8 @@ class Context {
   char* heap_ = nullptr;
   char* peer_[kMaxProcs] = {};
   bool opened_[kMaxProcs] = {};
-  bool cooperative_ = true;
+  int cooperative_mode_ = -1;
+  cudaError_t clear_library_regions();
   bool trace_ = false;
   int bulk_mode_ = 0;
   int bulk_ctas_ = 0;
@@ -146,6 +168,13 @@ class Context {
   int max_ctas_ = 1, sm_count_ = 1;
   StatusBlock* host_status_ = nullptr;
   StatusBlock* host_status_dev_ = nullptr;
+  TraceBlock* host_trace_ = nullptr;
+  TraceBlock* host_trace_dev_ = nullptr;
+  const DevPlan* last_plan_ = nullptr;
+  double last_plan_build_s_ = 0;   // host time spent compiling the plan of the last prepare() (0: cached)
+  int static_max_ctas_ = 1;
+  int static_occ_ = 1;             // CTAs per SM the static kernel is built for (RBV_STATIC_OCC=2: the 64-register build)
+  int prepare_static(const DevPlan* dp, int type_size, const CallArgs& args, const CallOptions& opt, Prepared* out);
   std::string last_error_;
   std::map<std::tuple<int, int, int, int, int, int, int>, std::unique_ptr<DevPlan>> plans_;
   // free list of the user region: offset -> size
@@ -169,6 +198,9 @@ size_t a2av_smem_bytes_bulk(int P);
 int a2av_bulk_ctas_per_sm(int P);
 cudaError_t a2av_configure(int P, int* max_ctas_per_sm);
 cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream);
+// implemented in kernels/a2av_static.cu
+cudaError_t a2av_static_configure(int occupancy, int* max_ctas_per_sm);
+cudaError_t a2av_static_launch(const StaticArgs& args, int grid, int occupancy, bool cooperative, cudaStream_t stream);
 // implemented in kernels/a2av_eager.cu
 cudaError_t a2av_eager_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream);
 

@@ -9,13 +9,21 @@
 //
 // Every context owns one "symmetric heap" with the same internal layout on all processes:
 //
-//   [ CtrlBlock | cell flags | metadata tables x2 | staging arenas (L ranks x 2 parities) | user ]
+//   [ CtrlBlock | cell flags | metadata tables x2 | staging arenas (L ranks x 2 parities) |
+//     eager cell arenas (L ranks x 2 parities) | user ]
+//
+// Everything in front of the user region is zero when a context is created and after reset().  The eager
+// protocol's cells have a region of their own: its units are valid by the call number in their flag words, so
+// the region must never hold bytes that did not come from an eager call (user payload staged by the rendezvous
+// protocol could carry any value), and the call number never goes back without the region being cleared.
 //
 // Cross-rank synchronisation uses monotonic counters and sequence-stamped flags only, so nothing
 // has to be reset between calls:
 //   * metadata table units and eager cell units carry the call number in their flag words
 //   * recv_arrivals[local rank]  += 1 per chunk landed in recvbuf; the owner keeps the running target
-//   * cell_flag[parity][lr][c]    = seq + 1 when staging cell c holds this call's block
+//   * chunk_flag[parity][lr][f]   = seq + 1 when chunk f % flags_per_cell of staging cell f / flags_per_cell holds
+//     this call's data (a relay hop forwards chunk k as soon as chunk k has landed, so the hops of a
+//     store-and-forward schedule overlap chunk by chunk)
 // Staging arenas, cell flags and metadata tables alternate by call parity: a peer can run at most
 // one call ahead (it cannot finish call c+1 without data this rank sends in call c+1), so two
 // copies suffice.
@@ -29,6 +37,8 @@ namespace rbv {
 constexpr int kMaxRanks = 64;         // logical ranks per communicator
 constexpr int kMaxProcs = 16;         // processes (GPUs) per communicator
 constexpr int kMaxCellsPerRank = 2048;
+constexpr int kMaxFlagsPerRank = 16384;   // chunk flags per rank and parity (cells x chunks per cell of one call)
+constexpr int kMaxTraceKeys = 256;        // plan keys (rounds / batches) that can carry their own time stamps
 constexpr int kInlineMeta = 64;       // L * P up to this many count/displacement entries travel as kernel parameters
 constexpr int kThreads = 512;
 
@@ -55,14 +65,21 @@ struct StatusBlock {
                                 // and with CALL_TRACE 5 latest CTA start, 6 latest CTA done
 };
 
+// Time stamps per plan key of the most recent traced call (CALL_TRACE): earliest start and latest end over all
+// warps of the process that executed an item of that key.  Keys are numbered in issue order (Op::flags >> 16).
+struct TraceBlock {
+  unsigned long long kstart[kMaxTraceKeys];   // ~0ull: no item of this key ran
+  unsigned long long kend[kMaxTraceKeys];
+};
+
 // Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.
 struct CtrlBlock {
   unsigned long long recv_arrivals[kMaxRanks];   // += 1 per chunk landed in a local rank's recvbuf
   unsigned long long recv_target[kMaxRanks];     // running total of chunks expected so far (kept by the owner)
   unsigned int abort_flag;       // set locally on error, and by peers that want everyone to stop
   unsigned int pad0;
-  unsigned int exit_count;       // CTAs that finished the current call (the last one publishes the status)
-  unsigned int call_seq;         // 0-based number of the next call; bumped by the last CTA of every call, so
+  unsigned int exit_count;       // traced calls only: CTAs that finished (the last one copies the stamps to the host)
+  unsigned int call_seq;         // 0-based number of the next call; advanced by whoever completes start_count, so
                                  // that kernel arguments do not change from call to call
   StatusBlock status;
   // Auxiliary barriers of the fused kernels built on the same heap (0 MoE dispatch, 1 MoE combine,
@@ -70,16 +87,26 @@ struct CtrlBlock {
   unsigned long long aux_arrivals[4];
   unsigned int aux_seq[4];
   unsigned int aux_exit[4];
+  // entered[q] = call number + 1 of the latest static call that process q has started; written by q.  A sender of
+  // the static kernel stores into process q's memory only once q has entered the same call: without it a fast rank
+  // could overwrite a receive buffer (or a staging cell of the same parity) that q still uses for the call before.
+  // The dynamic kernel gets the same guarantee from its metadata exchange, the eager protocol from its headers.
+  unsigned int entered[kMaxProcs];
+  int last_code;                 // code of the first failure since the block was last cleared
+  unsigned int start_count;      // CTAs (eager protocol with an item table: warps) that have read call_seq in this call
 };
 
 // Byte offsets of the regions of a heap; identical on every process of a communicator.
 struct HeapLayout {
   unsigned long long ctrl_off;      // CtrlBlock
-  unsigned long long flags_off;     // uint32 cell_flag[2][L][kMaxCellsPerRank]
+  unsigned long long trace_off;     // TraceBlock
+  unsigned long long flags_off;     // uint32 chunk_flag[2][L][flags_per_rank]
+  unsigned long long flags_per_rank;
   unsigned long long meta_off;      // 2 x MetaTable(P)
   unsigned long long meta_bytes;    // size of one parity copy
   unsigned long long stage_off;     // staging arenas: [L][2] x arena_bytes
   unsigned long long arena_bytes;   // per rank per parity
+  unsigned long long eager_off;     // eager cell arenas: [L][2] x arena_bytes (only eager units are ever stored here)
   unsigned long long user_off;      // user allocations
   unsigned long long total_bytes;
 };
@@ -107,6 +134,26 @@ enum CallFlags : unsigned {
   CALL_TRACE = 4u,        // copy the status block (with the phase time stamps) to the host after every call,
                           // not only after a failing one
   CALL_BULK = 8u,         // large aligned chunks go through the bulk-copy engine (shared-memory ring per warp)
+  CALL_STATIC = 16u,      // every count of the call was known on the host: the kernel walks a table of resolved
+                          // copy descriptors (StaticItem) and has no metadata phase
+};
+
+// One resolved copy of the static rendezvous kernel: chunk k of one op with its addresses worked out on the host.
+// Addresses that point into a staging arena are those of call parity 0; the kernel adds the parity stride.
+struct alignas(16) StaticItem {
+  unsigned long long src;   // address in this process (send buffer, staging cell, or own heap)
+  unsigned long long dst;   // address as mapped in this process (own heap or a peer mapping)
+  unsigned len;             // bytes (0: the item only signals)
+  unsigned short dst_rank;  // logical rank written to
+  unsigned short flags;     // ITEM_* bits | key index << 8
+  unsigned wait_flag;       // chunk flag of this process to wait for (index at parity 0), kNoFlag: none
+  unsigned signal_flag;     // chunk flag on the destination's process to raise, kNoFlag: the chunk counts as an
+                            // arrival in dst_rank's receive buffer instead
+};
+static_assert(sizeof(StaticItem) == 32, "two 16-byte loads per item");
+constexpr unsigned kNoFlag = 0xffffffffu;
+enum ItemFlags : unsigned short {
+  ITEM_SRC_STAGE = 1, ITEM_DST_STAGE = 2, ITEM_REMOTE = 4, ITEM_SELF = 8,
 };
 
 struct InlineMeta {
@@ -152,7 +199,28 @@ struct KernelArgs {
   const long long* sdispls;
   const long long* rdispls;
   StatusBlock* host_status;  // pinned, mapped: a copy of the final status
+  TraceBlock* host_trace;    // pinned, mapped: per-key stamps of a traced call
   InlineMeta inl;
+};
+
+constexpr int kInlineItems = 48;   // items of a small static call travel in the kernel parameters
+
+// Arguments of the static rendezvous kernel (a2av_static.cu): a persistent call whose counts were all known on
+// the host.  Everything that depends on counts sits in the table behind `items`.
+struct StaticArgs {
+  int P, L, nproc, proc;
+  unsigned flags;                       // CALL_TRACE
+  unsigned nitems;
+  const StaticItem* items;              // issue order; item c is handled by warp c mod (warps in the grid)
+  const unsigned long long* expect;     // [L] chunks that land in each local rank's receive buffer per call
+  unsigned long long timeout_ns;
+  HeapLayout lay;
+  char* heap[kMaxProcs];
+  StatusBlock* host_status;
+  TraceBlock* host_trace;               // pinned copy of the per-key stamps (written when CALL_TRACE is set)
+  // A call of at most kInlineItems items carries them here: the first fetch of a small call then costs no trip to
+  // device memory (after an L2 flush that trip is a DRAM access on the critical path).
+  StaticItem inl[kInlineItems];
 };
 
 }  // namespace rbv

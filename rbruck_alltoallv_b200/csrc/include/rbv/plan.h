@@ -45,7 +45,10 @@ enum Algo : int {
   ALG_TTPL_BT_S2 = 16,        // TTPL_BT_alltoallv_s2                staggered + in-place option
   ALG_UNIFORM_SPREADOUT_TWOLAYER = 17,  // uniform_spreadout_twolayer(n, r)
   ALG_UNIFORM_ISPLIT_RBRUCK = 18,       // uniform_inverse_isplit_r_bruck(n, r1, r2)
-  ALG_COUNT = 19
+  ALG_MERGE = 19,             // merge_alltoallv(n): benchmarks/merge_benchmark.cpp:155-332 (completed)
+  ALG_SIMPLE_MERGE = 20,      // simply_merge_alltoallv(n): benchmarks/simple_merge_benchmark.cpp:138-210
+  ALG_SPLIT = 21,             // split_alltoallv: benchmarks/split_benchmark.cpp:147-205
+  ALG_COUNT = 22
 };
 
 const char* algo_name(int algo);
@@ -70,9 +73,30 @@ struct Op {
   int32_t src_cell;  // -1: read sendbuf[sdispls[D]] of src (then src == S); else staging cell of src
   int32_t dst_cell;  // -1: write recvbuf[rdispls[S]] of dst (then dst == D); else staging cell of dst
   uint32_t key;      // issue order: ops are executed in non-decreasing key order per process
-  uint32_t flags;    // bit0: self copy
+  uint32_t flags;    // bit 0: self copy; bit 1: eager unpack (added by the runtime); bits 2-8: part index and
+                     // bits 9-15: part count of an op that moves one slice of its block (0: the whole block);
+                     // bits 16-31: number of the op's key among the plan's distinct keys, in issue order
 };
 static_assert(sizeof(Op) == 24, "device code depends on this layout");
+
+#if defined(__CUDACC__)
+#define RBV_HD __host__ __device__
+#else
+#define RBV_HD
+#endif
+constexpr uint32_t kOpSelf = 1u, kOpUnpack = 2u;
+RBV_HD inline uint32_t op_part(const Op& o) { return (o.flags >> 2) & 127u; }
+RBV_HD inline uint32_t op_nparts(const Op& o) { return (o.flags >> 9) & 127u; }
+RBV_HD inline uint32_t op_key_index(const Op& o) { return o.flags >> 16; }
+// Elements [first, first + n) of a block of `count` elements that the op moves: the whole block, or slice
+// `part` of `nparts` equal slices (the last one also takes the remainder).
+RBV_HD inline void op_slice(const Op& o, long long count, long long* first, long long* n) {
+  const long long np = op_nparts(o);
+  if (np == 0) { *first = 0; *n = count; return; }
+  const long long div = count / np, p = op_part(o);
+  *first = p * div;
+  *n = (p == np - 1) ? count - p * div : div;
+}
 
 struct PlanStats {
   int w = 0;            // digits of the (intra) Bruck
@@ -82,6 +106,7 @@ struct PlanStats {
   long long hops = 0;   // total ops excluding self copies (forwarded volume in blocks)
   int phases = 0;       // number of distinct keys
 };
+constexpr int kMaxOpParts = 127;
 
 struct Plan {
   AlgoSpec spec;        // normalised (clamped) parameters
@@ -89,6 +114,7 @@ struct Plan {
   std::string errmsg;
   int ncells = 0;       // staging cells needed on every rank
   std::vector<Op> ops;  // all ranks, stable-sorted by key
+  std::vector<uint32_t> keys;  // the distinct keys in issue order (Op::flags >> 16 indexes this list)
   PlanStats stats;
   bool uniform = false;       // algorithm takes one count for all pairs
   bool inplace_ok = false;    // algorithm accepts sendbuf == NULL (data taken from recvbuf)
@@ -110,6 +136,8 @@ std::vector<int> to_base(int w, int N, int b);
 // sendbufs/recvbufs: P pointers.  counts: sendcounts[s*P+d], sdispls[s*P+d] (elements, per sender s),
 // rdispls[d*P+s] (elements, per receiver d).  Returns 0, or a negative code when the plan violates a
 // hazard rule (read of an unfilled cell: -10, second write to a cell: -11, bad op: -12).
+// build_plan itself refuses (err -13) a schedule in which some (origin, destination) pair has no first hop or
+// more than one: the eager protocol's cell reuse relies on every pair exchanging a header in every call.
 int host_execute(const Plan& plan, int type_size, const char* const* sendbufs, char* const* recvbufs,
                  const int* sendcounts, const long long* sdispls, const long long* rdispls);
 

@@ -85,6 +85,21 @@ void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
                   const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
                   const int* recvcounts, const long long* sdispls, const long long* rdispls,
                   int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes);
+/* The same with the arguments of the whole communicator, gathered by the caller on the host: g_counts[s * P + d]
+ * (what rank s sends to rank d), g_caps[d * P + s] (recvcounts of rank d, -1 unchecked; may be null),
+ * g_rdispls[d * P + s], g_recvoff[d] (byte offset of rank d's receive buffer in its process's heap).  With them a
+ * call with host-side counts is resolved completely on the host and runs without a metadata phase; every
+ * process must then pass them.  A process that hosts all ranks gets this from rbv_prepare already.
+ * flags: bit 0 in-place, bit 8 keep the dynamic kernel even where the static one is possible. */
+void* rbv_prepare_global(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
+                         const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
+                         const int* recvcounts, const long long* sdispls, const long long* rdispls,
+                         int counts_on_device, long long bytes_hint, unsigned flags, int grid, size_t chunk_bytes,
+                         const int* g_counts, const int* g_caps, const long long* g_rdispls,
+                         const unsigned long long* g_recvoff);
+/* Which kernel a prepared call runs: 0 dynamic rendezvous, 1 eager, 2 static rendezvous;
+ * out3 = grid, cooperative launch needed (0 / 1), work items. */
+int rbv_prepared_info(void* prepared, long long* out3);
 int rbv_launch(rbv_ctx_t ctx, void* prepared, void* cuda_stream);
 void rbv_prepared_free(rbv_ctx_t ctx, void* prepared);
 /* NVLS: keep the metadata tables in a caller-provided buffer that is bound to an NVLink multicast object (local
@@ -98,7 +113,11 @@ size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx);
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes);
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on);       /* report phase time stamps after every call */
 void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode);      /* bulk-copy engine for large chunks: 0 off (default), 1 on, -1 by size */
-void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on); /* cooperative (default) or plain kernel launches */
+void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int mode); /* -1 where a call needs it (default), 0 never, 1 always */
+void rbv_ctx_set_static(rbv_ctx_t ctx, int on);      /* 0: persistent calls keep the dynamic kernel */
+/* Time stamps (device clock, ns) per key of the schedule (a round, a batch; key = phase << 24 | step) of the most
+ * recent traced call: earliest start and latest end over all warps of this process.  Returns the number filled. */
+int rbv_ctx_last_trace(rbv_ctx_t ctx, unsigned* keys, unsigned long long* start_ns, unsigned long long* end_ns, int max);
 
 /* Phase timers of the most recent call, filled by rbv_update_timers() (which synchronises;
  * call rbv_ctx_set_trace(ctx, 1) first).
@@ -107,8 +126,9 @@ void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int on); /* cooperative (default) or
 extern double init_time, findMax_time, rotateIndex_time, alcCopy_time, getBlock_time, prepData_time,
     excgMeta_time, excgData_time, replace_time, orgData_time, prepSP_time, SP_time;
 extern double intra_time;
-extern double* iteration_time;
+extern double* iteration_time;   /* one entry per inter-group batch, malloc'ed by rbv_update_timers, freed by the caller */
 int rbv_update_timers(rbv_ctx_t ctx);
+int rbv_iteration_count(rbv_ctx_t ctx); /* entries of iteration_time for the most recent call */
 
 /* ---- helpers (src/utils.cpp) ---- */
 int myPow(int x, unsigned int p);
@@ -159,6 +179,15 @@ int twolayer_communicator_linear_s3(int n, int bblock1, int bblock2, char* sendb
 int twolayer_communicator_linear_s4(int n, int bblock1, int bblock2, char* sendbuf, int* sendcounts, int* sdispls,
                                     rbv_datatype sendtype, char* recvbuf, int* recvcounts, int* rdispls,
                                     rbv_datatype recvtype, rbv_comm_t comm);
+/* Exchange schemes of the reference's benchmark programs (benchmarks/merge_benchmark.cpp,
+ * simple_merge_benchmark.cpp, split_benchmark.cpp), with the hand-out to the destinations that the reference's
+ * merge leaves commented out. */
+int merge_alltoallv(int ncores, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                    int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int simply_merge_alltoallv(int ncores, char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype,
+                           char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
+int split_alltoallv(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                    int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
 /* Declared but never defined in the reference (src/rbruckv.h:80-81); here: the automatic choice. */
 int ML_benchmark(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf, int* recvcounts,
                  int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);

@@ -10,7 +10,8 @@
 // e.g. src/tuna2.cpp:160-185, folded into one stream).  The destination rank copies the payload from its
 // arrival cell into recvbuf[rdispls[source]] itself, so only the owner ever writes a receive buffer and no
 // "receiver ready" handshake is needed.  Relay hops of the Bruck schedules forward a cell unit by unit as it
-// arrives.  Cells live in the staging arenas and alternate with the call parity, like staging cells do.
+// arrives.  Cells live in arenas of their own (never touched by the rendezvous protocol, zero when the context
+// is created or reset) and alternate with the call parity, like staging cells do.
 //
 // Work items (one warp each, walked in list order): the plan's send ops, cut into chunks, followed by one unpack
 // op per (local rank, source).  Block sizes of relay and unpack items are not known before the header arrives;
@@ -33,7 +34,7 @@ __device__ __forceinline__ CtrlBlock* ctrl_of(const KernelArgs& a, int proc) {
 }
 __device__ __forceinline__ size_t cell_stride(const KernelArgs& a) { return 16 + 2 * (size_t)a.eager_payload; }
 __device__ __forceinline__ uint4* cell_of(const KernelArgs& a, int proc, int parity, int lr, int cell) {
-  return reinterpret_cast<uint4*>(a.heap[proc] + a.lay.stage_off + (size_t)(lr * 2 + parity) * a.lay.arena_bytes +
+  return reinterpret_cast<uint4*>(a.heap[proc] + a.lay.eager_off + (size_t)(lr * 2 + parity) * a.lay.arena_bytes +
                                   (size_t)cell * cell_stride(a));
 }
 __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
@@ -69,12 +70,7 @@ __device__ __forceinline__ bool poll_unit(const uint4* p, const EagerCtx& c, uin
 }
 
 __device__ void eager_error(const KernelArgs& a, int code, int site, int d0, int d1) {
-  CtrlBlock* c = ctrl_of(a, a.proc);
-  if (atomicCAS(&c->status.code, 0, code) == 0) { c->status.site = site; c->status.detail0 = d0; c->status.detail1 = d1; }
-  __threadfence();
-  dev::st_relaxed_sys(&c->abort_flag, 1u);
-  for (int q = 0; q < a.nproc; q++)
-    if (q != a.proc) dev::st_relaxed_sys(&ctrl_of(a, q)->abort_flag, 1u);
+  dev::note_failure(a.heap, a.nproc, a.proc, a.lay.ctrl_off, a.host_status, code, site, d0, d1);
 }
 
 // payload word i (4 bytes) of a block that starts at `src` (any alignment), zero beyond `bytes`
@@ -107,6 +103,9 @@ __device__ __forceinline__ void store_words(char* dst, size_t unit, unsigned w0,
 __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_constant__ KernelArgs a) {
   __shared__ unsigned s_prefix[kOpTileE + 1];
   __shared__ unsigned s_total, s_seq;
+  __shared__ int s_last;
+  const bool trace = (a.flags & CALL_TRACE) != 0;
+  TraceBlock* tb = reinterpret_cast<TraceBlock*>(a.heap[a.proc] + a.lay.trace_off);
   const int P = a.P, L = a.L, ts = a.type_size;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned warps_per_cta = blockDim.x >> 5;
@@ -122,11 +121,16 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
 
   // the call number is fetched while the first tile of work items is being sized (one barrier less on the
   // critical path of small calls)
+  // Whoever completes CtrlBlock::start_count knows that everybody has read the call number and advances it for the
+  // next call: CTAs count when the work items are sized in the kernel (thread 0 reads the number for its CTA), warps
+  // count when the call brings its item table (every warp reads the number itself).
+  const bool pre = a.items != nullptr;
   unsigned seq_early = 0;
   if (tid == 0) {
-    seq_early = __ldcg(&my->call_seq);
+    seq_early = dev::read_call_seq(my);
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
     if (a.flags & CALL_TRACE) atomicMax(&my->status.trace[5], dev::globaltimer());   // latest CTA start
+    if (!pre && atomicAdd(&my->start_count, 1u) == gridDim.x - 1) dev::advance_call_seq(my, seq_early);
   }
   unsigned seq = 0;
   int parity = 0;
@@ -135,10 +139,13 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
 
   // Persistent calls with host-side counts bring a table of their work items: no sizing pass, no block-wide
   // barrier before the first byte moves; every warp fetches the call number itself.
-  const bool pre = a.items != nullptr;
+  unsigned start_rank = 0;   // lane 0: how many warps had read the call number before this one
   if (pre) {
     unsigned sq = 0;
-    if (lane == 0) sq = (tid == 0) ? seq_early : __ldcg(&my->call_seq);
+    if (lane == 0) {
+      sq = (tid == 0) ? seq_early : dev::read_call_seq(my);
+      start_rank = atomicAdd(&my->start_count, 1u);   // the result is looked at after the warp's items
+    }
     seq = __shfl_sync(0xffffffffu, sq, 0);
     parity = seq & 1;
     ec.flag = seq + 1u;
@@ -213,6 +220,8 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         o = a.ops[t0 + oi];
       }
       const int lsrc = o.src - a.proc * L;
+      const unsigned kidx = min(op_key_index(o), (unsigned)kMaxTraceKeys - 1);
+      if (trace && lane == 0) atomicMin(&tb->kstart[kidx], dev::globaltimer());
       const size_t u0 = (size_t)k * (chunk / 8);           // first payload unit of this item
       const size_t cu = chunk / 8;
 
@@ -225,6 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
           dev::group_copy(a.heap[a.proc] + a.recvoff[lsrc] + (size_t)rdispls[(size_t)lsrc * P + o.origin] * ts + off,
                           a.sendbuf[lsrc] + (size_t)sdispls[(size_t)lsrc * P + o.dest] * ts + off, len, lane, 32);
         }
+        if (trace && lane == 0) atomicMax(&tb->kend[kidx], dev::globaltimer());
         continue;
       }
       if (o.flags & 2u) {
@@ -269,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
           }
         }
         alive = __all_sync(0xffffffffu, alive);
+        if (trace && lane == 0) atomicMax(&tb->kend[kidx], dev::globaltimer());
         continue;
       }
       // ---- send: send buffer or staging cell -> cell on the destination rank ----
@@ -332,31 +343,30 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         }
         alive = __all_sync(0xffffffffu, alive);
       }
+      if (trace && lane == 0) atomicMax(&tb->kend[kidx], dev::globaltimer());
     }
     if (blockIdx.x == 0 && tid == 0) my->status.trace[2] = dev::globaltimer();   // first warp's items done
     base += total;
     __syncthreads();
   }
 
-  // The last CTA to leave advances the call number and publishes the status.
-  __syncthreads();
-  if (tid == 0) {
-    if (blockIdx.x == 0) my->status.trace[3] = dev::globaltimer();               // first CTA done
-    if (a.flags & CALL_TRACE) {                                                  // latest CTA done, and which one
+  // No end-of-call pass.  With an item table the warp that completed the start count advances the call number now
+  // (its own items are done, so the atomic's result has long arrived); it also reports a communicator that was
+  // told to stop.  (The rendezvous protocol keeps no per-call counter targets here, so the protocols mix freely.)
+  if (pre && lane == 0 && start_rank == nwarps - 1) {
+    dev::advance_call_seq(my, seq);
+    if (dev::ld_relaxed_sys(&my->abort_flag)) eager_error(a, RBV_ERR_ABORTED, 0, 0, 0);
+  }
+  if (!pre && blockIdx.x == 0 && tid == 0 && dev::ld_relaxed_sys(&my->abort_flag)) eager_error(a, RBV_ERR_ABORTED, 0, 0, 0);
+  if (trace) {
+    __syncthreads();
+    if (tid == 0) {
       const unsigned long long now = dev::globaltimer();
-      if (atomicMax(&my->status.trace[6], now) < now) my->status.trace[7] = blockIdx.x;
+      if (blockIdx.x == 0) my->status.trace[3] = now;                            // first CTA done
+      if (atomicMax(&my->status.trace[6], now) < now) my->status.trace[7] = blockIdx.x;   // latest CTA done, and which
+      atomicMax(&my->status.trace[4], now);
     }
-    __threadfence();
-    if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
-      my->exit_count = 0;
-      my->call_seq = seq + 1u;
-      // (the rendezvous protocol keeps no per-call counter targets, so the two protocols can be mixed freely)
-      my->status.trace[4] = dev::globaltimer();
-      if (my->status.code == 0 && dev::ld_relaxed_sys(&my->abort_flag)) my->status.code = RBV_ERR_ABORTED;
-      __threadfence();
-      if (a.host_status && (my->status.code != 0 || (a.flags & CALL_TRACE))) *a.host_status = my->status;
-      my->status.code = 0;
-    }
+    dev::publish_trace(my, tb, a.host_trace, a.host_status, &s_last);
   }
 }
 

@@ -14,10 +14,17 @@
 // Work distribution: ops are cut into chunks of `chunk_bytes`; chunk c of the process-wide
 // sequence is handled by WARP c mod (warps in the grid).  A warp copies its chunk with 16-byte
 // vectors (512 contiguous bytes per warp instruction; optionally with cp.async.bulk through a
-// shared-memory ring, see bulk_copy.cuh) and, when it completes a staging op, signals the destination.  Small blocks thus proceed in parallel, one warp each, and large blocks are spread
-// over all warps of all SMs.  Warps walk their chunks in plan order, so a wait on a staging cell
-// only ever depends on chunks of an earlier plan key, which rules out cycles as long as all CTAs
-// are resident (cooperative launch).
+// shared-memory ring, see bulk_copy.cuh).  A chunk that lands in a staging cell raises that chunk's own flag on the
+// destination, and the relay hop that forwards chunk k waits for chunk k only, so the hops of a store-and-forward
+// schedule overlap chunk by chunk (the reference keeps all rounds of a digit in flight and unpacks after the
+// digit, src/tuna2.cpp:184-223; here the pipeline is per chunk).  Small blocks thus proceed in parallel, one warp
+// each, and large blocks are spread over all warps of all SMs.  Warps walk their chunks in plan order, so a wait
+// on a staging chunk only ever depends on chunks of an earlier plan key, which rules out cycles as long as all
+// CTAs are resident (cooperative launch).
+//
+// This kernel serves calls whose counts are not all known on the host (device-resident counts, one-shot calls of
+// a multi-process communicator) and in-place calls; persistent calls with host-side counts run the static kernel
+// (a2av_static.cu).  A block that a plan sends in slices (split_alltoallv) travels whole here, with its first slice.
 //
 // Signals use gpu scope when producer and consumer are on the same GPU and system scope across
 // GPUs.  The call number lives in device memory (CtrlBlock::call_seq), so the kernel arguments of
@@ -52,9 +59,12 @@ struct Smem {
 __device__ __forceinline__ CtrlBlock* ctrl_of(const KernelArgs& a, int proc) {
   return reinterpret_cast<CtrlBlock*>(a.heap[proc] + a.lay.ctrl_off);
 }
-__device__ __forceinline__ unsigned* cell_flag_of(const KernelArgs& a, int proc, int parity, int lr, int cell) {
+__device__ __forceinline__ unsigned* chunk_flag_of(const KernelArgs& a, int proc, int parity, int lr, size_t f) {
   return reinterpret_cast<unsigned*>(a.heap[proc] + a.lay.flags_off) +
-         ((size_t)(parity * a.L + lr) * kMaxCellsPerRank + cell);
+         ((size_t)(parity * a.L + lr) * a.lay.flags_per_rank + f);
+}
+__device__ __forceinline__ TraceBlock* trace_of(const KernelArgs& a) {
+  return reinterpret_cast<TraceBlock*>(a.heap[a.proc] + a.lay.trace_off);
 }
 __device__ __forceinline__ char* meta_of(const KernelArgs& a, int proc, int parity) {
   return a.heap[proc] + a.lay.meta_off + (size_t)parity * a.lay.meta_bytes;
@@ -70,17 +80,7 @@ __device__ __forceinline__ char* stage_of(const KernelArgs& a, int proc, int par
 }
 
 __device__ void report_error(const KernelArgs& a, int code, int site, int d0, int d1) {
-  CtrlBlock* c = ctrl_of(a, a.proc);
-  if (atomicCAS(&c->status.code, 0, code) == 0) {
-    c->status.site = site;
-    c->status.detail0 = d0;
-    c->status.detail1 = d1;
-  }
-  __threadfence();
-  dev::st_relaxed_sys(&c->abort_flag, 1u);
-  // ask the other processes to stop waiting as well
-  for (int q = 0; q < a.nproc; q++)
-    if (q != a.proc) dev::st_relaxed_sys(&ctrl_of(a, q)->abort_flag, 1u);
+  dev::note_failure(a.heap, a.nproc, a.proc, a.lay.ctrl_off, a.host_status, code, site, d0, d1);
 }
 
 __device__ __forceinline__ const int* in_sendcounts(const KernelArgs& a) {
@@ -153,9 +153,12 @@ __device__ void publish_metadata(const KernelArgs& a, int parity, unsigned flag)
   }
 }
 
+// Bytes the op moves: the whole block; a block that the plan cuts into slices travels with its first slice.
 __device__ __forceinline__ size_t op_bytes(const Op& o, const Smem& sm, int P, int ts) {
+  if (op_nparts(o) && op_part(o)) return 0;
   return (size_t)sm.counts[(size_t)o.origin * P + o.dest] * (size_t)ts;
 }
+__device__ __forceinline__ bool op_skipped(const Op& o) { return op_nparts(o) && op_part(o); }
 
 }  // namespace
 
@@ -164,6 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   __shared__ int s_flag;
   __shared__ unsigned s_total;
   __shared__ unsigned s_seq;
+  __shared__ int s_last;
   __shared__ unsigned s_arrived[kMaxRanks];   // chunks this CTA delivered to each rank's receive buffer, not yet reported
   const int P = a.P, L = a.L, ts = a.type_size;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -191,8 +195,11 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
 
   if (tid < kMaxRanks) s_arrived[tid] = 0;
   if (tid == 0) {
-    s_seq = __ldcg(&my->call_seq);
+    const unsigned sq = dev::read_call_seq(my);
+    s_seq = sq;
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
+    // the last CTA to read the call number advances it for the next call
+    if (atomicAdd(&my->start_count, 1u) == gridDim.x - 1) dev::advance_call_seq(my, sq);
   }
   __syncthreads();
   const unsigned seq = s_seq;
@@ -266,6 +273,8 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     for (int s = 0; s < P; s++) chunk_b = max(chunk_b, (unsigned long long)sm.schunk[s]);
   }
   size_t stride = 0;
+  unsigned long long fpc = 1;   // chunk flags per staging cell
+  const bool trace = (a.flags & CALL_TRACE) != 0;
   if (alive) {
     // global max block -> staging cell stride (the reference's max_send_count allreduce)
     if (a.ncells > 0) {
@@ -279,6 +288,11 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
         if (blockIdx.x == 0 && tid == 0) report_error(a, RBV_ERR_CAPACITY, 0, a.ncells, (int)(stride >> 10));
         alive = false;
       }
+      // every chunk of a staging cell has a flag of its own: chunks must be large enough for the flags to suffice
+      // (same inputs on every rank, hence the same result)
+      fpc = a.lay.flags_per_rank / (unsigned long long)a.ncells;
+      const unsigned long long need = ((stride + fpc - 1) / fpc + 15) & ~15ull;
+      chunk_b = max(chunk_b, need);
     }
     // the owner of a receive buffer adds the chunks it expects in this call to its running target
     if (blockIdx.x == 0 && tid < L) {
@@ -302,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
       const Op o = a.ops[t0 + i];
       size_t b = alive ? op_bytes(o, sm, P, ts) : 0;
       unsigned nch = (unsigned)((b + chunk_b - 1) / chunk_b);
-      sm.prefix[i + 1] = nch ? nch : 1u;   // empty blocks still signal their arrival
+      sm.prefix[i + 1] = op_skipped(o) ? 0u : (nch ? nch : 1u);   // empty blocks still signal their arrival
     }
     __syncthreads();
     if (tid < 32) {
@@ -332,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
       oi = dev::find_op(sm.prefix, oi, tn, c);   // chunks are visited in order: the search resumes at the last op
       const Op o = a.ops[t0 + oi];
       const unsigned k = c - sm.prefix[oi];
-      const unsigned nch = sm.prefix[oi + 1] - sm.prefix[oi];
+      if (trace && lane == 0) atomicMin(&trace_of(a)->kstart[min(op_key_index(o), (unsigned)kMaxTraceKeys - 1)], dev::globaltimer());
       const int lsrc = o.src - a.proc * L;
       const int dproc = o.dst / L, ldst = o.dst - dproc * L;
       const bool remote = dproc != a.proc;
@@ -347,11 +361,11 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
           bytes = 0;
         }
       }
-      // wait for the source cell
+      // wait for this chunk of the source cell
       if (ok && o.src_cell >= 0) {
         int r = 0;
         if (lane == 0) {
-          r = dev::wait_ge(cell_flag_of(a, a.proc, parity, lsrc, o.src_cell), seq + 1u, wc, multi);
+          r = dev::wait_ge(chunk_flag_of(a, a.proc, parity, lsrc, (size_t)o.src_cell * fpc + k), seq + 1u, wc, multi);
           if (r == dev::WAIT_TIMEOUT) report_error(a, RBV_ERR_TIMEOUT, WAIT_CELL, t0 + oi, o.src_cell);
         }
         r = __shfl_sync(0xffffffffu, r, 0);
@@ -392,20 +406,11 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
       // completion.  Final hops: every chunk counts towards the receiver's arrival counter (the receiver knows
       // how many to expect); nobody looks at that counter before the end of the call, so the chunks are tallied
       // per CTA and reported once per op tile, which spares a fence and a remote atomic per chunk.
-      // Staging cells: the warp that finishes the last chunk of the op raises the cell's flag at once.
+      // Staging cells: the chunk's own flag on the destination goes up as soon as the chunk has been stored.
       if (lane == 0) {
-        if (o.dst_cell < 0) {
-          atomicAdd(&s_arrived[o.dst], 1u);
-        } else {
-          bool last = true;
-          if (nch > 1) {
-            dev::fence_acq_rel(remote);   // this chunk's stores become visible before the count does
-            unsigned old = atomicAdd(&a.op_done[t0 + oi], 1u);
-            last = (old == nch - 1);
-            if (last) a.op_done[t0 + oi] = 0;
-          }
-          if (last && ok) dev::signal_store(cell_flag_of(a, dproc, parity, ldst, o.dst_cell), seq + 1u, remote);
-        }
+        if (o.dst_cell < 0) atomicAdd(&s_arrived[o.dst], 1u);
+        else if (ok) dev::signal_store(chunk_flag_of(a, dproc, parity, ldst, (size_t)o.dst_cell * fpc + k), seq + 1u, remote);
+        if (trace) atomicMax(&trace_of(a)->kend[min(op_key_index(o), (unsigned)kMaxTraceKeys - 1)], dev::globaltimer());
       }
     }
     // this warp's stores are performed before the CTA reports them
@@ -434,22 +439,15 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
       if (r == dev::WAIT_TIMEOUT)
         report_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, tid, (int)(target - my->recv_arrivals[tid]));
     }
+    // a process that was told to stop (or runs on a communicator that failed earlier and was not reset) says so;
+    // the load overlaps with the wait above
+    if (tid == 32 && dev::ld_relaxed_sys(&my->abort_flag)) report_error(a, RBV_ERR_ABORTED, 0, 0, 0);
     __syncthreads();
     if (tid == 0) my->status.trace[4] = dev::globaltimer();
   }
-  // The last CTA to leave publishes the status of this call and clears it for the next one.
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    if (atomicAdd(&my->exit_count, 1u) == gridDim.x - 1) {
-      my->exit_count = 0;
-      my->call_seq = seq + 1u;
-      if (my->status.code == 0 && dev::ld_relaxed_sys(&my->abort_flag)) my->status.code = RBV_ERR_ABORTED;
-      __threadfence();
-      if (a.host_status && (my->status.code != 0 || (a.flags & CALL_TRACE))) *a.host_status = my->status;
-      my->status.code = 0;
-    }
-  }
+  // No end-of-call pass: the call number was advanced at the start and failures are reported where they happen.
+  // Only traced calls gather their stamps here.
+  if (trace) dev::publish_trace(my, trace_of(a), a.host_trace, a.host_status, &s_last);
 }
 
 size_t a2av_smem_bytes(int P) {
@@ -486,7 +484,9 @@ int a2av_bulk_ctas_per_sm(int P) {
 cudaError_t a2av_launch(const KernelArgs& args, int grid, bool cooperative, cudaStream_t stream) {
   void* params[] = {(void*)&args};
   const size_t smem = (args.flags & CALL_BULK) ? a2av_smem_bytes_bulk(args.P) : a2av_smem_bytes(args.P);
-  if (cooperative)
+  // An in-place call synchronises the whole grid after moving the send data aside, which is defined for
+  // cooperative launches only: such a call is launched cooperatively whatever the caller's preference.
+  if (cooperative || (args.flags & CALL_INPLACE))
     return cudaLaunchCooperativeKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params, smem, stream);
   return cudaLaunchKernel((const void*)a2av_kernel, dim3(grid), dim3(kThreads), params, smem, stream);
 }

@@ -8,6 +8,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "rbv/context.h"
 #include "rbv/device_types.h"
@@ -24,14 +25,17 @@ constexpr int kMaxOpsNA = kNR * 13;                  // 12 hops + 1 self copy pe
 
 constexpr size_t align_up_c(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr size_t kCtrlOff = 0;
-constexpr size_t kFlagsOff = align_up_c(sizeof(CtrlBlock), 256);
-constexpr size_t kFlagsBytes = sizeof(unsigned) * 2ull * kNR * kMaxCellsPerRank;
+constexpr size_t kTraceOff = align_up_c(sizeof(CtrlBlock), 256);
+constexpr size_t kFlagsOff = kTraceOff + align_up_c(sizeof(TraceBlock), 256);
+constexpr size_t kFlagsPerRank = 256;                // 5 staging cells x up to 51 chunk flags each
+constexpr size_t kFlagsBytes = sizeof(unsigned) * 2ull * kNR * kFlagsPerRank;
 constexpr size_t kMetaOff = kFlagsOff + kFlagsBytes;
 constexpr size_t kMetaBytes = 3584;                  // >= meta_table_bytes(8)
-constexpr size_t kDoneOff = kMetaOff + 2 * kMetaBytes;
-constexpr size_t kOpsOff = align_up_c(kDoneOff + sizeof(unsigned) * kMaxOpsNA, 256);
-constexpr size_t kClearBytes = kOpsOff;              // everything before the schedule starts at zero per call
-constexpr size_t kStageOff = align_up_c(kOpsOff + sizeof(Op) * kMaxOpsNA, 4096);
+constexpr size_t kClearBytes = align_up_c(kMetaOff + 2 * kMetaBytes, 256);   // starts at zero in every call
+// schedules for every rank count 1..8, uploaded once per device; slot P - 1 holds kMaxOpsNA ops
+constexpr size_t kOpsOff = kClearBytes;
+constexpr size_t kOpsSlot = align_up_c(sizeof(Op) * kMaxOpsNA, 256);
+constexpr size_t kStageOff = align_up_c(kOpsOff + kOpsSlot * kNR, 4096);
 constexpr size_t kTotal = kStageOff + 2ull * kNR * kArena;
 static_assert(kMetaBytes >= 48 * kNR * kNR + 16 * kNR, "metadata tables do not fit");
 static_assert(kTotal <= RBV_NOALLOC_SCRATCH_BYTES, "scratch array too small for the stated limits");
@@ -43,11 +47,11 @@ constexpr int kMaxDevices = 64;
 struct DeviceState {
   bool ready;
   unsigned char* base;     // device address of g_scratch on that device
-  int ranks_uploaded;      // rank count whose schedule currently sits in the scratch array
-  int nops, ncells;
+  int nops[kNR + 1], ncells[kNR + 1];   // per rank count
   int sm_count;
 };
 DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mutex;    // guards the first-call set-up of a device against concurrent host threads
 thread_local char g_msg[256];
 
 int fail(int code, const char* what, cudaError_t e = cudaSuccess) {
@@ -123,7 +127,10 @@ extern "C" int rbv_alltoallv_noalloc(int nranks, int type_size, const void* cons
   if (dev < 0 || dev >= kMaxDevices) return fail(RBV_NOALLOC_ERR_BAD_ARG, "device index out of range");
   DeviceState& ds = g_dev[dev];
 
-  // ---- first call on this device: resolve the scratch array's device address (with this device current) ----
+  // ---- first call on this device: resolve the scratch array's device address (with this device current) and
+  //      upload the schedules of all rank counts; later calls never synchronise ----
+  {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
   if (!ds.ready) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_scratch);
@@ -134,18 +141,17 @@ extern "C" int rbv_alltoallv_noalloc(int nranks, int type_size, const void* cons
     int per_sm = 0;
     e = a2av_configure(kNR, &per_sm);
     if (e != cudaSuccess || per_sm < 1) return fail(RBV_NOALLOC_ERR_CUDA, "kernel configuration", e);
-    ds.ranks_uploaded = 0;
+    for (int np = 1; np <= kNR; np++) {
+      Op host_ops[kMaxOpsNA];
+      ds.nops[np] = build_schedule(np, host_ops, &ds.ncells[np]);
+      e = cudaMemcpy(ds.base + kOpsOff + kOpsSlot * (np - 1), host_ops, sizeof(Op) * ds.nops[np], cudaMemcpyHostToDevice);
+      if (e != cudaSuccess) return fail(RBV_NOALLOC_ERR_CUDA, "schedule upload", e);
+    }
+    // the per-key stamps of a traced call start at "never"; this path does not trace, but the block is part of the layout
+    e = cudaMemset(ds.base + kTraceOff, 0xff, sizeof(TraceBlock::kstart));
+    if (e != cudaSuccess) return fail(RBV_NOALLOC_ERR_CUDA, "cudaMemset(trace block)", e);
     ds.ready = true;
   }
-  // ---- schedule for this rank count (uploaded when it changes; synchronous, so not during capture) ----
-  if (ds.ranks_uploaded != P) {
-    Op host_ops[kMaxOpsNA];
-    ds.nops = build_schedule(P, host_ops, &ds.ncells);
-    e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) return fail(RBV_NOALLOC_ERR_CUDA, "cudaStreamSynchronize", e);
-    e = cudaMemcpy(ds.base + kOpsOff, host_ops, sizeof(Op) * ds.nops, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) return fail(RBV_NOALLOC_ERR_CUDA, "schedule upload", e);
-    ds.ranks_uploaded = P;
   }
 
   // ---- per call: control words start at zero ----
@@ -157,18 +163,20 @@ extern "C" int rbv_alltoallv_noalloc(int nranks, int type_size, const void* cons
   ka.P = P; ka.L = P; ka.nproc = 1; ka.proc = 0;
   ka.type_size = type_size;
   ka.flags = CALL_META_INLINE;
-  ka.nops = ds.nops;
+  ka.nops = ds.nops[P];
   ka.absent_rank = -1;
-  ka.ncells = ds.ncells;
-  ka.ops = reinterpret_cast<const Op*>(ds.base + kOpsOff);
-  ka.op_done = reinterpret_cast<unsigned*>(ds.base + kDoneOff);
+  ka.ncells = ds.ncells[P];
+  ka.ops = reinterpret_cast<const Op*>(ds.base + kOpsOff + kOpsSlot * (P - 1));
+  ka.op_done = nullptr;
   ka.chunk_bytes = 8 << 10;
   ka.timeout_ns = 2000000000ull;
-  ka.lay.ctrl_off = kCtrlOff; ka.lay.flags_off = kFlagsOff; ka.lay.meta_off = kMetaOff;
+  ka.lay.ctrl_off = kCtrlOff; ka.lay.trace_off = kTraceOff; ka.lay.flags_off = kFlagsOff;
+  ka.lay.flags_per_rank = kFlagsPerRank; ka.lay.meta_off = kMetaOff;
   ka.lay.meta_bytes = kMetaBytes; ka.lay.stage_off = kStageOff; ka.lay.arena_bytes = kArena;
-  ka.lay.user_off = kTotal; ka.lay.total_bytes = kTotal;
+  ka.lay.eager_off = kTotal; ka.lay.user_off = kTotal; ka.lay.total_bytes = kTotal;
   ka.heap[0] = reinterpret_cast<char*>(ds.base);
   ka.host_status = nullptr;
+  ka.host_trace = nullptr;
   ka.meta_self = reinterpret_cast<char*>(ds.base) + kMetaOff;
   ka.meta_mc = nullptr;
   for (int r = 0; r < P; r++) {
@@ -189,15 +197,16 @@ extern "C" int rbv_alltoallv_noalloc(int nranks, int type_size, const void* cons
   return RBV_NOALLOC_OK;
 }
 
-// Synchronises the stream and returns the device-side status code of the last call on the current device
-// (0 ok; otherwise an rbv::Status value such as a time-out or a truncated block).
+// Synchronises the stream and returns the device-side status code of the last call on the current device:
+// 0 ok; otherwise the rbv::Status value that the kernel recorded first (1 a bounded wait ran out, 3 staging
+// capacity, 4 a block larger than the receiver's recvcount, 5 stopped after an error elsewhere).
 extern "C" int rbv_noalloc_status(void* cuda_stream) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || !g_dev[dev].ready) return -1;
   if (cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream)) != cudaSuccess) return -1;
-  // the kernel leaves status.code cleared after reporting, but the abort flag stays up after any failure
-  unsigned flag = 0;
-  const CtrlBlock* c = reinterpret_cast<const CtrlBlock*>(g_dev[dev].base);
-  if (cudaMemcpy(&flag, &c->abort_flag, sizeof flag, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  return flag ? (int)RBV_ERR_ABORTED : 0;
+  // the kernel keeps the code of the call it has just finished in the control block
+  CtrlBlock c;
+  if (cudaMemcpy(&c, g_dev[dev].base, sizeof c, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (c.last_code) return c.last_code;
+  return c.abort_flag ? (int)RBV_ERR_ABORTED : 0;
 }

@@ -7,6 +7,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include "rbv/device_types.h"
+
 namespace rbv {
 namespace dev {
 
@@ -230,6 +232,69 @@ __device__ __forceinline__ void signal_store(unsigned* p, unsigned v, bool sys) 
 __device__ __forceinline__ void signal_add(unsigned long long* p, unsigned long long v, bool sys) {
   fence_acq_rel(sys);
   red_relaxed_add(p, v, sys);
+}
+
+// ---- call bookkeeping shared by the three alltoallv kernels ---------------------------------------------------
+// The call number lives in device memory (kernel arguments of a repeated call stay constant).  Every CTA (or warp)
+// reads it with an acquire load and then adds itself to CtrlBlock::start_count; whoever completes the count knows
+// that all others have read the number and advances it for the next call.  Doing this when the kernel starts
+// rather than when it ends takes an atomic round trip and the stores that follow it off the tail of every call.
+__device__ __forceinline__ unsigned read_call_seq(const CtrlBlock* c) { return ld_acquire_gpu(&c->call_seq); }
+__device__ __forceinline__ void advance_call_seq(CtrlBlock* c, unsigned seq) {
+  c->start_count = 0;
+  c->call_seq = seq + 1u;
+}
+
+// First failure of a call: kept in the control block (first one wins) and handed to the host at once, so that no
+// end-of-kernel pass is needed to publish it.  The abort flag makes every other wait on this process leave, and the
+// peers are told to stop waiting as well.  `heap` / `nproc` / `proc` / `ctrl_off` locate the peers' control blocks.
+__device__ inline void note_failure(char* const* heap, int nproc, int proc, unsigned long long ctrl_off,
+                                    StatusBlock* host, int code, int site, int d0, int d1) {
+  CtrlBlock* c = reinterpret_cast<CtrlBlock*>(heap[proc] + ctrl_off);
+  if (atomicCAS(&c->status.code, 0, code) == 0) {
+    c->status.site = site;
+    c->status.detail0 = d0;
+    c->status.detail1 = d1;
+    c->last_code = code;
+  }
+  __threadfence();
+  if (host && *reinterpret_cast<volatile int*>(&host->code) == 0) {   // sticky on the host until it has been read
+    host->site = site;
+    host->detail0 = d0;
+    host->detail1 = d1;
+    __threadfence_system();
+    *reinterpret_cast<volatile int*>(&host->code) = code;
+  }
+  if (code != RBV_ERR_ABORTED) {
+    st_relaxed_sys(&c->abort_flag, 1u);
+    for (int q = 0; q < nproc; q++)
+      if (q != proc) st_relaxed_sys(&reinterpret_cast<CtrlBlock*>(heap[q] + ctrl_off)->abort_flag, 1u);
+  }
+}
+
+// End of a traced call: the last CTA to get here copies the per-key stamps and the status block to the host and
+// clears the stamps.  All threads of the CTA must call it; `s_last` is a shared-memory word.
+__device__ inline void publish_trace(CtrlBlock* c, TraceBlock* tb, TraceBlock* host_trace, StatusBlock* host_status,
+                                     int* s_last) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    *s_last = atomicAdd(&c->exit_count, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < kMaxTraceKeys; i += blockDim.x) {
+    if (host_trace) { host_trace->kstart[i] = __ldcg(&tb->kstart[i]); host_trace->kend[i] = __ldcg(&tb->kend[i]); }
+    tb->kstart[i] = ~0ull;
+    tb->kend[i] = 0ull;
+  }
+  if (threadIdx.x == 0) {
+    c->exit_count = 0;
+    if (host_status) {
+      for (int i = 0; i < 8; i++) host_status->trace[i] = c->status.trace[i];
+    }
+  }
 }
 
 }  // namespace dev

@@ -14,7 +14,8 @@ static const char* kAlgoNames[ALG_COUNT] = {
     "xor",             "twolayer_linear",  "twolayer_linear_s2", "twolayer_linear_s3",
     "twolayer_linear_s4", "rbruck",        "rbruck_om",        "tuna",
     "tuna2",           "ttpl",             "ttpl_bt",          "ttpl_bt_s1",
-    "ttpl_bt_s2",      "uniform_spreadout_twolayer", "uniform_isplit_rbruck"};
+    "ttpl_bt_s2",      "uniform_spreadout_twolayer", "uniform_isplit_rbruck",
+    "merge",           "simple_merge",     "split"};
 
 const char* algo_name(int algo) {
   return (algo >= 0 && algo < ALG_COUNT) ? kAlgoNames[algo] : "unknown";
@@ -91,14 +92,35 @@ struct Builder {
     std::stable_sort(tmp.begin(), tmp.end(),
                      [](const TmpOp& a, const TmpOp& b) { return a.order < b.order; });
     pl.ops.reserve(tmp.size());
-    std::map<uint32_t, int> keys;
     for (auto& t : tmp) {
+      if (pl.keys.empty() || pl.keys.back() != t.op.key) pl.keys.push_back(t.op.key);
+      t.op.flags = (t.op.flags & 0xffffu) | ((uint32_t)(pl.keys.size() - 1) << 16);
       pl.ops.push_back(t.op);
-      keys[t.op.key]++;
       if (!(t.op.flags & 1u)) pl.stats.hops++;
     }
-    pl.stats.phases = (int)keys.size();
+    pl.stats.phases = (int)pl.keys.size();
     pl.ncells = (int)cells.size();
+    check_coverage();
+  }
+  // Every (origin, destination) pair must leave its origin exactly once per call (in `nparts` slices when the
+  // block is split), and every rank copies its own block exactly once.
+  void check_coverage() {
+    if (pl.keys.size() > 65535u) { pl.err = -13; pl.errmsg = "too many distinct issue keys"; return; }
+    std::vector<int> seen((size_t)P * P, 0), want((size_t)P * P, 1);
+    for (const Op& o : pl.ops) {
+      if (o.src_cell >= 0) continue;
+      if (o.origin != o.src) { pl.err = -13; pl.errmsg = "first hop executed by a rank that is not the origin"; return; }
+      const size_t i = (size_t)o.origin * P + o.dest;
+      seen[i]++;
+      if (op_nparts(o)) want[i] = (int)op_nparts(o);
+    }
+    for (size_t i = 0; i < seen.size(); i++)
+      if (seen[i] != want[i]) {
+        pl.err = -13;
+        pl.errmsg = "schedule does not send block " + std::to_string(i / P) + " -> " + std::to_string(i % P) +
+                    " exactly once";
+        return;
+      }
   }
 };
 
@@ -388,6 +410,65 @@ void build_twolayer_linear(Builder& B, const AlgoSpec& s) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Leader-routed exchanges (reference: benchmarks/merge_benchmark.cpp:155-332 and
+// benchmarks/simple_merge_benchmark.cpp:138-210).  The ranks of a group hand their blocks to one
+// leader, the leaders exchange them, and each leader hands the blocks to their destinations:
+//   S -> leader(group of S) -> leader(group of D) -> D,
+// where a hop is dropped when both ends are the same rank.  In the "merge" scheme local rank 0 of
+// every group is the rank with the large messages: it neither gathers nor is gathered (it talks to
+// the other groups' rank 0 and leaders directly) and local rank 1 is the leader of the small-message
+// ranks.  The reference stops before the hand-out to the destinations (its scatter is commented out);
+// here it is done.  In the "simple merge" scheme local rank 0 is the leader of everybody.
+// Keys: phase 1 gather, phase 2 exchange between holders (spread-out order over the holder index),
+// phase 3 hand-out, so the three stages can be timed separately, like the reference's
+// gather_time / ata_time / scatter_time.
+// ---------------------------------------------------------------------------------------------
+void build_leader_routed(Builder& B, int n, int leader_lr, int exempt_lr) {
+  const int P = B.P, G = P / n;
+  auto holder = [&](int R) { return (R % n == exempt_lr) ? R : (R / n) * n + leader_lr; };
+  // index of a holder among the ranks that take part in the exchange stage (for the spread-out order)
+  auto hidx = [&](int H) { return (H / n) * 2 + ((H % n == leader_lr) ? 1 : 0); };
+  for (int R = 0; R < P; R++) B.self_copy(R);
+  for (int S = 0; S < P; S++)
+    for (int D = 0; D < P; D++) {
+      if (S == D) continue;
+      const int h1 = holder(S), h2 = holder(D);
+      int cur = S, cell = -1;
+      if (h1 != cur) {                                  // gather
+        const int dc = (h1 == D) ? -1 : B.cell(3, 1, S % n, D);
+        B.emit(1, 0, (uint32_t)(S % n) * P + D, cur, h1, S, D, cell, dc);
+        cur = h1; cell = dc;
+      }
+      if (cur != D && h2 != cur) {                      // exchange between holders
+        const int dc = (h2 == D) ? -1 : B.cell(3, 2, S, D % n);
+        const int dist = mod(hidx(cur) - hidx(h2), 2 * G);
+        B.emit(2, 0, (uint32_t)dist * P * P + (uint32_t)S * P + D, cur, h2, S, D, cell, dc);
+        cur = h2; cell = dc;
+      }
+      if (cur != D) B.emit(3, 0, (uint32_t)(D % n) * P + S, cur, D, S, D, cell, -1);   // hand-out
+    }
+}
+
+// Spread-out exchange in which the block from rank 0 to rank P - 1 (the one huge block of the reference's
+// benchmark) travels as `parts` separate messages, all posted together with the other blocks
+// (benchmarks/split_benchmark.cpp:147-205; the reference drops count % P elements, here the last part
+// takes them).
+void build_split(Builder& B, int parts) {
+  const int P = B.P;
+  for (int R = 0; R < P; R++)
+    for (int i = 0; i < P; i++) {
+      const int T = mod(R - i, P);
+      if (R == 0 && T == P - 1 && P > 1 && parts > 1) {
+        for (int p = 0; p < parts; p++) {
+          B.emit(1, 0, (uint32_t)i * 256 + p, R, T, R, T, -1, -1, ((uint32_t)p << 2) | ((uint32_t)parts << 9));
+        }
+      } else {
+        B.direct(1, 0, (uint32_t)i * 256, R, T);
+      }
+    }
+}
+
 bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
 }  // namespace
@@ -406,6 +487,7 @@ Plan build_plan(const AlgoSpec& in) {
 
   const bool hier = (s.algo >= ALG_TTPL && s.algo <= ALG_UNIFORM_ISPLIT_RBRUCK);
   const bool tl_linear = (s.algo >= ALG_TWOLAYER_LINEAR && s.algo <= ALG_TWOLAYER_LINEAR_S4);
+  const bool leader = (s.algo == ALG_MERGE || s.algo == ALG_SIMPLE_MERGE);
 
   // Argument rules of the reference (return codes and clamps), evaluated before the P == 1 shortcut
   // so that an invalid radix is reported for every P.
@@ -425,7 +507,15 @@ Plan build_plan(const AlgoSpec& in) {
     case ALG_XOR:
       if (!is_pow2(P)) return fail(-1, "XOR exchange needs a power-of-two rank count");  // src/exclusive_or_alltoallv.cpp:31
       break;
+    case ALG_SPLIT:
+      if (s.b <= 0 || s.b > kMaxOpParts) s.b = std::min(P, kMaxOpParts);   // one message per rank, as the reference
+      break;
     default: break;
+  }
+  if (leader) {
+    if (s.n < 1) return fail(-1, "group size must be >= 1");
+    if (s.n > P) s.n = P;
+    if (P % s.n != 0) return fail(-1, "group size must divide the rank count");
   }
   if (hier || tl_linear) {
     if (hier && s.algo != ALG_UNIFORM_ISPLIT_RBRUCK && s.r < 2) return fail(-1, "radix must be >= 2");
@@ -466,6 +556,9 @@ Plan build_plan(const AlgoSpec& in) {
     case ALG_RBRUCK_OM: build_flat_bruck(B, s.r, false, 0, false); break;
     case ALG_TUNA:      build_flat_bruck(B, s.r, false, s.b, false); break;
     case ALG_TUNA2:     build_flat_bruck(B, s.r, false, s.b, true); break;
+    case ALG_MERGE:        build_leader_routed(B, s.n, s.n >= 2 ? 1 : 0, s.n >= 2 ? 0 : -1); break;
+    case ALG_SIMPLE_MERGE: build_leader_routed(B, s.n, 0, -1); break;
+    case ALG_SPLIT:        build_split(B, s.b); break;
     default:
       if (hier) build_hier(B, s);
       else if (tl_linear) build_twolayer_linear(B, s);
@@ -497,11 +590,14 @@ int host_execute(const Plan& plan, int ts, const char* const* sendbufs, char* co
   }
   for (const Op& o : plan.ops) {
     if (o.src >= P || o.dst >= P || o.origin >= P || o.dest >= P) return -12;
-    const size_t bytes = (size_t)sendcounts[(size_t)o.origin * P + o.dest] * ts;
+    long long first = 0, cnt = 0;
+    op_slice(o, sendcounts[(size_t)o.origin * P + o.dest], &first, &cnt);
+    if (op_nparts(o) && (o.src_cell >= 0 || o.dst_cell >= 0)) return -12;   // slices travel in one hop only
+    const size_t bytes = (size_t)cnt * ts;
     const char* src;
     if (o.src_cell < 0) {
       if (o.src != o.origin) return -12;
-      src = sendbufs[o.src] + sdispls[(size_t)o.src * P + o.dest] * ts;
+      src = sendbufs[o.src] + (sdispls[(size_t)o.src * P + o.dest] + first) * ts;
     } else {
       if (o.src_cell >= plan.ncells) return -12;
       if (state[o.src][o.src_cell] != 1) return -10;
@@ -511,7 +607,7 @@ int host_execute(const Plan& plan, int ts, const char* const* sendbufs, char* co
     char* dst;
     if (o.dst_cell < 0) {
       if (o.dst != o.dest) return -12;
-      dst = recvbufs[o.dst] + rdispls[(size_t)o.dst * P + o.origin] * ts;
+      dst = recvbufs[o.dst] + (rdispls[(size_t)o.dst * P + o.origin] + first) * ts;
     } else {
       if (o.dst_cell >= plan.ncells) return -12;
       if (state[o.dst][o.dst_cell] != 0) return -11;

@@ -40,21 +40,52 @@ def env_overrides() -> dict:
     return out
 
 
+SAFE_CHOICE = {"algo": "spreadout", "protocol": "rendezvous"}
+
+
+def agreed_block_stats(c, sendcounts, ts: int):
+    """(mean block bytes, coefficient of variation) of the WHOLE exchange: the sums over this process's rows are
+    added up over the host side group, so every process gets the same two numbers (a process that looked at its
+    own rows only would, with skewed counts, land in another size class than its peers and pick another
+    algorithm or protocol, which ends in a time-out)."""
+    a = np.asarray(sendcounts, dtype=np.float64).ravel() * ts
+    acc = torch.tensor([float(a.sum()), float((a * a).sum()), float(a.size)], dtype=torch.float64)
+    side = getattr(c, "_side", None)
+    if side is not None:
+        c._dist.all_reduce(acc, group=side)
+    s1, s2, n = (float(v) for v in acc)
+    if n <= 0 or s1 <= 0:
+        return 0.0, 0.0
+    mean = s1 / n
+    return mean, float(np.sqrt(max(s2 / n - mean * mean, 0.0)) / mean)
+
+
 def _auto_choice(c, recv, sendcounts, kw, agree_on_max: bool):
-    """Resolves ``algo="auto"`` into keyword arguments for the communicator, using the tuner table."""
+    """Resolves ``algo="auto"`` into keyword arguments for the communicator, using the tuner table.  The outcome is
+    the same on every process: persistent calls (``agree_on_max``) agree on the size and skew class by a host-side
+    reduction; one-shot calls of a multi-process communicator use the caller's ``mean_block_bytes=`` hint (which
+    must be the same everywhere) or, without it, the spread-out order with the rendezvous protocol, which mixes
+    safely with itself whatever the counts are."""
     ts = kw.get("type_size") or (recv.element_size() if isinstance(recv, torch.Tensor) else recv[0].element_size())
     host_counts = not (isinstance(sendcounts, torch.Tensor) and sendcounts.is_cuda)
-    if host_counts:
-        mean_block = float(np.mean(np.asarray(sendcounts))) * ts
+    kw = dict(kw)
+    hint = kw.pop("mean_block_bytes", None)
+    cv = float(kw.pop("block_cv", 0.0) or 0.0)
+    multi = getattr(c, "nproc", 1) > 1
+    if hint is not None:
+        mean_block = float(hint)
+    elif host_counts and (agree_on_max or not multi):
+        mean_block, cv = agreed_block_stats(c, sendcounts, ts) if agree_on_max else _tuner.block_stats(sendcounts, ts)
+    elif not host_counts and kw.get("bytes_hint", -1) and kw.get("bytes_hint", -1) > 0 and not multi:
+        mean_block = kw["bytes_hint"] / (c.L * c.P)
     else:
-        hint = kw.get("bytes_hint", -1)
-        mean_block = hint / (c.L * c.P) if hint and hint > 0 else 64 << 10
-    choice = _tuner.choose(c.P, c.nproc, mean_block)
+        mean_block = None
+    choice = _tuner.choose(c.P, c.nproc, mean_block, cv) if mean_block is not None else dict(SAFE_CHOICE)
     forced = env_overrides()
     if "algo" in forced and forced["algo"] != choice.get("algo"):
         choice = {"algo": forced["algo"], "protocol": choice.get("protocol", "rendezvous")}   # drop the other algorithm's knobs
     choice.update(forced)
-    out = dict(kw)
+    out = kw
     out["algo"] = choice.pop("algo")
     protocol = choice.pop("protocol", "rendezvous")
     # The eager protocol needs one cell size on all ranks: either the caller promises an upper bound
@@ -74,13 +105,16 @@ def alltoallv(send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=Non
               algo: str = "auto", **kw) -> None:
     """One-shot call.  With ``algo="auto"`` the tuner picks algorithm, radix and batch; the low-latency eager
     protocol is used only when the caller bounds the block size with ``max_block_bytes=`` (a one-shot call does
-    not pay for a host-side reduction; :func:`prepare` does)."""
+    not pay for a host-side reduction; :func:`prepare` does).  Across several processes the choice needs a number
+    that is the same on all of them: pass ``mean_block_bytes=`` (and optionally ``block_cv=``), or the call uses
+    the spread-out order with the rendezvous protocol."""
     c = comm or _comm.get_default_comm()
     if algo == "auto":
         kw = _auto_choice(c, recv, sendcounts, kw, agree_on_max=False)
         algo = kw.pop("algo")
     else:
-        kw.pop("max_block_bytes", None)
+        for k in ("max_block_bytes", "mean_block_bytes", "block_cv"):
+            kw.pop(k, None)
     c.alltoallv(send, recv, sendcounts, sdispls, recvcounts, rdispls, algo=algo, **kw)
 
 
@@ -93,7 +127,8 @@ def prepare(send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None,
         kw = _auto_choice(c, recv, sendcounts, kw, agree_on_max=True)
         algo = kw.pop("algo")
     else:
-        kw.pop("max_block_bytes", None)
+        for k in ("max_block_bytes", "mean_block_bytes", "block_cv"):
+            kw.pop(k, None)
     kw.pop("stream", None)
     return c.prepare(send, recv, sendcounts, sdispls, recvcounts, rdispls, algo=algo, **kw)
 

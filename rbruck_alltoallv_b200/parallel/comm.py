@@ -51,11 +51,18 @@ class _Block:
 class PreparedCall:
     """A resolved collective; see :meth:`Communicator.prepare`."""
 
+    KINDS = {0: "rendezvous", 1: "eager", 2: "static"}
+
     def __init__(self, comm: "Communicator", handle, keep):
         self._comm, self._h, self._keep = comm, C.c_void_p(handle), keep
         self._launch = comm._lib.rbv_launch
         self._ctx = comm._ctx
         self._dev = comm.device
+        info = (C.c_longlong * 3)()
+        #: which kernel runs the call: "static" (all counts resolved on the host, no metadata phase),
+        #: "rendezvous" (metadata exchanged by the kernel) or "eager"
+        self.kind = self.KINDS[comm._lib.rbv_prepared_info(self._h, info)]
+        self.grid, self.cooperative, self.items = int(info[0]), bool(info[1]), int(info[2])
 
     def launch(self, stream: Optional[torch.cuda.Stream] = None) -> None:
         st = stream or torch.cuda.current_stream(self._dev)
@@ -262,6 +269,7 @@ class Communicator:
         # through a symmetric bounce buffer (two extra local copies; the eager protocol needs none).
         recv_l = [recv] if isinstance(recv, torch.Tensor) else list(recv)
         bounce = None
+        st = stream or torch.cuda.current_stream(self.device)
         if not eager_max_bytes and not inplace:
             outside = [not self._lib.rbv_ctx_in_heap(self._ctx, C.c_void_p(t.data_ptr()), t.numel() * t.element_size())
                        for t in recv_l]
@@ -270,7 +278,8 @@ class Communicator:
                 for t, out in zip(recv_l, outside):
                     if out:
                         bt = self._bounce_for(t)
-                        bt.copy_(t.reshape(-1).view(torch.uint8), non_blocking=True)   # keep what lies between the blocks
+                        with torch.cuda.stream(st):   # ordered with the collective, whatever the current stream is
+                            bt.copy_(t.reshape(-1).view(torch.uint8), non_blocking=True)   # keep what lies between the blocks
                         bounce.append(bt)
                     else:
                         bounce.append(t)
@@ -279,7 +288,6 @@ class Communicator:
                     type_size = recv_l[0].element_size()
         ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
-        st = stream or torch.cuda.current_stream(self.device)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
         self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
         self._lib.rbv_ctx_set_bulk(self._ctx, int(self._bulk if bulk is None else bulk))
@@ -289,9 +297,10 @@ class Communicator:
         if rcode:
             raise CommError(f"alltoallv({algo}) failed with code {rcode}: {self._lib.rbv_last_error().decode()}")
         if bounce is not None:
-            for t, bt in zip(recv_l, bounce):
-                if bt is not t:
-                    t.reshape(-1).view(torch.uint8).copy_(bt, non_blocking=True)
+            with torch.cuda.stream(st):
+                for t, bt in zip(recv_l, bounce):
+                    if bt is not t:
+                        t.reshape(-1).view(torch.uint8).copy_(bt, non_blocking=True)
 
     def _bounce_for(self, t: torch.Tensor) -> torch.Tensor:
         """A symmetric buffer of t's size, kept for reuse (one per size and position in the call)."""
@@ -325,23 +334,72 @@ class Communicator:
     def prepare(self, send, recv, sendcounts, sdispls=None, recvcounts=None, rdispls=None, *,
                 algo: str = "spreadout", n: int = 0, r: int = 2, r2: int = 0, b: int = 0, b2: int = 0,
                 type_size: Optional[int] = None, inplace: bool = False, grid: int = 0, chunk_bytes: int = 0,
-                bytes_hint: int = -1, eager_max_bytes: int = 0, bulk: Optional[int] = None) -> "PreparedCall":
+                bytes_hint: int = -1, eager_max_bytes: int = 0, bulk: Optional[int] = None,
+                static: Optional[bool] = None) -> "PreparedCall":
         """Persistent form of :meth:`alltoallv` (compare ``MPI_Alltoallv_init``): everything is resolved once;
         ``.launch()`` then costs one kernel launch.  Buffers and counts are fixed (device-resident counts are
-        re-read by every launch, so a router may still change their values)."""
+        re-read by every launch, so a router may still change their values).
+
+        With host-side counts the rendezvous protocol is resolved completely on the host: the processes gather
+        each other's counts, displacements and buffer offsets over the host side group here, once, and every launch
+        runs the static kernel, which has no metadata phase (``static=False`` or ``RBV_STATIC=0`` keeps the
+        kernel that exchanges metadata itself).  Collective over the processes."""
         ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
         self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
         self._lib.rbv_ctx_set_bulk(self._ctx, int(self._bulk if bulk is None else bulk))
-        h = self._lib.rbv_prepare(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
-                                  1 if on_dev else 0, int(bytes_hint), 1 if inplace else 0, int(grid),
-                                  int(chunk_bytes))
+        if static is None:
+            static = os.environ.get("RBV_STATIC", "1") != "0"
+        flags = (1 if inplace else 0) | (0 if static else 0x100)
+        g = (None, None, None, None)
+        if self.nproc > 1 and not eager_max_bytes and not inplace:
+            g = self._gather_global(keep, on_dev or not static)
+        h = self._lib.rbv_prepare_global(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
+                                         1 if on_dev else 0, int(bytes_hint), flags, int(grid), int(chunk_bytes), *g)
         if not h:
             raise CommError(f"prepare({algo}) failed: {self._lib.rbv_last_error().decode()}")
         return PreparedCall(self, h, keep)
 
+    def _gather_global(self, keep, opt_out: bool):
+        """All processes' host-side arguments of one call, as the four tables ``rbv_prepare_global`` takes (or four
+        ``None`` when some process cannot take part: device-resident counts, static resolution switched off).
+        ``keep`` is the list :meth:`_marshal` built: ... sc, rc, sd, rd, send pointers, receive pointers."""
+        sc, rc, sd, rd = keep[2:6] if not opt_out else (None, None, None, None)
+        mine = None
+        if not opt_out:
+            base = int(self._lib.rbv_ctx_heap(self._ctx, self.proc))
+            off = np.array([int(p) - base for p in keep[-1]], dtype=np.uint64)
+            mine = (sc, rc, rd, off)
+        allv = [None] * self.nproc
+        self._dist.all_gather_object(allv, mine, group=self._side)
+        if any(v is None for v in allv):
+            return (None, None, None, None)
+        g_counts = np.ascontiguousarray(np.concatenate([v[0] for v in allv], axis=0), dtype=np.int32)
+        have_caps = all(v[1] is not None for v in allv)
+        g_caps = np.ascontiguousarray(np.concatenate([v[1] for v in allv], axis=0), dtype=np.int32) if have_caps else None
+        g_rd = np.ascontiguousarray(np.concatenate([v[2] for v in allv], axis=0), dtype=np.int64)
+        g_off = np.ascontiguousarray(np.concatenate([v[3] for v in allv]), dtype=np.uint64)
+        keep += [g_counts, g_caps, g_rd, g_off]
+        return (g_counts.ctypes.data, g_caps.ctypes.data if g_caps is not None else None, g_rd.ctypes.data,
+                g_off.ctypes.data)
+
     # ---- status -------------------------------------------------------------------------------
+    def trace(self) -> list:
+        """Per-key time stamps of the most recent call made with :meth:`enable_trace` on: one entry per key of the
+        schedule (a round or a batch), ``{"phase", "step", "start_us", "end_us"}`` relative to the first start;
+        phase 0 self copies, 1 intra-group / flat rounds, 2 inter-group, 3 hand-out, 255 eager unpacking."""
+        n = 257
+        keys, t0, t1 = (C.c_uint * n)(), (C.c_ulonglong * n)(), (C.c_ulonglong * n)()
+        self._lib.rbv_ctx_set_stream(self._ctx, C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        m = self._lib.rbv_ctx_last_trace(self._ctx, keys, t0, t1, n)
+        rows = [(int(keys[i]), int(t0[i]), int(t1[i])) for i in range(m) if int(t0[i]) != 2 ** 64 - 1 and int(t1[i])]
+        if not rows:
+            return []
+        base = min(r[1] for r in rows)
+        return [{"phase": k >> 24, "step": k & 0xffffff, "start_us": (a - base) / 1e3, "end_us": (b - base) / 1e3}
+                for k, a, b in rows]
+
     def status(self) -> dict:
         """Synchronises the current stream and returns the device-side status of the last call."""
         st = Status()
@@ -377,8 +435,11 @@ class Communicator:
         """Have every following call report its phase time stamps (``status()['phases_us']``)."""
         self._lib.rbv_ctx_set_trace(self._ctx, 1 if on else 0)
 
-    def set_cooperative(self, on: bool) -> None:
-        self._lib.rbv_ctx_set_cooperative(self._ctx, 1 if on else 0)
+    def set_cooperative(self, mode) -> None:
+        """Kernel launch mode: ``None`` / -1 cooperative only where a call needs all its CTAs resident (default),
+        ``True`` / 1 always cooperative, ``False`` / 0 never (in-place calls excepted)."""
+        m = -1 if mode is None else int(mode)
+        self._lib.rbv_ctx_set_cooperative(self._ctx, -1 if m < 0 else (1 if m else 0))
 
     def set_timeout_ms(self, ms: float) -> None:
         self._lib.rbv_ctx_set_timeout_ms(self._ctx, float(ms))

@@ -19,11 +19,13 @@ ALGOS = (
     "rbruck", "rbruck_om", "tuna", "tuna2",
     "ttpl", "ttpl_bt", "ttpl_bt_s1", "ttpl_bt_s2",
     "uniform_spreadout_twolayer", "uniform_isplit_rbruck",
+    "merge", "simple_merge", "split",
 )
 ALGO_ID = {name: i for i, name in enumerate(ALGOS)}
 HIERARCHICAL = {"ttpl", "ttpl_bt", "ttpl_bt_s1", "ttpl_bt_s2", "uniform_spreadout_twolayer",
                 "uniform_isplit_rbruck", "twolayer_linear", "twolayer_linear_s2", "twolayer_linear_s3",
                 "twolayer_linear_s4"}
+LEADER_ROUTED = {"merge", "simple_merge"}
 
 OP_DTYPE = np.dtype([("src", "<u2"), ("dst", "<u2"), ("origin", "<u2"), ("dest", "<u2"),
                      ("src_cell", "<i4"), ("dst_cell", "<i4"), ("key", "<u4"), ("flags", "<u4")])

@@ -1,10 +1,14 @@
 """Algorithm selection from measured timings.
 
-The reference has no selection logic beyond a hard-coded table of batch limits by rank count
-(examples/twophaseLayer_example2.cpp:136-152).  Here a table of measured timings, keyed by
-(ranks, processes, message-size class), decides algorithm, radix and batch.  ``sweep`` fills the table on
-the machine at hand; ``choose`` reads it and falls back to the built-in defaults measured on 8 x B200.
-The table is the only state the library persists (JSON under ``$RBV_TUNER_CACHE`` or the package folder).
+The reference has no selection logic beyond a hard-coded table of batch limits by rank count and block size
+(examples/twophaseLayer_example2.cpp:136-152) and sweeps of the batch parameter in its drivers
+(examples/twophaseLayer_example.cpp:120-144, twophaseLayer_example2.cpp:96-191).  Here a table of measured
+timings, keyed by (ranks, processes, message-size class, skew class), decides algorithm, group size, radix, batch
+and protocol.  ``sweep`` fills the table on the machine at hand (batch and group size are swept too); ``choose``
+reads it and falls back to the built-in rule.  Candidates are listed simplest first and a later candidate only
+replaces the current winner when it is more than ``MARGIN`` faster, so that differences inside the measurement
+noise never put an exotic schedule into the table.  The table is the only state the library persists (JSON
+under ``$RBV_TUNER_CACHE`` or the package folder); the C API reads the same file (``csrc/api/tuner_native.cpp``).
 """
 from __future__ import annotations
 
@@ -26,8 +30,27 @@ def _cache_path() -> Path:
     return Path(p) if p else Path(__file__).resolve().parent / "tuner_table.json"
 
 
-def _key(P: int, nproc: int, cls: int) -> str:
-    return f"P{P}-G{nproc}-c{cls}"
+MARGIN = 0.03          # a candidate must beat the current winner by more than this fraction to replace it
+MIN_STEPS = 30         # timed steps per candidate in a sweep
+SKEW_CV = 0.5          # coefficient of variation of the block sizes from which an exchange counts as skewed
+
+
+def skew_class(cv: float) -> int:
+    """0: balanced (block sizes within about +-50 % of the mean), 1: skewed (Zipf-like, many empty blocks)."""
+    return 1 if cv >= SKEW_CV else 0
+
+
+def block_stats(counts, type_size: int = 1):
+    """(mean block bytes, coefficient of variation) of a count matrix."""
+    import numpy as np
+    a = np.asarray(counts, dtype=np.float64).ravel() * type_size
+    if a.size == 0 or a.mean() <= 0:
+        return 0.0, 0.0
+    return float(a.mean()), float(a.std() / a.mean())
+
+
+def _key(P: int, nproc: int, cls: int, skew: int = 0) -> str:
+    return f"P{P}-G{nproc}-c{cls}" + (f"-s{skew}" if skew else "")
 
 
 def load_table() -> Dict[str, dict]:
@@ -50,11 +73,26 @@ def save_table() -> None:
     os.replace(tmp, path)
 
 
-def record(P: int, nproc: int, mean_block_bytes: float, choice: dict, us: float) -> None:
+def record(P: int, nproc: int, mean_block_bytes: float, choice: dict, us: float, cv: float = 0.0,
+           replace: bool = False) -> None:
+    """Enters a measurement.  An existing entry is replaced only by one that is more than ``MARGIN`` faster
+    (``replace=True``: unconditionally, for a fresh sweep whose winner was chosen by the same rule)."""
     tab = load_table()
-    k = _key(P, nproc, size_class(mean_block_bytes))
-    if k not in tab or us < tab[k]["us"]:
+    k = _key(P, nproc, size_class(mean_block_bytes), skew_class(cv))
+    if replace or k not in tab or us < tab[k]["us"] * (1.0 - MARGIN):
         tab[k] = {"choice": choice, "us": us}
+
+
+def pick_winner(timings) -> tuple:
+    """``timings``: (choice, microseconds) in order of preference, simplest first.  Returns the first entry that no
+    later entry beats by more than ``MARGIN``: the simplest configuration within the margin of the best."""
+    best = None
+    for choice, us in timings:
+        if us is None:
+            continue
+        if best is None or us < best[1] * (1.0 - MARGIN):
+            best = (choice, us)
+    return best
 
 
 def default_choice(P: int, nproc: int, mean_block_bytes: float) -> dict:
@@ -66,36 +104,65 @@ def default_choice(P: int, nproc: int, mean_block_bytes: float) -> dict:
     return {"algo": "spreadout", "protocol": "eager" if mean_block_bytes <= (64 << 10) else "rendezvous"}
 
 
-def choose(P: int, nproc: int, mean_block_bytes: float) -> dict:
+def choose(P: int, nproc: int, mean_block_bytes: float, cv: float = 0.0) -> dict:
+    """The table's entry for this size and skew class; neighbours (other skew class first, then the adjacent size
+    classes) stand in for classes that were not measured; then the built-in rule."""
     tab = load_table()
-    cls = size_class(mean_block_bytes)
+    cls, sk = size_class(mean_block_bytes), skew_class(cv)
     for c in (cls, cls - 1, cls + 1):
-        hit = tab.get(_key(P, nproc, c))
-        if hit:
-            return dict(hit["choice"])
+        for s in (sk, 1 - sk):
+            hit = tab.get(_key(P, nproc, c, s))
+            if hit:
+                return dict(hit["choice"])
     return default_choice(P, nproc, mean_block_bytes)
 
 
-def candidates(P: int, groups: Optional[List[int]] = None) -> List[dict]:
-    """The configurations a sweep tries."""
-    out: List[dict] = [{"algo": "spreadout"}, {"algo": "linear"}, {"algo": "pairwise"},
-                       {"algo": "scattered", "b": max(1, P // 2)}]
-    if P & (P - 1) == 0:
-        out.append({"algo": "xor"})
-    for r in sorted({2, 3, 4, P}):
-        if 2 <= r <= P:
-            out.append({"algo": "rbruck", "r": r})
-            out.append({"algo": "tuna2", "r": min(r, max(2, P - 1)), "b": 0})
-    for n in (groups or [g for g in (2, 4) if P % g == 0 and g < P]):
-        out.append({"algo": "ttpl_bt_s1", "n": n, "r": 2, "b": 0})
-        out.append({"algo": "ttpl_bt", "n": n, "r": 2, "b": 0})
+def _pow2_upto(limit: int) -> List[int]:
+    out, b = [], 1
+    while b < limit:
+        out.append(b)
+        b *= 2
     return out
 
 
+def candidates(P: int, groups: Optional[List[int]] = None, full: bool = True) -> List[dict]:
+    """The configurations a sweep tries, simplest first (single hop, then flat Bruck by decreasing radix, then the
+    two-layer schedules).  Batch parameters run over 1, 2, 4, ... like the reference's drivers sweep them
+    (0 = everything in flight at once); ``full=False`` keeps one batch value per schedule."""
+    out: List[dict] = [{"algo": "spreadout"}, {"algo": "linear"}, {"algo": "pairwise"}]
+    if P & (P - 1) == 0:
+        out.append({"algo": "xor"})
+    for b in (_pow2_upto(P) if full else [max(1, P // 2)]):
+        out.append({"algo": "scattered", "b": b})
+    for r in sorted({2, 3, 4, P}, reverse=True):
+        if 2 <= r <= P:
+            out.append({"algo": "rbruck", "r": r})
+            rt = min(r, max(2, P - 1))
+            for b in ([0] + _pow2_upto(rt - 1) if full else [0]):
+                out.append({"algo": "tuna2", "r": rt, "b": b})
+    for n in (groups or [g for g in (2, 4, 8, 16) if P % g == 0 and g < P]):
+        G = P // n
+        for b in ([0] + _pow2_upto(P) if full else [0]):
+            out.append({"algo": "ttpl_bt_s1", "n": n, "r": 2, "b": b})
+        for b in ([0] + _pow2_upto(G) if full else [0]):
+            out.append({"algo": "ttpl_bt", "n": n, "r": 2, "b": b})
+    seen, uniq = set(), []
+    for c in out:
+        k = tuple(sorted(c.items()))
+        if k not in seen:
+            seen.add(k)
+            uniq.append(c)
+    return uniq
+
+
 def sweep(comm, mean_block_bytes=(16, 256, 4096, 65536, 1 << 20, 4 << 20), type_size: int = 2, skew: str = "normal",
-          steps: int = 10, warmup: int = 3, seed: int = 0, groups=None, verbose: bool = True) -> List[dict]:
+          steps: int = MIN_STEPS, warmup: int = 3, seed: int = 0, groups=None, verbose: bool = True,
+          full: bool = True) -> List[dict]:
     """Times every candidate (both protocols where the blocks fit the eager cells) for each size class on
-    ``comm`` and records the winners in the table.  Collective: every process of the communicator calls it."""
+    ``comm`` and records the winners in the table: at least ``MIN_STEPS`` timed steps per candidate, median, and
+    the simplest candidate within ``MARGIN`` of the best wins (:func:`pick_winner`).  Collective: every process of
+    the communicator calls it."""
+    steps = max(int(steps), MIN_STEPS)
     import numpy as np
     import torch
 
@@ -115,10 +182,11 @@ def sweep(comm, mean_block_bytes=(16, 256, 4096, 65536, 1 << 20, 4 << 20), type_
         recv = [comm.symm_empty(max(int(rc[i].sum()), 1) * type_size, torch.uint8) for i in range(L)]
         emax = comm.max_block_bytes(sc, type_size)
         cell_room = comm.arena_bytes // (2 * max(emax, 8) + 16)
-        row = {"mean_block_bytes": nbytes, "skew": skew, "max_block_bytes": emax, "us": {}}
-        best, best_us = None, float("inf")
-        for cand in candidates(P, groups):
-            for eager in (False, True):
+        mean_b, cv = block_stats(counts, type_size)
+        row = {"mean_block_bytes": nbytes, "skew": skew, "cv": round(cv, 3), "max_block_bytes": emax, "us": {}}
+        timings = []
+        for cand in candidates(P, groups, full):
+            for eager in (True, False):
                 kw = dict(cand)
                 if eager:
                     if emax > (256 << 10) or cell_room < P + 64:
@@ -137,12 +205,13 @@ def sweep(comm, mean_block_bytes=(16, 256, 4096, 65536, 1 << 20, 4 << 20), type_
                     continue
                 us = float(np.median(t)) * 1e3
                 row["us"][name] = round(us, 2)
-                if us < best_us:
-                    best, best_us = dict(cand, protocol="eager" if eager else "rendezvous"), us
-        if best is not None:
-            record(P, comm.nproc, nbytes, best, best_us)
-            row["best"] = best
-            row["best_us"] = round(best_us, 2)
+                timings.append((dict(cand, protocol="eager" if eager else "rendezvous"), us))
+        win = pick_winner(timings)
+        if win is not None:
+            record(P, comm.nproc, mean_b, win[0], win[1], cv=cv, replace=True)
+            row["best"] = win[0]
+            row["best_us"] = round(win[1], 2)
+            row["fastest_us"] = round(min(u for _, u in timings), 2)
         rows.append(row)
         if verbose and comm.proc == 0:
             print(json.dumps(row), flush=True)

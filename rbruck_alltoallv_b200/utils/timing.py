@@ -39,8 +39,10 @@ class RankAligner:
         self.zd = np.zeros((L, P), dtype=np.int64)
         self.recv = [comm.symm_empty(16, torch.uint8) for _ in range(L)]
         self.send = [torch.empty(16, dtype=torch.uint8, device=f"cuda:{comm.device}") for _ in range(L)]
+        # the kernel that exchanges metadata waits for every rank's row: that wait is the alignment (the static
+        # kernel would find nothing to do for an exchange of empty blocks and return at once)
         self.call = comm.prepare(self.send, self.recv, self.z, self.zd, self.z, self.zd, algo="spreadout",
-                                 type_size=1, grid=1)
+                                 type_size=1, grid=1, static=False)
 
     def __call__(self):
         self.call.launch()

@@ -11,15 +11,17 @@ pytestmark = pytest.mark.gpu
 _comms = {}
 
 
-def get_comm(P):
+def get_comm(P, big_arena=False):
     from rbruck_alltoallv_b200.parallel.comm import Communicator
-    if P not in _comms:
-        _comms[P] = Communicator(nranks=P, heap_bytes=256 << 20, arena_bytes=4 << 20)
-    return _comms[P]
+    key = (P, big_arena)
+    if key not in _comms:
+        _comms[key] = Communicator(nranks=P, heap_bytes=256 << 20, arena_bytes=(24 << 20) if big_arena else (4 << 20))
+    return _comms[key]
 
 
-def run_case(P, algo, ts, counts, packed=True, seed=0, with_recvcounts=True, device_counts=False, **kw):
-    comm = get_comm(P)
+def run_case(P, algo, ts, counts, packed=True, seed=0, with_recvcounts=True, device_counts=False, persistent=False,
+             launches=1, big_arena=False, **kw):
+    comm = get_comm(P, big_arena)
     prob = oracle.make_problem(counts, ts, seed, packed=packed)
     send_h = oracle.fill_send(prob, seed)
     want = oracle.expected_recv(prob, send_h)
@@ -34,11 +36,21 @@ def run_case(P, algo, ts, counts, packed=True, seed=0, with_recvcounts=True, dev
         sd = torch.from_numpy(sd).cuda()
         rd = torch.from_numpy(rd).cuda()
         rc = torch.from_numpy(rc.astype(np.int32)).cuda() if rc is not None else None
-    comm.alltoallv(send, recv, sc, sd, rc, rd, algo=algo, type_size=ts, **kw)
+    call = None
+    if persistent:
+        call = comm.prepare(send, recv, sc, sd, rc, rd, algo=algo, type_size=ts, **kw)
+        for i in range(launches):
+            if i:
+                for t in recv:
+                    t.fill_(oracle.CANARY)
+            call.launch()
+    else:
+        comm.alltoallv(send, recv, sc, sd, rc, rd, algo=algo, type_size=ts, **kw)
     comm.check()
     got = [t.cpu().numpy() for t in recv]
     bad = oracle.first_mismatch(got, want)
     assert bad is None, f"{algo} P={P} {kw}: first mismatch at rank/offset {bad}"
+    return call
 
 
 ALL = [("linear", {}), ("spreadout", {}), ("scattered", dict(b=3)), ("pairwise", {}), ("xor", {}),
@@ -58,11 +70,114 @@ def test_all_algorithms_p8(algo, kw):
     run_case(8, algo, 4, counts, packed=False, seed=5, **kw)
 
 
+NEW_SCHEMES = [("merge", dict(n=4)), ("merge", dict(n=2)), ("simple_merge", dict(n=4)), ("simple_merge", dict(n=2)),
+               ("split", {}), ("split", dict(b=3))]
+
+
+@pytest.mark.parametrize("algo,kw", ALL + NEW_SCHEMES,
+                         ids=[f"{a}-{'-'.join(f'{k}{v}' for k, v in kw.items())}" for a, kw in ALL + NEW_SCHEMES])
+def test_static_kernel_all_algorithms_p8(algo, kw):
+    """Persistent calls with host-side counts run the static kernel (descriptors resolved on the host)."""
+    counts = dist.uniform(8, 300, seed=4)
+    counts[counts < 30] = 0
+    call = run_case(8, algo, 4, counts, packed=False, seed=6, persistent=True, launches=3, **kw)
+    assert call.kind == "static"
+
+
+@pytest.mark.parametrize("algo,kw", NEW_SCHEMES, ids=[f"{a}-{'-'.join(f'{k}{v}' for k, v in kw.items())}" for a, kw in NEW_SCHEMES])
+def test_leader_routed_and_split_schemes_dynamic_kernel(algo, kw):
+    counts = dist.uniform(8, 300, seed=14)
+    counts[counts < 30] = 0
+    run_case(8, algo, 8, counts, packed=False, seed=15, **kw)
+
+
+def test_static_kernel_forwards_chunk_by_chunk():
+    # blocks of about 0.5 MB in 16 KB chunks: relay hops start while earlier chunks of the same block still travel
+    counts = dist.normal(8, 120_000, seed=2)
+    for algo, kw in (("rbruck", dict(r=2)), ("tuna2", dict(r=2, b=0)), ("ttpl_bt_s1", dict(n=4, r=2)), ("merge", dict(n=4))):
+        call = run_case(8, algo, 4, counts, seed=3, persistent=True, launches=2, chunk_bytes=16 << 10, big_arena=True, **kw)
+        assert call.kind == "static" and call.items > 8 * 7 * 20
+    # the dynamic kernel has the same per-chunk flags
+    run_case(8, "rbruck", 4, counts, seed=4, r=2, chunk_bytes=16 << 10, big_arena=True)
+    run_case(8, "split", 4, counts, seed=5, persistent=True, chunk_bytes=32 << 10, big_arena=True)
+
+
+def test_static_kernel_refuses_what_the_host_can_see():
+    from rbruck_alltoallv_b200.parallel.comm import CommError
+    P, ts = 4, 4
+    comm = get_comm(P)
+    prob = oracle.make_problem(dist.constant(P, 64), ts, 0)
+    send = [torch.zeros(int(b), dtype=torch.uint8, device="cuda") for b in prob.send_bytes]
+    recv = [comm.symm_empty(int(b), torch.uint8) for b in prob.recv_bytes]
+    rc = prob.recvcounts.copy()
+    rc[2, 1] = 10                      # rank 2 expects less from rank 1 than rank 1 sends
+    with pytest.raises(CommError, match="larger than the receiver"):
+        comm.prepare(send, recv, prob.counts, prob.sdispls, rc, prob.rdispls, algo="spreadout", type_size=ts)
+    rd = prob.rdispls.copy()
+    rd[3, 0] += 1 << 40                # a displacement that would send a peer's stores outside the heap
+    with pytest.raises(CommError, match="heap"):
+        comm.prepare(send, recv, prob.counts, prob.sdispls, prob.recvcounts, rd, algo="spreadout", type_size=ts)
+    with pytest.raises(CommError, match="heap"):
+        comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, rd, algo="spreadout", type_size=ts)
+
+
+def test_eager_cells_never_show_flags_of_an_earlier_life():
+    """Eager units are valid by the call number in their flag words.  The cells must therefore never hold flag
+    words that did not come from the current numbering: not from rendezvous staging of user payload (which may
+    contain any value), not from calls made before reset() put the call number back, and not from a context whose
+    heap memory this context inherited."""
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    P, ts = 8, 4
+    for life in range(2):            # the second communicator is likely to get the first one's memory
+        comm = Communicator(nranks=P, heap_bytes=64 << 20, arena_bytes=2 << 20)
+
+        def eager_call(hi, seed):
+            counts = dist.uniform(P, hi, seed=seed)
+            prob = oracle.make_problem(counts, ts, seed, packed=True)
+            send_h = oracle.fill_send(prob, seed)
+            want = oracle.expected_recv(prob, send_h)
+            send = [torch.from_numpy(b).cuda() for b in send_h]
+            recv = [comm.symm_empty(len(w), torch.uint8) for w in want]
+            for t in recv:
+                t.fill_(oracle.CANARY)
+            comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="rbruck", r=2,
+                           type_size=ts, eager_max_bytes=hi * ts)
+            comm.check()
+            assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
+
+        # rendezvous Bruck stages user payload made of small integers that look like call numbers
+        words = np.arange(1, 40, dtype=np.int32)
+        counts = dist.constant(P, 4096)
+        prob = oracle.make_problem(counts, ts, 0)
+        send = [torch.from_numpy(np.resize(words, int(b) // 4).view(np.uint8).copy()).cuda() for b in prob.send_bytes]
+        recv = [comm.symm_empty(int(b), torch.uint8) for b in prob.recv_bytes]
+        for _ in range(2):
+            comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="rbruck", r=2,
+                           type_size=ts)
+        comm.check()
+        for i in range(6):
+            eager_call(3000, 10 + i)             # large blocks: flags of calls 3..8 far into the cells
+        # a rank that never joins: time-out, then reset() restarts the numbering
+        comm.set_timeout_ms(50)
+        comm.inject_absent_rank(1)
+        comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="spreadout", type_size=ts)
+        assert comm.status()["name"] == "timeout"
+        comm.inject_absent_rank(-1)
+        comm.set_timeout_ms(2000)
+        comm.reset()
+        for i in range(4):
+            eager_call(40, 30 + i)               # small blocks overwrite only the front of the cells ...
+        for i in range(8):
+            eager_call(3000, 40 + i)             # ... and large ones walk the numbering up to the old values
+        comm.close()
+
+
 @pytest.mark.parametrize("P", [1, 2, 3, 5, 6, 7, 12, 16])
 def test_rank_counts(P):
     counts = dist.uniform(P, 100, seed=P)
     for algo, kw in [("spreadout", {}), ("rbruck", dict(r=2)), ("tuna2", dict(r=3, b=2)), ("rbruck_om", dict(r=max(P, 2)))]:
         run_case(P, algo, 8, counts, packed=(P % 2 == 0), seed=P, **kw)
+        run_case(P, algo, 8, counts, packed=(P % 2 == 1), seed=P + 1, persistent=True, launches=2, **kw)
 
 
 @pytest.mark.parametrize("ts", [1, 2, 4, 8, 16])
@@ -265,8 +380,31 @@ def test_phase_timers_follow_the_reference_names():
              "excgMeta_time", "excgData_time", "replace_time", "orgData_time", "prepSP_time", "SP_time", "intra_time"]
     vals = {n: C.c_double.in_dll(lib, n).value for n in names}
     assert all(v >= 0 for v in vals.values())
-    assert vals["excgMeta_time"] > 0 and vals["excgData_time"] + vals["SP_time"] > 0
+    assert vals["excgMeta_time"] > 0 and vals["excgData_time"] > 0 and vals["SP_time"] > 0
+    assert vals["intra_time"] == vals["excgData_time"] and vals["alcCopy_time"] > 0
     assert vals["replace_time"] == 0 and vals["orgData_time"] == 0      # pack / unpack / organise no longer exist
+    # two-layer linear: intra_time and one iteration_time entry per inter-group batch
+    # (src/twolayer_communicator_linear.cpp:125-128,143,183)
+    lib.rbv_iteration_count.restype = C.c_int
+    for persistent in (False, True):
+        run_case(8, "twolayer_linear_s2", 8, counts, seed=10, n=4, b=2, b2=2, persistent=persistent)
+        assert lib.rbv_update_timers(comm._ctx) == 0
+        nb = lib.rbv_iteration_count(comm._ctx)
+        assert nb == 3                          # flat offsets 4..7 reach the other group: batches (f - 1) // 2 = 1, 2, 3
+        it = C.POINTER(C.c_double).in_dll(lib, "iteration_time")
+        assert C.c_double.in_dll(lib, "intra_time").value > 0 and C.c_double.in_dll(lib, "SP_time").value > 0
+        assert all(it[i] > 0 for i in range(nb))
+        C.CDLL(None).free(it)
+    tr = comm.trace()
+    assert {t["phase"] for t in tr} >= {1, 2} and all(t["end_us"] >= t["start_us"] for t in tr)
+    # leader-routed exchange: gather, exchange and hand-out are phases 1, 2, 3
+    run_case(8, "simple_merge", 8, counts, seed=11, n=4, persistent=True)
+    assert lib.rbv_update_timers(comm._ctx) == 0
+    assert C.c_double.in_dll(lib, "orgData_time").value > 0
+    # eager protocol: unpacking is timed as replace_time
+    run_case(8, "rbruck", 4, dist.uniform(8, 300, seed=1), seed=12, r=2, eager_max_bytes=1200)
+    assert lib.rbv_update_timers(comm._ctx) == 0
+    assert C.c_double.in_dll(lib, "replace_time").value > 0
     comm.enable_trace(False)
 
 

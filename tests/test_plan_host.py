@@ -119,5 +119,50 @@ def test_every_pair_delivered_once():
         p = Plan(algo, P, n=n, r=2, r2=2, b=2, b2=2).check()
         ops = p.ops()
         final = ops[ops["dst_cell"] < 0]
-        pairs = sorted((int(o["origin"]), int(o["dest"])) for o in final)
+        # an op that moves one slice of its block (bits 2-15 of flags) counts once per block
+        whole = [o for o in final if ((int(o["flags"]) >> 9) & 127) == 0 or ((int(o["flags"]) >> 2) & 127) == 0]
+        pairs = sorted((int(o["origin"]), int(o["dest"])) for o in whole)
         assert pairs == [(s, d) for s in range(P) for d in range(P)], algo
+
+
+@pytest.mark.parametrize("algo", ["merge", "simple_merge"])
+@pytest.mark.parametrize("P,n", [(1, 1), (2, 1), (2, 2), (4, 2), (8, 4), (8, 2), (8, 1), (8, 8), (6, 3), (12, 4),
+                                 (16, 4), (27, 9)])
+def test_leader_routed_exchanges(algo, P, n):
+    # merge_alltoallv / simply_merge_alltoallv of the reference's benchmarks, hand-out to the destinations included
+    plan = Plan(algo, P, n=n).check()
+    run(plan, P, ts=8, seed=P + n, packed=(n % 2 == 0), hi=40)
+    ops = plan.ops()
+    if n >= 2 and P > n:
+        leader = 1 if algo == "merge" else 0
+        # between groups only group leaders (and, for merge, the local rank 0 with the large messages) talk
+        for o in ops:
+            s, d = int(o["src"]), int(o["dst"])
+            if s // n != d // n:
+                allowed = {leader, 0} if algo == "merge" else {leader}
+                assert s % n in allowed and d % n in allowed, (s, d)
+    assert Plan(algo, 8, n=3).err == -1
+
+
+@pytest.mark.parametrize("P", [1, 2, 3, 8, 16])
+def test_split_sends_the_large_block_in_parts(P):
+    for b in (0, 2, 5, 200):
+        plan = Plan("split", P, b=b).check()
+        run(plan, P, ts=4, seed=P, hi=100)
+        ops = plan.ops()
+        parts = [o for o in ops if (int(o["flags"]) >> 9) & 127]
+        if P > 1 and plan.spec["b"] > 1:
+            assert len(parts) == plan.spec["b"]
+            assert all(int(o["origin"]) == 0 and int(o["dest"]) == P - 1 for o in parts)
+            assert sorted((int(o["flags"]) >> 2) & 127 for o in parts) == list(range(plan.spec["b"]))
+        else:
+            assert not parts
+
+
+def test_key_indices_follow_issue_order():
+    for algo in ALGOS:
+        ops = Plan(algo, 8, n=4, r=2, r2=2, b=2, b2=2).check().ops()
+        idx = (ops["flags"] >> 16).astype(np.int64)
+        keys = ops["key"].astype(np.int64)
+        assert idx[0] == 0 and np.all(np.diff(idx) >= 0) and np.all(np.diff(idx) <= 1)
+        assert np.array_equal(np.diff(idx) > 0, np.diff(keys) > 0), algo
