@@ -9,6 +9,7 @@ small ``inputs/`` are copied verbatim to ``baseline/_ref/reference``; (3) ``src/
 """
 from __future__ import annotations
 
+import os
 import shutil
 import subprocess
 import sys
@@ -35,7 +36,7 @@ def copy_sources(reference: Path) -> None:
     shutil.copy2(reference / "rbrucks.h", SRC_COPY / "rbrucks.h")
     for d in ("src", "examples", "benchmarks"):
         shutil.copytree(reference / d, SRC_COPY / d)
-    for p in ("4proc", "8proc", "16proc", "32proc", "64proc"):
+    for p in ("4proc", "8proc", "16proc", "32proc", "64proc", "128proc", "256proc", "512proc", "1024proc"):
         if (reference / "inputs" / p).exists():
             shutil.copytree(reference / "inputs" / p, SRC_COPY / "inputs" / p)
 
@@ -53,24 +54,38 @@ def build() -> Path:
     return out
 
 
+def find_reference() -> Path | None:
+    """The reference's source tree: ``$RBV_REFERENCE_DIR``, or a folder named ``reference`` beside this repository."""
+    cands = []
+    if os.environ.get("RBV_REFERENCE_DIR"):
+        cands.append(Path(os.environ["RBV_REFERENCE_DIR"]))
+    cands.append(HERE.parent.parent / "reference")
+    for cand in cands:
+        if (cand / "src" / "rbruckv.h").exists():
+            return cand
+    return None
+
+
 def ensure_built() -> Path | None:
-    """Path of the runner, building it from the copied sources when needed; None if there is no copy."""
+    """Path of the runner, building it from the copied sources when needed (and when the harness is newer than
+    the binary); None if there is neither a copy nor a reference tree to copy from."""
     out = REF / "ref_runner"
-    if out.exists():
+    fresh = out.exists() and out.stat().st_mtime >= (HERE / "ref_runner.cpp").stat().st_mtime
+    if fresh:
         return out
     if not (SRC_COPY / "src").exists():
-        # no copy yet: make one if the reference tree is mounted on this machine
-        for cand in (Path("/root/reference"),):
-            if (cand / "src" / "rbruckv.h").exists():
-                REF.mkdir(exist_ok=True)
-                copy_sources(cand)
-                return build()
-        return None
+        cand = find_reference()
+        if cand is None:
+            return out if out.exists() else None
+        REF.mkdir(exist_ok=True)
+        copy_sources(cand)
     return build()
 
 
 def main():
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    reference = Path(sys.argv[1]) if len(sys.argv) > 1 else find_reference()
+    if reference is None:
+        raise SystemExit("usage: install_reference.py <path of the reference tree>  (or set RBV_REFERENCE_DIR)")
     REF.mkdir(exist_ok=True)
     print(pip_attempt(reference))
     copy_sources(reference)

@@ -6,7 +6,10 @@
 //
 // usage: ref_runner <algo> <P> <type_size> <counts_file> <iters> <warmup> [n r r2 b b2]
 //   counts_file: P x P whitespace-separated integers, row s = elements rank s sends to each rank.
-// Output: one JSON line on stdout.
+// Output: one JSON line on stdout (mean, median and minimum of the per-iteration maxima over ranks).
+// With REF_SEND_DIR / REF_RECV_DIR in the environment rank r takes its (packed) send buffer from
+// <REF_SEND_DIR>/send_<r>.bin and writes its receive buffer to <REF_RECV_DIR>/recv_<r>.bin, so that a test can
+// compare the reference's receive bytes with another implementation's.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -79,6 +82,12 @@ void rank_main(int rank, int P, void* arg) {
     size_t n = (size_t)sc[d] * esz, o = (size_t)sd[d] * esz;
     for (size_t k = 0; k < n; k++) sb[o + k] = (char)pattern(rank, d, k);
   }
+  const char* send_dir = std::getenv("REF_SEND_DIR");
+  const char* recv_dir = std::getenv("REF_RECV_DIR");
+  if (send_dir) {
+    std::ifstream f(std::string(send_dir) + "/send_" + std::to_string(rank) + ".bin", std::ios::binary);
+    f.read(sb.data(), (std::streamsize)((size_t)stot * esz));
+  }
   const bool twolayer_s2 = (J.algo == "twolayer_linear_s2");
   for (int it = 0; it < J.warmup + J.iters; it++) {
     MPI_Barrier(MPI_COMM_WORLD);
@@ -96,9 +105,14 @@ void rank_main(int rank, int P, void* arg) {
     if (rank == 0 && it >= J.warmup) J.times.push_back(mx);
   }
   long long bad = 0;
-  for (int s = 0; s < P; s++) {
-    size_t n = (size_t)rc[s] * esz, o = (size_t)rd[s] * esz;
-    for (size_t k = 0; k < n; k++) bad += ((unsigned char)rb[o + k] != pattern(s, rank, k));
+  if (!send_dir)
+    for (int s = 0; s < P; s++) {
+      size_t n = (size_t)rc[s] * esz, o = (size_t)rd[s] * esz;
+      for (size_t k = 0; k < n; k++) bad += ((unsigned char)rb[o + k] != pattern(s, rank, k));
+    }
+  if (recv_dir) {
+    std::ofstream f(std::string(recv_dir) + "/recv_" + std::to_string(rank) + ".bin", std::ios::binary);
+    f.write(rb.data(), (std::streamsize)((size_t)rtot * esz));
   }
   J.errors[rank] = bad;
 }

@@ -5,15 +5,19 @@ Workload (fixed, whatever the GPU count): an 8-rank alltoallv of fp32 elements; 
 Zipf-skewed (s = 1.2, largest block 64 KB, about 10 % empty blocks) from a fixed seed.  The 8 logical ranks
 are spread over the N GPUs (8/N ranks per GPU), so N = 8 is one rank per B200 and N = 1 keeps the whole
 exchange inside one GPU: strong scaling of a fixed problem.  A step is one `twophase_rbruck_alltoallv`
-call whose radix is picked from {2, 3, 4, 8} by timing during warm-up (the tunable radix is the point of
-the algorithm; at 8 ranks radix 8 degenerates to one direct round).
+call whose radix is picked from {2, 3, 4, 8} and whose protocol from {rendezvous, eager} by timing during
+warm-up (the tunable radix is the point of the algorithm; at 8 ranks radix 8 degenerates to one direct round).
 
     python bench.py --gpus N --steps K --warmup W            # this library (device kernels)
     python bench.py --impl reference --gpus N --steps K ...  # the unmodified reference on CPU threads
 
 Prints one JSON line.  `value` = total bytes sent by all ranks / device time of the slowest rank, in GB/s,
-summed over the job; `e2e` is the same metric through the public Python API including the host->device
-copy of every rank's send buffer from pinned memory and the device->host copy of every receive buffer.
+summed over the job (`config.algbw_per_rank_GBps` is the per-rank figure nccl-tests would print); `e2e` is the
+same metric through the public Python API including the host->device copy of every rank's send buffer from
+pinned memory and the device->host copy of every receive buffer.  Outside the timed steps the line also carries:
+a cross-GPU self check of every algorithm, the in-kernel phase stamps of every rank, NCCL's grouped send/recv on
+the same kind of exchange, a block-size sweep over the algorithm families (16 B - 4 MB), the MoE layer and the
+FFT pencil transposes of the other benchmark configurations (`--quick` leaves those blocks out).
 """
 from __future__ import annotations
 
@@ -23,6 +27,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import time
 from pathlib import Path
 
 import numpy as np
@@ -38,9 +43,9 @@ RADICES = (2, 3, 4, 8)
 METRIC = "alltoallv_algbw_GBps"
 
 
-def workload():
+def workload(P=NRANKS):
     from rbruck_alltoallv_b200.utils import distributions as dist
-    return dist.zipf(NRANKS, MAX_BLOCK_ELEMS, s=1.2, zero_frac=0.10, seed=SEED)
+    return dist.zipf(P, MAX_BLOCK_ELEMS, s=1.2, zero_frac=0.10, seed=SEED)
 
 
 def config_dict(n_gpus, extra=None):
@@ -82,6 +87,9 @@ def run_reference(args):
             per_radix[r] = json.loads(out.stdout.strip().splitlines()[-1])
     finally:
         os.unlink(path)
+    # radix picked like in the other arm: the fastest over the K timed steps; `value` uses the MEAN of the K
+    # per-step maxima over ranks (sum / K), the same statistic as the other arm.  Median and minimum are listed
+    # beside it: the ranks are CPU threads on a shared host and single steps scatter widely.
     best = min(per_radix, key=lambda r: per_radix[r]["sum_s"])
     res = per_radix[best]
     ms = res["sum_s"] / max(args.steps, 1) * 1e3
@@ -90,7 +98,10 @@ def run_reference(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
             "config": config_dict(args.gpus, {"radix": best, "transport": "threads-as-ranks MPI stand-in, host memory",
+                                              "statistic": "mean of the K per-step maxima over ranks",
                                               "us_per_radix": {str(r): per_radix[r]["mean_us"] for r in RADICES},
+                                              "us_median_per_radix": {str(r): per_radix[r].get("median_us") for r in RADICES},
+                                              "us_min_per_radix": {str(r): per_radix[r].get("min_us") for r in RADICES},
                                               "mismatched_bytes": res["mismatched_bytes"]}),
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "CPU code on host buffers: there is no device copy to include"},
@@ -100,14 +111,257 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------------------------------
+class Deadline:
+    """Optional blocks are skipped once the run has used its time allowance."""
+
+    def __init__(self, seconds):
+        self.t0, self.limit = time.time(), seconds
+
+    def left(self):
+        return self.limit - (time.time() - self.t0)
+
+
+def gather_objects(comm, obj):
+    if comm._side is None:
+        return [obj]
+    out = [None] * comm.nproc
+    comm._dist.all_gather_object(out, obj, group=comm._side)
+    return out
+
+
+def phase_stamps(comm, make_call, flush, align, reps=5):
+    """In-kernel time stamps of one call on EVERY process (microseconds after the start of the kernel on that
+    process; median over a few traced launches).  Rendezvous kernels: metadata (or peers entered) / loop of CTA 0
+    done / deliveries reported / everything received.  Eager kernel: first warp / first CTA / last CTA done."""
+    import torch
+    comm.enable_trace(True)
+    call = make_call()
+    rows = []
+    for _ in range(reps):
+        flush()
+        align()
+        call.launch()
+        s = comm.status()
+        tr = s["trace_ns"]
+        rows.append([(v - tr[0]) / 1e3 if v and tr[0] and abs(v - tr[0]) < 1e9 else None for v in tr])
+    comm.enable_trace(False)
+    del call
+    torch.cuda.synchronize()
+
+    def med(i):
+        vals = [r[i] for r in rows if r[i] is not None]
+        return round(float(np.median(vals)), 2) if vals else None
+
+    if make_call.kind == "eager":
+        mine = {"first_warp_done": med(2), "first_cta_done": med(3), "last_cta_done": med(4)}
+    else:
+        mine = {"loop_done_cta0": med(5), "deliveries_reported": med(6), "all_received": med(4)}
+    return {f"gpu{q}": v for q, v in enumerate(gather_objects(comm, mine))}
+
+
+def nccl_time(sc_row, rc_row, ts, dev, flush, align, steps=30):
+    """NCCL grouped send/recv (torch.distributed.all_to_all_single) for one rank per process, microseconds
+    (median over steps of the per-step maximum over ranks)."""
+    import torch
+    import torch.distributed as dist
+    from rbruck_alltoallv_b200.utils.timing import time_steps
+    dt = {1: torch.uint8, 2: torch.bfloat16, 4: torch.float32, 8: torch.float64}[ts]
+    ns, nr = int(sc_row.sum()), int(rc_row.sum())
+    s1 = torch.zeros(max(ns, 1), dtype=dt, device=dev)
+    r1 = torch.empty(max(nr, 1), dtype=dt, device=dev)
+    ins, outs = [int(x) for x in sc_row], [int(x) for x in rc_row]
+    fn = lambda: dist.all_to_all_single(r1[:nr], s1[:ns], output_split_sizes=outs, input_split_sizes=ins)
+    t = time_steps(fn, steps=steps, warmup=5, flush=flush, align=align)
+    return float(np.median(t)) * 1e3
+
+
+def measure(comm, counts, ts, variants, flush, align, steps=20):
+    """Times persistent calls of several configurations on one count matrix: {name: row}."""
+    import torch
+    from rbruck_alltoallv_b200.parallel.plan import Plan
+    from rbruck_alltoallv_b200.utils.metrics import alltoallv_row
+    from rbruck_alltoallv_b200.utils.timing import time_steps
+    L, mine = comm.L, comm.local_ranks
+    dev = f"cuda:{comm.device}"
+    sc = counts[mine].astype(np.int32)
+    rc = counts.T[mine].astype(np.int32)
+    send = [torch.zeros(max(int(sc[i].sum()), 1) * ts, dtype=torch.uint8, device=dev) for i in range(L)]
+    recv = [comm.symm_empty(max(int(rc[i].sum()), 1) * ts, torch.uint8) for i in range(L)]
+    emax = comm.max_block_bytes(sc, ts)
+    out = {}
+    for name, kw in variants:
+        kw = dict(kw)
+        if kw.pop("eager", False):
+            if emax > (256 << 10) or (comm.P + 64) * (2 * emax + 16) > comm.arena_bytes:
+                continue
+            kw["eager_max_bytes"] = emax
+        try:
+            call = comm.prepare(send, recv, sc, None, rc, None, type_size=ts, **kw)
+        except Exception as e:  # noqa: BLE001 - a configuration that does not fit this communicator
+            out[name] = {"us": None, "error": str(e)[:80]}
+            continue
+        t = time_steps(call.launch, steps, 3, flush=flush, align=align)
+        st = comm.status()
+        if st["code"]:
+            comm.reset()
+            out[name] = {"us": None, "error": st["name"]}
+            continue
+        pk = {k: v for k, v in kw.items() if k in ("n", "r", "r2", "b", "b2")}
+        ops = Plan(kw.get("algo", "spreadout"), comm.P, **pk).ops()
+        out[name] = alltoallv_row(counts, ts, float(np.median(t)) * 1e3, ops, L)
+        out[name]["kernel"] = call.kind
+        del call
+    if comm.nproc > 1 and L == 1:
+        from rbruck_alltoallv_b200.utils.metrics import alltoallv_row as row
+        out["nccl_grouped_sendrecv"] = row(counts, ts, nccl_time(sc[0], rc[0], ts, dev, flush, align, steps))
+    del send, recv
+    return out
+
+
+SWEEP_VARIANTS = [("spreadout_eager", dict(algo="spreadout", eager=True)), ("spreadout", dict(algo="spreadout")),
+                  ("rbruck_r2_eager", dict(algo="rbruck", r=2, eager=True)), ("rbruck_r2", dict(algo="rbruck", r=2)),
+                  ("tuna2_r2", dict(algo="tuna2", r=2)), ("ttpl_bt_s1_2x4", dict(algo="ttpl_bt_s1", n=4, r=2)),
+                  ("ttpl_bt_s1_4x2", dict(algo="ttpl_bt_s1", n=2, r=2))]
+
+
+def run_sweep(comm, flush, align, deadline):
+    """Latency / bandwidth over block sizes (normal(mean 2^k, 0.25 mean) bf16 blocks) for the algorithm families."""
+    from rbruck_alltoallv_b200.utils import distributions as D
+    rows = []
+    for k in (4, 10, 16, 20, 22):           # mean block 16 B, 1 KB, 64 KB, 1 MB, 4 MB
+        if deadline.left() < 60:
+            break
+        counts = D.normal(comm.P, max(1, (1 << k) // 2), 0.25, seed=k)
+        rows.append({"mean_block_bytes": 1 << k, "ranks": comm.P, "total_bytes": int(counts.sum()) * 2,
+                     "algos": measure(comm, counts, 2, SWEEP_VARIANTS, flush, align)})
+    return rows
+
+
+def run_vs_nccl(world, flush_dev, deadline):
+    """One rank per GPU (P = N): the Zipf exchange of the headline and the block-size sweep, this library's
+    spread-out order (both protocols) next to NCCL's grouped send/recv on the same counts."""
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    from rbruck_alltoallv_b200.utils import distributions as D
+    from rbruck_alltoallv_b200.utils.timing import L2Flusher, RankAligner
+    comm = Communicator(nranks=world, heap_bytes=1 << 30, arena_bytes=64 << 20)
+    flush, align = flush_dev, RankAligner(comm)
+    variants = [("spreadout_eager", dict(algo="spreadout", eager=True)), ("spreadout", dict(algo="spreadout")),
+                ("rbruck_r2_eager", dict(algo="rbruck", r=2, eager=True)), ("rbruck_r2", dict(algo="rbruck", r=2))]
+    out = {"ranks": world, "rows": []}
+    z = measure(comm, workload(world), TYPE_SIZE, variants, flush, align, steps=30)
+    out["zipf64KB_fp32"] = z
+    for k in (4, 10, 16, 20, 22):
+        if deadline.left() < 60:
+            break
+        counts = D.normal(world, max(1, (1 << k) // 2), 0.25, seed=k)
+        out["rows"].append({"mean_block_bytes": 1 << k, "algos": measure(comm, counts, 2, variants, flush, align)})
+
+    def best_of(rows):
+        ours = [v["us"] for n, v in rows.items() if n != "nccl_grouped_sendrecv" and v.get("us")]
+        nc = rows.get("nccl_grouped_sendrecv", {}).get("us")
+        return (min(ours) if ours else None), nc
+
+    o, n = best_of(z)
+    out["zipf_ours_us"], out["zipf_nccl_us"] = o, n
+    out["zipf_vs_nccl"] = round(n / o, 3) if o and n else None
+    del align
+    comm.close()
+    return out
+
+
+def run_moe(world, deadline):
+    """MoE layer of the benchmark configuration: 8 experts per GPU, 8192 tokens per GPU, hidden 4096, FFN 14336,
+    top-2, bf16 (weak scaling: the same per-GPU sizes at every N)."""
+    import torch
+    import torch.distributed as dist
+    from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    from rbruck_alltoallv_b200.utils.moe_bench import _peaks, _time
+    T, H, I, El = 8192, 4096, 14336, 8
+    cap_rows = int(np.ceil(2.0 * 2 * T / 128.0)) * 128
+    comm = Communicator(nranks=world, heap_bytes=2 * cap_rows * H * 2 + (64 << 20), arena_bytes=1 << 20)
+    layer = MoEExpertParallel(comm, El * world, H, I, T, seed=3)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + comm.proc)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(T, El * world, device="cuda", generator=g)
+    out = torch.empty_like(x)
+    layer.forward(x, logits, out)
+    layer.check()
+    t = _time(lambda: layer.forward(x, logits, out), 10, 3)
+    layer.check()
+    rows = torch.tensor([float(layer.totals[0].item())], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(rows, op=dist.ReduceOp.MAX)
+    rows_max = int(rows.item())
+    pk = _peaks()
+    flops = rows_max * 2.0 * H * 2 * I + rows_max * 2.0 * I * H
+    ms = float(np.median(t))
+    link_ms = 2 * rows_max * H * 2.0 * (world - 1) / max(world, 1) / 900e9 * 1e3
+    res = {"ms_layer": round(ms, 3), "rows_busiest_gpu": rows_max, "tflops": round(flops / ms / 1e9, 1),
+           "roofline_ms_burst_peak": round(max(flops / (pk["bf16_tflops"] * 1e9), link_ms), 3),
+           "fraction_of_roofline_burst_peak": round(max(flops / (pk["bf16_tflops"] * 1e9), link_ms) / ms, 3),
+           "fraction_of_roofline_sustained_peak": round(max(flops / (pk["bf16_tflops_sustained"] * 1e9), link_ms) / ms, 3),
+           "peaks": pk, "config": "8 experts/GPU, 8192 tokens/GPU, hidden 4096, FFN 14336, top-2, bf16"}
+    del layer, x, logits, out
+    comm.close()
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_fft(world, deadline):
+    """Pencil transposes of a 1024^3 complex64 grid over the N GPUs (+-5 % jittered splits), fused kernel next to
+    NCCL all-to-all with separate pack / unpack kernels."""
+    import torch
+    import torch.distributed as dist
+    from rbruck_alltoallv_b200.ops.fft import PencilTranspose
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    from rbruck_alltoallv_b200.utils.timing import L2Flusher, time_steps
+    n = 1024
+    pr = {1: 1, 2: 1, 4: 2, 8: 2}.get(world, 1)
+    pc = world // pr
+    per_rank = (n ** 3 * 8) // world
+    comm = Communicator(nranks=world, heap_bytes=int(2.3 * per_rank) + (64 << 20), arena_bytes=1 << 20)
+    tp = PencilTranspose(comm, n, pr, pc, seed=11)
+    dev = f"cuda:{comm.device}"
+    src_x = torch.view_as_complex(torch.randn(*tp.shape_x, 2, device=dev))
+    src_y = torch.view_as_complex(torch.randn(*tp.shape_y, 2, device=dev))
+    flush = L2Flusher(dev)
+    t_xy = time_steps(lambda: tp.x_to_y(src_x), 10, 3, flush=flush)
+    t_yz = time_steps(lambda: tp.y_to_z(src_y), 10, 3, flush=flush)
+    tp.check()
+    res = {"grid": n, "process_grid": [pr, pc], "dtype": "complex64"}
+    for name, t, (total, remote) in (("x_to_y", t_xy, tp.bytes_sent_xy()), ("y_to_z", t_yz, tp.bytes_sent_yz())):
+        ms = float(np.median(t))
+        res[name] = {"ms": round(ms, 3), "ms_min": round(float(np.min(t)), 3), "ms_max": round(float(np.max(t)), 3),
+                     "bytes_per_gpu": int(total), "bytes_leaving_gpu": int(remote),
+                     "frac_of_900GBps": round(remote / 900e9 / (ms * 1e-3), 3) if remote else None,
+                     "local_GBps": round(2 * total / ms / 1e6, 1)}
+    if world > 1:
+        cols = [dist.new_group([r * pc + c for r in range(pr)]) for c in range(pc)]
+        rows = [dist.new_group([r * pc + c for c in range(pc)]) for r in range(pr)]
+        if pr > 1:
+            t_n = time_steps(lambda: tp.nccl_x_to_y(src_x, cols[tp.me_c]), 5, 2, flush=flush)
+            res["x_to_y"]["ms_nccl_pack_unpack"] = round(float(np.median(t_n)), 3)
+        if pc > 1:
+            t_n = time_steps(lambda: tp.nccl_y_to_z(src_y, rows[tp.me_r]), 5, 2, flush=flush)
+            res["y_to_z"]["ms_nccl_pack_unpack"] = round(float(np.median(t_n)), 3)
+    del tp, src_x, src_y
+    comm.close()
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     from rbruck_alltoallv_b200.parallel.comm import Communicator
-    from rbruck_alltoallv_b200.utils import oracle
+    from rbruck_alltoallv_b200.utils import oracle, selftest
+    from rbruck_alltoallv_b200.utils.metrics import alltoallv_row
     from rbruck_alltoallv_b200.utils.timing import ClockSampler, L2Flusher, RankAligner, time_steps
 
+    deadline = Deadline(args.budget_s)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -116,11 +370,20 @@ def run_ours(args):
     n_gpus = world
     if NRANKS % n_gpus:
         raise SystemExit(f"--gpus must divide {NRANKS}")
-    comm = Communicator(nranks=NRANKS, heap_bytes=512 << 20, arena_bytes=8 << 20)
+    comm = Communicator(nranks=NRANKS, heap_bytes=1 << 30, arena_bytes=64 << 20)
     rank0 = comm.proc == 0
     dev = f"cuda:{comm.device}"
     L, P = comm.L, comm.P
     mine = comm.local_ranks
+
+    # every algorithm, every way a call can run, across the GPUs of this job, before anything is timed
+    fails = selftest.check_all(comm)
+    sc_t = torch.tensor([fails], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(sc_t)
+    selfcheck = {"cases": int(getattr(selftest.check_all, "cases", 0)), "failures": int(sc_t.item())}
+    if selfcheck["failures"]:
+        raise SystemExit(f"self check failed: {selfcheck}")
 
     counts = workload()
     prob = oracle.make_problem(counts, TYPE_SIZE, SEED, packed=True)
@@ -148,9 +411,9 @@ def run_ours(args):
     sd = prob.sdispls[mine]
     rd = prob.rdispls[mine]
 
-    # persistent calls (resolved once, one kernel launch per step), one per candidate radix
-    # Two protocols per radix: rendezvous (blocks go straight to the final address) and eager (blocks travel as
-    # self-validating units through library cells; lower latency for small blocks).
+    # Persistent calls (resolved once, one kernel launch per step), one per candidate radix and protocol:
+    # rendezvous (blocks go straight to their final address; with host-side counts the static kernel runs it) and
+    # eager (blocks travel as self-validating units through library cells; one NVLink trip per hop).
     emax = comm.max_block_bytes(prob.counts, TYPE_SIZE)
     calls = {}
     for r in RADICES:
@@ -164,22 +427,26 @@ def run_ours(args):
     flush = L2Flusher(dev)
     align = RankAligner(comm)
 
-    # correctness once, before timing
-    for key in ((2, "rendezvous"), (2, "eager"), (8, "eager")):
-        dev_recv.fill_(0xA5)
-        step(key)
-        comm.check()
+    def verify(what):
         got = dev_recv.cpu().numpy()
         for i, r in enumerate(mine):
             if not np.array_equal(got[r_off[i]:r_off[i] + r_sizes[i]], want[r]):
-                raise SystemExit(f"rank {r}: receive buffer differs from the direct-copy expectation ({key})")
+                raise SystemExit(f"rank {r}: receive buffer differs from the direct-copy expectation ({what})")
 
-    # radix choice by measurement (part of warm-up)
+    # correctness of every candidate once, before timing
+    for key in calls:
+        dev_recv.fill_(0xA5)
+        step(key)
+        comm.check()
+        verify(key)
+
+    # radix / protocol choice by measurement (part of warm-up); the simplest within 3 % of the best wins
     per_radix = {}
     for key in calls:
-        t = time_steps(lambda: step(key), steps=20, warmup=3, flush=flush, align=align)
-        per_radix[key] = float(np.mean(t)) * 1e3
+        t = time_steps(lambda: step(key), steps=30, warmup=3, flush=flush, align=align)
+        per_radix[key] = float(np.median(t)) * 1e3
     keys = list(calls)
+    fastest = min(per_radix.values())
     best_i = min(range(len(keys)), key=lambda i: per_radix[keys[i]])
     if world > 1:
         b = torch.tensor([best_i], device=dev)
@@ -251,79 +518,64 @@ def run_ours(args):
     if world > 1:
         hb = torch.tensor([h2d, d2h], device=dev, dtype=torch.int64)
         dist.all_reduce(hb)
-        h2d, d2h = int(hb[0]) , int(hb[1])
+        h2d, d2h = int(hb[0]), int(hb[1])
 
-    sweep = None
-    if args.sweep:
-        sweep = run_sweep(comm, flush, align, world)
+    # ---- everything below is outside the timed steps ----
+    def make_best():
+        kw = dict(eager_max_bytes=emax) if best[1] == "eager" else {}
+        return comm.prepare(send, recv, sc, sd, rc, rd, algo="rbruck", r=best[0], type_size=TYPE_SIZE, **kw)
+    make_best.kind = best[1]
+    phases = phase_stamps(comm, make_best, flush, align)
+    from rbruck_alltoallv_b200.parallel.plan import Plan
+    head_row = alltoallv_row(counts, TYPE_SIZE, ms * 1e3, Plan("rbruck", P, r=best[0]).ops(), L)
+
+    extra = {}
+    if not args.quick:
+        blocks = [("sweep", lambda: run_sweep(comm, flush, align, deadline))]
+        if world > 1:
+            blocks.append(("one_rank_per_gpu_vs_nccl", lambda: run_vs_nccl(world, flush, deadline)))
+        blocks += [("moe_layer", lambda: run_moe(world, deadline)), ("fft_transpose_1024", lambda: run_fft(world, deadline))]
+        for name, fn in blocks:
+            if deadline.left() < 90:
+                extra[name] = {"skipped": "time allowance of the run used up"}
+                continue
+            try:
+                extra[name] = fn()
+            except Exception as e:  # noqa: BLE001 - an optional block must not take the headline line with it
+                extra[name] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
 
     if rank0:
+        cfg = config_dict(n_gpus, {
+            "radix": best[0], "protocol": best[1], "kernel": calls[best].kind,
+            "us_per_radix": {f"{k[0]}/{k[1]}": round(v, 2) for k, v in per_radix.items()},
+            "total_bytes": total_bytes, "us_median": float(np.median(t)) * 1e3, "us_min": float(np.min(t)) * 1e3,
+            "algbw_per_rank_GBps": head_row.get("algbw_GBps"), "busbw_per_rank_GBps": head_row.get("busbw_GBps"),
+            "link_bytes_busiest_gpu": head_row.get("link_bytes_busiest_gpu"),
+            "frac_of_900GBps": head_row.get("frac_of_900GBps"),
+            "statistic": "mean of the K per-step maxima over ranks (sum / K); median and minimum beside it",
+            "selfcheck": selfcheck, "phase_us": phases,
+            "l2": "flushed: a 256 MiB buffer is written before every timed step (outside the timed span); "
+                  "a zero-byte alltoallv then lines the ranks up",
+            "timing": "CUDA events around each step, per-step max over ranks, summed over the K steps"})
+        vs = extra.get("one_rank_per_gpu_vs_nccl") or {}
+        if isinstance(vs, dict) and vs.get("zipf_nccl_us"):
+            cfg["nccl_us"], cfg["vs_nccl"] = vs["zipf_nccl_us"], vs["zipf_vs_nccl"]
+            cfg["nccl_note"] = (f"NCCL grouped send/recv and this library, one rank per GPU ({vs['ranks']} ranks), the "
+                                "same Zipf distribution; vs_nccl = NCCL time / this library's time")
         line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": n_gpus, "steps": args.steps, "warmup": warm,
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
-                "data": "synthetic",
-                "config": config_dict(n_gpus, {
-                    "radix": best[0], "protocol": best[1],
-                    "us_per_radix": {f"{k[0]}/{k[1]}": round(v, 2) for k, v in per_radix.items()},
-                    "total_bytes": total_bytes, "us_median": float(np.median(t)) * 1e3,
-                    "l2": "flushed: a 256 MiB buffer is written before every timed step (outside the timed span); "
-                          "a zero-byte alltoallv then lines the ranks up",
-                    "timing": "CUDA events around each step, per-step max over ranks, summed over the K steps"}),
-                "clocks": clocks.summary(),
+                "data": "synthetic", "config": cfg, "clocks": clocks.summary(),
                 "e2e": {"value": value_e, "unit": "GB/s", "ms_per_step": ms_e, "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "path": e2e_name,
                         "us_per_path": {k: round(v, 2) for k, v in e2e_us.items()}},
                 "gpu_launches": args.steps}
-        if sweep is not None:
-            line["sweep"] = sweep
+        line.update(extra)
         print(json.dumps(line), flush=True)
+    del calls, zc_call, ci_call, align
     comm.close()
     if world > 1:
         dist.destroy_process_group()
     return 0
-
-
-def run_sweep(comm, flush, align, world):
-    """Latency / bandwidth over block sizes for a few algorithm families (not part of the timed K steps)."""
-    import torch
-    import torch.distributed as dist
-    from rbruck_alltoallv_b200.utils import distributions as D
-    from rbruck_alltoallv_b200.utils.timing import time_steps
-
-    out = []
-    dev = f"cuda:{comm.device}"
-    L, P = comm.L, comm.P
-    mine = comm.local_ranks
-    for k in (4, 10, 14, 18, 22):           # mean block 16 B ... 4 MB of bf16
-        mean_elems = max(1, (1 << k) // 2)
-        counts = D.normal(P, mean_elems, 0.25, seed=k)
-        sc = counts[mine].astype(np.int32)
-        rc = counts.T[mine].astype(np.int32)
-        send = [torch.empty(max(int(sc[i].sum()), 1) * 2, dtype=torch.uint8, device=dev) for i in range(L)]
-        recv = [comm.symm_empty(max(int(rc[i].sum()), 1) * 2, torch.uint8) for i in range(L)]
-        tot = int(counts.sum()) * 2
-        row = {"mean_block_bytes": 1 << k, "total_bytes": tot, "us": {}}
-        for name, kw in (("spreadout", {}), ("rbruck_r2", dict(algo="rbruck", r=2)), ("tuna2_r2", dict(algo="tuna2", r=2)),
-                         ("ttpl_bt_s1_n4", dict(algo="ttpl_bt_s1", n=4, r=2))):
-            kw = dict(kw)
-            algo = kw.pop("algo", name)
-            fn = lambda: comm.alltoallv(send, recv, sc, None, rc, None, algo=algo, type_size=2, **kw)
-            t = time_steps(fn, steps=10, warmup=3, flush=flush, align=align)
-            if comm.status()["code"]:
-                comm.reset()
-                row["us"][name] = None
-                continue
-            row["us"][name] = round(float(np.median(t)) * 1e3, 2)
-        if world > 1 and L == 1:
-            s1 = send[0].view(torch.bfloat16)
-            r1 = torch.empty(max(int(rc[0].sum()), 1), dtype=torch.bfloat16, device=dev)
-            fn = lambda: dist.all_to_all_single(r1[: int(rc[0].sum())], s1[: int(sc[0].sum())],
-                                                output_split_sizes=[int(x) for x in rc[0]],
-                                                input_split_sizes=[int(x) for x in sc[0]])
-            t = time_steps(fn, steps=10, warmup=3, flush=flush, align=align)
-            row["us"]["nccl_grouped_sendrecv"] = round(float(np.median(t)) * 1e3, 2)
-        out.append(row)
-        del send, recv
-    return out
 
 
 def main():
@@ -332,7 +584,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--sweep", action="store_true", help="also report a block-size sweep (outside the timed steps)")
+    ap.add_argument("--quick", action="store_true", help="headline line only: no sweep, NCCL, MoE or FFT blocks")
+    ap.add_argument("--budget-s", type=float, default=600.0,
+                    help="optional blocks are skipped once the run has used this many seconds")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -21,7 +21,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = CSRC / "include"
 
-HOST_SOURCES = ["plan/plan.cpp", "plan/capi_host.cpp"]
+HOST_SOURCES = ["plan/plan.cpp", "plan/capi_host.cpp", "api/tuner_native.cpp"]
 CUDA_SOURCES = [
     "plan/plan.cpp",
     "plan/capi_host.cpp",
@@ -35,6 +35,7 @@ CUDA_SOURCES = [
     "kernels/fft_transpose.cu",
     "kernels/noalloc.cu",
     "api/c_api.cu",
+    "api/tuner_native.cpp",
     "api/drivers.cu",
 ]
 

@@ -60,6 +60,8 @@ def declare_cuda(lib):
     lib.rbv_ctx_last_trace.argtypes = [C.c_void_p, C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong),
                                        C.POINTER(C.c_ulonglong), C.c_int]
     lib.rbv_iteration_count.argtypes = [C.c_void_p]
+    lib.rbv_ctx_set_auto_hint.argtypes = [C.c_void_p, C.c_double, C.c_double]
+    lib.rbv_ctx_last_choice.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_prepared_free.argtypes = [C.c_void_p, C.c_void_p]
     lib.rbv_ctx_set_trace.argtypes = [C.c_void_p, C.c_int]
@@ -67,6 +69,11 @@ def declare_cuda(lib):
     lib.rbv_ctx_set_nvls_meta.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
     lib.rbv_ctx_meta_bytes.restype = C.c_size_t
     lib.rbv_ctx_meta_bytes.argtypes = [C.c_void_p]
+    lib.rbv_ctx_nvls_create.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_int), C.POINTER(C.c_size_t)]
+    lib.rbv_ctx_nvls_import.argtypes = [C.c_void_p, C.c_int, C.c_size_t]
+    lib.rbv_ctx_nvls_add_device.argtypes = [C.c_void_p]
+    lib.rbv_ctx_nvls_bind.argtypes = [C.c_void_p]
+    lib.rbv_ctx_nvls_teardown.argtypes = [C.c_void_p]
     lib.rbv_ctx_set_eager.argtypes = [C.c_void_p, C.c_ulonglong]
     lib.rbv_ctx_set_cooperative.argtypes = [C.c_void_p, C.c_int]
     declare_moe(lib)

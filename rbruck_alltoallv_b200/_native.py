@@ -15,6 +15,12 @@ c_int_p = C.POINTER(C.c_int)
 c_ll_p = C.POINTER(C.c_longlong)
 
 
+class Choice(C.Structure):
+    """``rbv_choice`` of the C API: a configuration as the tuner table stores it."""
+    _fields_ = [("algo", C.c_int), ("n", C.c_int), ("r", C.c_int), ("r2", C.c_int), ("b", C.c_int), ("b2", C.c_int),
+                ("eager", C.c_int)]
+
+
 def _declare_host(lib):
     lib.rbv_plan_create.restype = C.c_void_p
     lib.rbv_plan_create.argtypes = [C.c_int] * 7
@@ -39,6 +45,12 @@ def _declare_host(lib):
     lib.rbv_ipow.argtypes = [C.c_int, C.c_uint]
     lib.rbv_ndigits.argtypes = [C.c_int, C.c_int]
     lib.rbv_to_base.argtypes = [C.c_int, C.c_int, C.c_int, c_int_p]
+    lib.rbv_tuner_set_table.argtypes = [C.c_char_p]
+    lib.rbv_tuner_entries.argtypes = []
+    lib.rbv_tuner_choose.argtypes = [C.c_int, C.c_int, C.c_double, C.c_double, C.POINTER(Choice)]
+    # the C API's automatic entry points read the same table file as parallel/tuner.py
+    from .parallel import tuner as _tuner
+    lib.rbv_tuner_set_table(str(_tuner._cache_path()).encode())
 
 
 def host_lib():

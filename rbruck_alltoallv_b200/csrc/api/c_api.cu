@@ -1,5 +1,6 @@
 // C API: context management and the reference-shaped collective entry points (rbv/rbruckv.h).
 #include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -178,11 +179,38 @@ int rbv_ctx_set_nvls_meta(rbv_ctx_t ctx, void* self_ptr, void* mc_ptr, size_t by
   return rc;
 }
 size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx) { return ctx->c->nvls_bytes_needed(); }
+// The library's own NVLS set-up (see Context::nvls_*): each step returns 0 or an error code.
+int rbv_ctx_nvls_create(rbv_ctx_t ctx, size_t bytes, int* fd_out, size_t* size_out) {
+  int rc = ctx->c->nvls_create(bytes, fd_out);
+  if (rc) g_err = ctx->c->last_error();
+  else if (size_out) *size_out = ctx->c->nvls_object_bytes();
+  return rc;
+}
+int rbv_ctx_nvls_import(rbv_ctx_t ctx, int fd, size_t bytes) {
+  int rc = ctx->c->nvls_import(fd, bytes);
+  if (rc) g_err = ctx->c->last_error();
+  return rc;
+}
+int rbv_ctx_nvls_add_device(rbv_ctx_t ctx) {
+  int rc = ctx->c->nvls_add_device();
+  if (rc) g_err = ctx->c->last_error();
+  return rc;
+}
+int rbv_ctx_nvls_bind(rbv_ctx_t ctx) {
+  void *self = nullptr, *mc = nullptr;
+  size_t bytes = 0;
+  int rc = ctx->c->nvls_bind_and_map(&self, &mc, &bytes);
+  if (!rc) rc = ctx->c->set_nvls_meta(self, mc, bytes);
+  if (rc) g_err = ctx->c->last_error();
+  return rc;
+}
+void rbv_ctx_nvls_teardown(rbv_ctx_t ctx) { ctx->c->nvls_teardown(); }
 void rbv_ctx_set_eager(rbv_ctx_t ctx, unsigned long long max_block_bytes) { ctx->eager = max_block_bytes; }
 void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
 void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode) { ctx->c->set_bulk(mode); }
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int mode) { ctx->c->set_cooperative(mode < 0 ? -1 : (mode ? 1 : 0)); }
 void rbv_ctx_set_static(rbv_ctx_t ctx, int on) { ctx->allow_static = on != 0; }
+void rbv_ctx_set_auto_hint(rbv_ctx_t ctx, double mean_block_bytes, double cv) { ctx->hint_mean = mean_block_bytes; ctx->hint_cv = cv; }
 
 // Per-key time stamps of the most recent traced call: fills keys[i] (plan key: phase << 24 | step), start_ns[i],
 // end_ns[i] for up to `max` keys and returns the number of keys of the plan (the eager protocol adds one more entry
@@ -288,6 +316,13 @@ std::vector<int> convert10tob(int w, int N, int b) { return to_base(w, N, b); }
 // ---- per-rank entry points -------------------------------------------------------------------
 namespace {
 
+AlgoSpec mk(int algo, int n = 0, int r = 2, int r2 = 0, int b = 0, int b2 = 0) {
+  AlgoSpec s;
+  s.algo = algo; s.n = n; s.r = r; s.r2 = r2; s.b = b; s.b2 = b2;
+  return s;
+}
+AlgoSpec mk_spreadout() { return mk(ALG_SPREADOUT); }
+
 int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbuf, const int* sendcounts,
             const int* sdispls, char* recvbuf, const int* recvcounts, const int* rdispls, unsigned flags) {
   if (!comm) { g_err = "null communicator"; return RBV_ERR_BAD_ARG; }
@@ -296,6 +331,9 @@ int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbu
   const int P = c.P(), L = c.L(), lr = comm->local;
   AlgoSpec spec = spec_in;
   spec.P = P;
+  const bool automatic = spec.algo < 0;
+  if (automatic) spec = mk_spreadout();   // placeholder until all local ranks have arrived
+  spec.P = P;
   // argument validation happens in the plan compiler; evaluate it now so that every rank gets the code
   try {
     const DevPlan* dp = c.plan_for(spec);
@@ -303,8 +341,9 @@ int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbu
     if (dp->plan.err) { g_err = dp->plan.errmsg; return dp->plan.err; }
   } catch (const std::exception& e) { g_err = e.what(); return RBV_ERR_BAD_ARG; }
   if (ctx->pend == 0) {
-    ctx->spec = spec; ctx->ts = ts; ctx->flags = flags;
-  } else if (std::memcmp(&ctx->spec, &spec, sizeof spec) != 0 || ctx->ts != ts || ctx->flags != flags) {
+    ctx->spec = spec; ctx->ts = ts; ctx->flags = flags; ctx->automatic = automatic;
+  } else if (std::memcmp(&ctx->spec, &spec, sizeof spec) != 0 || ctx->ts != ts || ctx->flags != flags ||
+             ctx->automatic != automatic) {
     g_err = "local ranks called different collectives";
     return RBV_ERR_BAD_ARG;
   }
@@ -323,6 +362,35 @@ int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbu
   std::fill(ctx->seen.begin(), ctx->seen.end(), 0);
   bool have_rc = true;
   for (int v : ctx->rc) if (v < 0) have_rc = false;
+  unsigned long long saved_eager = ctx->eager;
+  if (automatic) {
+    // The choice must be the same on every process.  A process that hosts all ranks sees the whole count matrix;
+    // otherwise the caller's hint decides, and without one the spread-out order with the rendezvous protocol,
+    // which every process can pick on its own.
+    double mean = ctx->hint_mean, cv = ctx->hint_cv;
+    long long mx = 0;
+    if (L == P) {
+      double s1 = 0, s2 = 0;
+      for (int v : ctx->sc) { const double b2 = (double)v * ts; s1 += b2; s2 += b2 * b2; mx = std::max<long long>(mx, (long long)v * ts); }
+      const double nn = (double)ctx->sc.size();
+      mean = s1 / nn;
+      cv = mean > 0 ? std::sqrt(std::max(0.0, s2 / nn - mean * mean)) / mean : 0.0;
+    }
+    rbv_choice ch;
+    std::memset(&ch, 0, sizeof ch);
+    ch.algo = ALG_SPREADOUT; ch.r = 2;
+    if (mean >= 0) rbv_tuner_choose(P, c.nproc(), mean, cv, &ch);
+    spec = mk(ch.algo, ch.n, ch.r, ch.r2, ch.b, ch.b2);
+    spec.P = P;
+    const DevPlan* dp = nullptr;
+    try { dp = c.plan_for(spec); } catch (const std::exception&) { dp = nullptr; }
+    if (!dp || dp->plan.err) { spec = mk_spreadout(); spec.P = P; ch.eager = 0; }   // a table entry that does not fit this communicator
+    // eager needs one cell size on all processes: known only where the whole matrix is
+    ctx->eager = (ch.eager && L == P && mx > 0 && mx <= (256 << 10) &&
+                  (unsigned long long)(P + 64) * (2ull * mx + 16) <= c.layout().arena_bytes) ? (unsigned long long)mx : 0ull;
+    ctx->last_choice = ch;
+  }
+  struct Restore { rbv_ctx_s* c; unsigned long long e; bool on; ~Restore() { if (on) c->eager = e; } } restore{ctx, saved_eager, automatic};
   // The call is resolved once and kept: a loop that repeats the same collective (same buffers, counts and
   // parameters) pays for the resolution once and then for one kernel launch per iteration.
   std::vector<char> key;
@@ -347,11 +415,7 @@ int enqueue(rbv_comm_t comm, const AlgoSpec& spec_in, int ts, const char* sendbu
   return rbv_launch(ctx, ctx->cached, ctx->stream);
 }
 
-AlgoSpec mk(int algo, int n = 0, int r = 2, int r2 = 0, int b = 0, int b2 = 0) {
-  AlgoSpec s;
-  s.algo = algo; s.n = n; s.r = r; s.r2 = r2; s.b = b; s.b2 = b2;
-  return s;
-}
+
 
 int uniform_call(const AlgoSpec& s, char* sendbuf, int sendcount, int ts, char* recvbuf, int recvcount,
                  rbv_comm_t comm) {
@@ -405,7 +469,11 @@ int twolayer_communicator_linear_s4(int n, int bblock1, int bblock2, RBV_V_ARGS)
 int merge_alltoallv(int ncores, RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_MERGE, ncores), 0); }
 int simply_merge_alltoallv(int ncores, RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_SIMPLE_MERGE, ncores), 0); }
 int split_alltoallv(RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_SPLIT), 0); }
-int ML_benchmark(RBV_V_ARGS) { return RBV_V_PASS(mk(ALG_SPREADOUT), 0); }
+// algo -1: resolved by the tuner once all local ranks have made their call
+int rbv_alltoallv_auto(RBV_V_ARGS) { return RBV_V_PASS(mk(-1), 0); }
+int ML_benchmark(RBV_V_ARGS) { return RBV_V_PASS(mk(-1), 0); }
+// the configuration the latest automatic call resolved to
+void rbv_ctx_last_choice(rbv_ctx_t ctx, rbv_choice* out) { *out = ctx->last_choice; }
 void spreadout_alltoallv(RBV_V_ARGS) { (void)RBV_V_PASS(mk(ALG_SPREADOUT), 0); }
 
 int uniform_spreadout_twolayer(int n, int r, char* sendbuf, int sendcount, rbv_datatype sendtype, char* recvbuf,

@@ -26,6 +26,9 @@ struct rbv_ctx_s {
   // arguments (a loop over one collective then costs one kernel launch per iteration)
   void* cached = nullptr;
   int last_rc = 0;                // return code of the latest rbv_prepare*
+  bool automatic = false;         // the collective being collected asked for the automatic choice
+  rbv_choice last_choice{};       // what the latest automatic call resolved to
+  double hint_mean = -1, hint_cv = 0;   // what the caller said about the whole exchange (automatic entry points)
   std::vector<char> cached_key;
   std::vector<rbv_comm_s> comms;
   // calls of the local ranks collected until all L have arrived

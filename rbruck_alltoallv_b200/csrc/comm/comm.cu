@@ -8,6 +8,8 @@
 #include <cstring>
 #include <stdexcept>
 
+#include <cuda.h>
+
 #include "rbv/context.h"
 
 namespace rbv {
@@ -28,7 +30,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size_t arena_bytes)
     : P_(P), L_(nproc > 0 ? P / nproc : 0), nproc_(nproc), proc_(proc), device_(device) {
-  if (P < 1 || P > kMaxRanks) throw std::runtime_error("rank count must be in 1..64");
+  if (P < 1 || P > kMaxRanksStatic) throw std::runtime_error("rank count must be in 1..1024");
   if (nproc < 1 || nproc > kMaxProcs || P % nproc != 0) throw std::runtime_error("process count must divide the rank count (max 16)");
   if (proc < 0 || proc >= nproc) throw std::runtime_error("process index out of range");
   RBV_CUDA_THROW(cudaSetDevice(device));
@@ -36,10 +38,10 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   RBV_CUDA_THROW(cudaGetDeviceProperties(&prop, device));
   sm_count_ = prop.multiProcessorCount;
   int per_sm = 1;
-  RBV_CUDA_THROW(a2av_configure(P, &per_sm));
+  RBV_CUDA_THROW(a2av_configure(std::min(P, kMaxRanks), &per_sm));
   per_sm = std::max(1, std::min(per_sm, 2));
   max_ctas_ = sm_count_ * per_sm;
-  bulk_ctas_ = sm_count_ * std::max(0, std::min(a2av_bulk_ctas_per_sm(P), 1));
+  bulk_ctas_ = sm_count_ * std::max(0, std::min(a2av_bulk_ctas_per_sm(std::min(P, kMaxRanks)), 1));
   if (const char* e = std::getenv("RBV_BULK")) bulk_mode_ = std::atoi(e);
   if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_mode_ = std::atoi(e) != 0 ? 1 : 0;
   if (const char* e = std::getenv("RBV_STATIC_OCC")) static_occ_ = std::atoi(e) >= 2 ? 2 : 1;
@@ -50,9 +52,9 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   lay_.ctrl_off = 0;
   lay_.trace_off = align_up(sizeof(CtrlBlock), 256);
   lay_.flags_off = lay_.trace_off + align_up(sizeof(TraceBlock), 256);
-  lay_.flags_per_rank = kMaxFlagsPerRank;
+  lay_.flags_per_rank = L_ <= kMaxRanks ? kMaxFlagsPerRank : kMaxCellsPerRank;   // many ranks per GPU: fewer chunk flags each
   lay_.meta_off = lay_.flags_off + align_up(sizeof(unsigned) * 2ull * L_ * lay_.flags_per_rank, 256);
-  lay_.meta_bytes = meta_table_bytes(P);
+  lay_.meta_bytes = P <= kMaxRanks ? meta_table_bytes(P) : 256;   // larger communicators run static calls only: no tables
   lay_.stage_off = align_up(lay_.meta_off + 2 * lay_.meta_bytes, 4096);
   lay_.arena_bytes = align_up(arena_bytes, 4096);
   lay_.eager_off = lay_.stage_off + 2ull * L_ * lay_.arena_bytes;
@@ -86,6 +88,7 @@ cudaError_t Context::clear_library_regions() {
 Context::~Context() {
   cudaSetDevice(device_);
   cudaDeviceSynchronize();
+  nvls_teardown();
   for (auto& kv : plans_) {
     if (kv.second->d_ops) cudaFree(kv.second->d_ops);
     if (kv.second->d_done) cudaFree(kv.second->d_done);
@@ -195,8 +198,9 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
         RBV_CUDA_THROW(cudaMalloc(&dp->d_done, ops.size() * sizeof(unsigned)));
         RBV_CUDA_THROW(cudaMemset(dp->d_done, 0, ops.size() * sizeof(unsigned)));
       }
-      // eager variant of the op list
+      // eager variant of the op list (communicators of more than 64 ranks run static calls only)
       std::vector<Op> eops;
+      if (P_ > kMaxRanks) ops.clear();
       eops.reserve(ops.size() + (size_t)L_ * P_);
       for (Op o : ops) {
         if (!(o.flags & 1u)) {
@@ -205,7 +209,7 @@ const DevPlan* Context::plan_for(const AlgoSpec& s) {
         }
         eops.push_back(o);
       }
-      for (int lr = 0; lr < L_; lr++) {
+      for (int lr = 0; lr < L_ && P_ <= kMaxRanks; lr++) {
         const int d = proc_ * L_ + lr;
         for (int s = 0; s < P_; s++) {
           if (s == d) continue;
@@ -310,6 +314,11 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   if (persistent && opt.allow_static && !ca.counts_on_device && !eager && !inplace && absent_rank_ < 0 &&
       (nproc_ == 1 || (ca.g_counts && ca.g_rdispls && ca.g_recvoff)))
     return prepare_static(dp, ts, ca, opt, out);
+  if (P_ > kMaxRanks) {
+    last_error_ = "communicators of more than 64 ranks take persistent calls with host-side counts only "
+                  "(rendezvous protocol, not in place): prepare the call, then launch it";
+    return RBV_ERR_BAD_ARG;
+  }
 
   KernelArgs& ka = out->ka;
   std::memset(&ka, 0, sizeof ka);
@@ -758,6 +767,110 @@ int Context::set_nvls_meta(void* self_ptr, void* mc_ptr, size_t bytes) {
   nvls_self_ = static_cast<char*>(self_ptr); nvls_mc_ = static_cast<char*>(mc_ptr); nvls_bytes_ = bytes;
   return cudaMemset(nvls_self_, 0, nvls_bytes_needed()) == cudaSuccess ? 0 : RBV_ERR_BAD_ARG;
 }
+
+// ---- NVLS: the library's own multicast object (CUDA driver API) ---------------------------------------------
+namespace {
+const char* cu_name(CUresult r) {
+  const char* s = nullptr;
+  cuGetErrorName(r, &s);
+  return s ? s : "unknown CUDA driver error";
+}
+}  // namespace
+#define RBV_CU(expr)                                                              \
+  do {                                                                            \
+    CUresult r__ = (expr);                                                        \
+    if (r__ != CUDA_SUCCESS) {                                                    \
+      last_error_ = std::string(#expr) + " failed: " + cu_name(r__);              \
+      return (int)r__;                                                            \
+    }                                                                             \
+  } while (0)
+
+int Context::nvls_create(size_t bytes, int* fd_out) {
+  int supported = 0;
+  RBV_CU(cuDeviceGetAttribute(&supported, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, device_));
+  if (!supported) { last_error_ = "this device does not support NVLink multicast"; return -1; }
+  CUmulticastObjectProp prop{};
+  prop.numDevices = (unsigned)nproc_;
+  prop.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  prop.size = bytes;
+  size_t gran = 0;
+  RBV_CU(cuMulticastGetGranularity(&gran, &prop, CU_MULTICAST_GRANULARITY_RECOMMENDED));
+  prop.size = align_up(std::max<size_t>(bytes, 1), gran);
+  CUmemGenericAllocationHandle mc = 0;
+  RBV_CU(cuMulticastCreate(&mc, &prop));
+  own_mc_handle_ = mc;
+  own_mc_bytes_ = prop.size;
+  int fd = -1;
+  RBV_CU(cuMemExportToShareableHandle(&fd, mc, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+  *fd_out = fd;
+  return 0;
+}
+
+int Context::nvls_import(int fd, size_t bytes) {
+  int supported = 0;
+  RBV_CU(cuDeviceGetAttribute(&supported, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, device_));
+  if (!supported) { last_error_ = "this device does not support NVLink multicast"; return -1; }
+  CUmemGenericAllocationHandle mc = 0;
+  RBV_CU(cuMemImportFromShareableHandle(&mc, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                        CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+  own_mc_handle_ = mc;
+  own_mc_bytes_ = bytes;   // the size process 0 rounded up
+  return 0;
+}
+
+int Context::nvls_add_device() {
+  if (!own_mc_handle_) { last_error_ = "no multicast object"; return -1; }
+  RBV_CU(cuMulticastAddDevice(own_mc_handle_, device_));
+  return 0;
+}
+
+int Context::nvls_bind_and_map(void** self_ptr, void** mc_ptr, size_t* bytes_out) {
+  if (!own_mc_handle_) { last_error_ = "no multicast object"; return -1; }
+  CUmemAllocationProp ap{};
+  ap.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  ap.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  ap.location.id = device_;
+  size_t gran = 0;
+  RBV_CU(cuMemGetAllocationGranularity(&gran, &ap, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
+  const size_t size = own_mc_bytes_;
+  if (size % gran) { last_error_ = "multicast size is not a multiple of the allocation granularity"; return -1; }
+  CUmemGenericAllocationHandle mem = 0;
+  RBV_CU(cuMemCreate(&mem, size, &ap, 0));
+  own_mem_handle_ = mem;
+  RBV_CU(cuMulticastBindMem(own_mc_handle_, 0, mem, 0, size, 0));
+  own_mc_bound_ = true;
+  CUmemAccessDesc acc{};
+  acc.location = ap.location;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  CUdeviceptr va = 0, mva = 0;
+  RBV_CU(cuMemAddressReserve(&va, size, gran, 0, 0));
+  own_va_ = va;
+  RBV_CU(cuMemMap(va, size, 0, mem, 0));
+  RBV_CU(cuMemSetAccess(va, size, &acc, 1));
+  RBV_CU(cuMemAddressReserve(&mva, size, gran, 0, 0));
+  own_mc_va_ = mva;
+  RBV_CU(cuMemMap(mva, size, 0, own_mc_handle_, 0));
+  RBV_CU(cuMemSetAccess(mva, size, &acc, 1));
+  *self_ptr = reinterpret_cast<void*>(va);
+  *mc_ptr = reinterpret_cast<void*>(mva);
+  *bytes_out = size;
+  return 0;
+}
+
+void Context::nvls_teardown() {
+  if (!own_mc_handle_) return;
+  cudaDeviceSynchronize();
+  nvls_self_ = nvls_mc_ = nullptr;
+  nvls_bytes_ = 0;
+  if (own_mc_va_) { cuMemUnmap(own_mc_va_, own_mc_bytes_); cuMemAddressFree(own_mc_va_, own_mc_bytes_); }
+  if (own_va_) { cuMemUnmap(own_va_, own_mc_bytes_); cuMemAddressFree(own_va_, own_mc_bytes_); }
+  if (own_mc_bound_) cuMulticastUnbind(own_mc_handle_, device_, 0, own_mc_bytes_);
+  if (own_mem_handle_) cuMemRelease(own_mem_handle_);
+  cuMemRelease(own_mc_handle_);
+  own_mc_handle_ = own_mem_handle_ = own_va_ = own_mc_va_ = 0;
+  own_mc_bound_ = false;
+}
+#undef RBV_CU
 
 StatusBlock Context::status(cudaStream_t stream) {
   cudaStreamSynchronize(stream);

@@ -146,6 +146,18 @@ class Context {
   unsigned long long* nvls_aux_mc() const {
     return nvls_mc_ ? reinterpret_cast<unsigned long long*>(nvls_mc_ + nvls_aux_off()) : nullptr;
   }
+  // NVLS set-up done by the library itself (CUDA driver API): an NVLink multicast object over one buffer per GPU.
+  // Collective, in four steps with a host barrier after each: (1) process 0 creates the object and exports it as a
+  // file descriptor, which the caller hands to the other processes (SCM_RIGHTS over a Unix socket); (2) every
+  // process imports it (process 0 skips this) and adds its device; (3) every process allocates its physical buffer,
+  // binds it to the object and maps both the buffer and the multicast view; (4) set_nvls_meta() with the two
+  // addresses.  Each returns 0 or a CUDA driver error code (last_error() has the text).
+  int nvls_create(size_t bytes, int* fd_out);
+  int nvls_import(int fd, size_t bytes);
+  int nvls_add_device();
+  int nvls_bind_and_map(void** self_ptr, void** mc_ptr, size_t* bytes_out);
+  void nvls_teardown();
+  size_t nvls_object_bytes() const { return own_mc_bytes_; }
   const std::string& last_error() const { return last_error_; }
   const DevPlan* plan_for(const AlgoSpec& spec);
 
@@ -164,6 +176,10 @@ class Context {
   char* nvls_self_ = nullptr;
   char* nvls_mc_ = nullptr;
   size_t nvls_bytes_ = 0;
+  // own multicast object (0: none, or the buffer came from the caller)
+  unsigned long long own_mc_handle_ = 0, own_mem_handle_ = 0, own_va_ = 0, own_mc_va_ = 0;
+  size_t own_mc_bytes_ = 0;
+  bool own_mc_bound_ = false;
   unsigned long long timeout_ns_ = 2000000000ull;
   int max_ctas_ = 1, sm_count_ = 1;
   StatusBlock* host_status_ = nullptr;

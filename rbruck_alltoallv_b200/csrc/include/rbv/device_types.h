@@ -34,7 +34,11 @@
 
 namespace rbv {
 
-constexpr int kMaxRanks = 64;         // logical ranks per communicator
+constexpr int kMaxRanks = 64;         // logical ranks per communicator for calls whose arguments travel as kernel
+                                      // parameters and whose tables sit in shared memory (dynamic and eager kernels)
+constexpr int kMaxRanksStatic = 1024; // logical ranks per communicator for persistent calls with host-side counts
+                                      // (static kernel: no per-rank state in the kernel beyond its arrival tallies);
+                                      // the reference's recorded traces go up to 1024 ranks
 constexpr int kMaxProcs = 16;         // processes (GPUs) per communicator
 constexpr int kMaxCellsPerRank = 2048;
 constexpr int kMaxFlagsPerRank = 16384;   // chunk flags per rank and parity (cells x chunks per cell of one call)
@@ -74,8 +78,8 @@ struct TraceBlock {
 
 // Lives at offset 0 of every heap.  Peers write the counters with system-scope atomics.
 struct CtrlBlock {
-  unsigned long long recv_arrivals[kMaxRanks];   // += 1 per chunk landed in a local rank's recvbuf
-  unsigned long long recv_target[kMaxRanks];     // running total of chunks expected so far (kept by the owner)
+  unsigned long long recv_arrivals[kMaxRanksStatic];   // += 1 per chunk landed in a local rank's recvbuf
+  unsigned long long recv_target[kMaxRanksStatic];     // running total of chunks expected so far (kept by the owner)
   unsigned int abort_flag;       // set locally on error, and by peers that want everyone to stop
   unsigned int pad0;
   unsigned int exit_count;       // traced calls only: CTAs that finished (the last one copies the stamps to the host)

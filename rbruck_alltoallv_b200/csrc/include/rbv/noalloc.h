@@ -16,8 +16,10 @@
  *   1 <= nranks <= RBV_NOALLOC_MAX_RANKS, every block (count * type_size) <= RBV_NOALLOC_MAX_BLOCK_BYTES.
  * Larger requests are refused with RBV_NOALLOC_ERR_TOO_LARGE before anything is launched.
  *
- * The first call on a device looks up the device address of the scratch array and uploads the schedule
- * (synchronously).  Make that first call outside any stream capture.
+ * The first call on a device looks up the device address of the scratch array and uploads the schedules of all
+ * rank counts from 1 to RBV_NOALLOC_MAX_RANKS (synchronous copies of about 20 KB in total).  Make that first call
+ * outside any stream capture.  Later calls on that device, with any rank count, only enqueue a memset and a
+ * kernel.  The first-call set-up is guarded by a mutex, so host threads may race to make it.
  *
  * All calls on a device share the one scratch array.  Each call clears the control words it needs at zero
  * (stream-ordered) and otherwise overwrites what the previous call left.  Two calls that overlap on the GPU
@@ -47,9 +49,10 @@ int rbv_alltoallv_noalloc(int nranks, int type_size, const void* const* sendbufs
                           const int* sendcounts, const long long* sdispls, const int* recvcounts,
                           const long long* rdispls, void* cuda_stream);
 
-/* Waits for `cuda_stream`, then returns 0 if the last call on the current device completed, a positive value if
- * its kernel gave up (a bounded wait ran out, or a block was larger than the receiver's recvcount), -1 if the
- * query itself failed.  Allocates nothing. */
+/* Waits for `cuda_stream`, then returns 0 if the last call on the current device completed, or the code of the
+ * first failure its kernel recorded: 1 a bounded wait ran out, 3 the blocks do not fit the built-in staging cells,
+ * 4 a block was larger than the receiver's recvcount, 5 stopped because of an error elsewhere; -1 if the query
+ * itself failed.  Allocates nothing. */
 int rbv_noalloc_status(void* cuda_stream);
 
 /* Text of the last error returned to this thread by rbv_alltoallv_noalloc. */

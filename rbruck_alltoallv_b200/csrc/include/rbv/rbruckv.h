@@ -107,6 +107,18 @@ void rbv_prepared_free(rbv_ctx_t ctx, void* prepared);
  * with one multimem.st per unit instead of one store per peer.  Collective: all processes or none. */
 int rbv_ctx_set_nvls_meta(rbv_ctx_t ctx, void* self_ptr, void* mc_ptr, size_t bytes);
 size_t rbv_ctx_meta_bytes(rbv_ctx_t ctx);
+/* The same with a multicast object that the library creates and binds itself (CUDA driver API), in collective steps
+ * with a host barrier after each: process 0 calls rbv_ctx_nvls_create (bytes = rbv_ctx_meta_bytes) and passes the
+ * file descriptor to the other processes (SCM_RIGHTS over a Unix socket) together with *size_out; they call
+ * rbv_ctx_nvls_import; everybody calls rbv_ctx_nvls_add_device, then rbv_ctx_nvls_bind (allocates this GPU's buffer,
+ * binds it, maps buffer and multicast view and switches the metadata tables over).  rbv_ctx_nvls_teardown undoes it
+ * (also done when the context is destroyed).  Keep NVLS off in anything that tests failures: a process that dies
+ * while bound to a multicast object disturbs the other GPUs. */
+int rbv_ctx_nvls_create(rbv_ctx_t ctx, size_t bytes, int* fd_out, size_t* size_out);
+int rbv_ctx_nvls_import(rbv_ctx_t ctx, int fd, size_t bytes);
+int rbv_ctx_nvls_add_device(rbv_ctx_t ctx);
+int rbv_ctx_nvls_bind(rbv_ctx_t ctx);
+void rbv_ctx_nvls_teardown(rbv_ctx_t ctx);
 
 /* Protocol of the following calls: 0 = rendezvous (any size); > 0 = eager, for blocks of at most this many bytes
  * (every rank must pass the same value; needs (P + cells) * (16 + 2 * bytes) of staging arena per rank). */
@@ -118,6 +130,25 @@ void rbv_ctx_set_static(rbv_ctx_t ctx, int on);      /* 0: persistent calls keep
 /* Time stamps (device clock, ns) per key of the schedule (a round, a batch; key = phase << 24 | step) of the most
  * recent traced call: earliest start and latest end over all warps of this process.  Returns the number filled. */
 int rbv_ctx_last_trace(rbv_ctx_t ctx, unsigned* keys, unsigned long long* start_ns, unsigned long long* end_ns, int max);
+
+/* ---- automatic choice ----
+ * A configuration as the tuner's table of measured winners stores it. */
+typedef struct rbv_choice_s {
+  int algo;          /* rbv::Algo value */
+  int n, r, r2, b, b2;
+  int eager;         /* 1: eager protocol (blocks up to 256 KB), 0: rendezvous */
+} rbv_choice;
+/* Table file to read (default: $RBV_TUNER_CACHE; the Python package points this at its own copy). */
+void rbv_tuner_set_table(const char* path);
+int rbv_tuner_entries(void);
+/* Winner for a communicator of P ranks on nproc processes, mean block size and coefficient of variation of the
+ * block sizes.  Returns 1 when it comes from the table, 0 for the built-in rule. */
+int rbv_tuner_choose(int P, int nproc, double mean_block_bytes, double cv, rbv_choice* out);
+/* What the automatic entry points know about the whole exchange when a process hosts only some of the ranks:
+ * mean block bytes and coefficient of variation, the same values on every process (mean < 0 forgets the hint;
+ * without one, several processes use the spread-out order with the rendezvous protocol, which needs no agreement). */
+void rbv_ctx_set_auto_hint(rbv_ctx_t ctx, double mean_block_bytes, double cv);
+void rbv_ctx_last_choice(rbv_ctx_t ctx, rbv_choice* out); /* what the latest automatic call resolved to */
 
 /* Phase timers of the most recent call, filled by rbv_update_timers() (which synchronises;
  * call rbv_ctx_set_trace(ctx, 1) first).
@@ -188,7 +219,10 @@ int simply_merge_alltoallv(int ncores, char* sendbuf, int* sendcounts, int* sdis
                            char* recvbuf, int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
 int split_alltoallv(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
                     int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
-/* Declared but never defined in the reference (src/rbruckv.h:80-81); here: the automatic choice. */
+/* Declared but never defined in the reference (src/rbruckv.h:80-81); here: the automatic choice, that is
+ * rbv_alltoallv_auto under the reference's name. */
+int rbv_alltoallv_auto(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,
+                       int* recvcounts, int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
 int ML_benchmark(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf, int* recvcounts,
                  int* rdispls, rbv_datatype recvtype, rbv_comm_t comm);
 void spreadout_alltoallv(char* sendbuf, int* sendcounts, int* sdispls, rbv_datatype sendtype, char* recvbuf,

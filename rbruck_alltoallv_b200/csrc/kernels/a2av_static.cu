@@ -48,7 +48,7 @@ __device__ void static_error(const StaticArgs& a, int code, int site, int d0, in
 // few spilled words for twice the warps, hence twice the loads in flight per SM.
 template <int MINB>
 __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __grid_constant__ StaticArgs a) {
-  __shared__ unsigned s_arrived[kMaxRanks];
+  __shared__ unsigned s_arrived[kMaxRanksStatic];
   __shared__ unsigned s_seq;
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
     // the last CTA to read the call number advances it for the next call
     if (atomicAdd(&my->start_count, 1u) == gridDim.x - 1) dev::advance_call_seq(my, sq);
   }
-  if (tid < kMaxRanks) s_arrived[tid] = 0;
+  for (int i = tid; i < a.P; i += blockDim.x) s_arrived[i] = 0;
   __syncthreads();
   const unsigned seq = s_seq;
   const int parity = seq & 1;
@@ -84,7 +84,8 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   if (multi && blockIdx.x == 0 && tid < a.nproc && tid != a.proc)
     dev::st_relaxed_sys(&ctrl_of(a, tid)->entered[a.proc], flagv);
   // the owner of a receive buffer adds the chunks this call brings to its running target
-  if (blockIdx.x == 0 && tid < a.L) my->recv_target[tid] += a.expect[tid];
+  if (blockIdx.x == 0)
+    for (int i = tid; i < a.L; i += blockDim.x) my->recv_target[i] += a.expect[i];
 
   bool alive = true;
   unsigned ready = 1u << a.proc;   // processes known to have entered this call
@@ -138,26 +139,26 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   __syncthreads();
   // report this CTA's deliveries: the barrier orders every warp's stores before the fence, which publishes them
   if (blockIdx.x == 0 && tid == 0) my->status.trace[5] = dev::globaltimer();
-  if (tid < a.P) {
-    const unsigned n = s_arrived[tid];
-    const int dproc = tid / a.L;
+  for (int d = tid; d < a.P; d += blockDim.x) {
+    const unsigned n = s_arrived[d];
+    const int dproc = d / a.L;
     const bool far = dproc != a.proc;
     if (n) {
       dev::fence_acq_rel(far);
-      dev::red_relaxed_add(&ctrl_of(a, dproc)->recv_arrivals[tid - dproc * a.L], (unsigned long long)n, far);
+      dev::red_relaxed_add(&ctrl_of(a, dproc)->recv_arrivals[d - dproc * a.L], (unsigned long long)n, far);
     }
   }
   if (blockIdx.x == 0) {
     if (tid == 0) my->status.trace[3] = my->status.trace[6] = dev::globaltimer();
-    if (tid < a.L) {
-      const unsigned long long target = my->recv_target[tid];
-      int r = alive ? dev::wait_ge(&my->recv_arrivals[tid], target, wc, multi) : (int)dev::WAIT_ABORTED;
+    for (int i = tid; i < a.L; i += blockDim.x) {
+      const unsigned long long target = my->recv_target[i];
+      int r = alive ? dev::wait_ge(&my->recv_arrivals[i], target, wc, multi) : (int)dev::WAIT_ABORTED;
       if (r == dev::WAIT_TIMEOUT)
-        static_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, tid, (int)(target - my->recv_arrivals[tid]));
+        static_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, i, (int)(target - my->recv_arrivals[i]));
     }
     // a process that was told to stop (or runs on a communicator that failed earlier and was not reset) says so;
-    // the load overlaps with the wait above
-    if (tid == 32 + (a.L > 32 ? 32 : 0) && dev::ld_relaxed_sys(&my->abort_flag)) static_error(a, RBV_ERR_ABORTED, 0, 0, 0);
+    // where fewer than all threads wait above, the load overlaps with that wait
+    if (tid == (int)blockDim.x - 1 && dev::ld_relaxed_sys(&my->abort_flag)) static_error(a, RBV_ERR_ABORTED, 0, 0, 0);
     __syncthreads();
     if (tid == 0) my->status.trace[4] = my->status.trace[7] = dev::globaltimer();
   }

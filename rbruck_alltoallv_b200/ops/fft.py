@@ -148,3 +148,21 @@ class PencilTranspose:
         recv = [torch.empty(nz, int(self.ysplit[r2]), nx, dtype=self.dtype, device=src.device) for r2 in range(self.pr)]
         dist.all_to_all(recv, send, group=group)
         return torch.cat(recv, dim=1).permute(0, 2, 1).contiguous()
+
+    def bytes_sent_yz(self) -> Tuple[int, int]:
+        """(all bytes of this rank's y-pencil, bytes that leave the GPU) for the y -> z transpose."""
+        nz, nx, n = self.shape_y
+        total = nz * nx * n * self.esize
+        local = nz * nx * int(self.y2split[self.me_c]) * self.esize
+        return total, total - local
+
+    def nccl_y_to_z(self, src: torch.Tensor, group) -> torch.Tensor:
+        """Baseline for the second transpose: pack per destination, NCCL all-to-all inside the row group, unpack
+        with a transposition."""
+        import torch.distributed as dist
+        nx = self.shape_y[1]
+        send = [src[:, :, self.y20[c2]:self.y20[c2] + self.y2split[c2]].contiguous() for c2 in range(self.pc)]
+        ny2 = int(self.y2split[self.me_c])
+        recv = [torch.empty(int(self.zsplit[c2]), nx, ny2, dtype=self.dtype, device=src.device) for c2 in range(self.pc)]
+        dist.all_to_all(recv, send, group=group)
+        return torch.cat(recv, dim=0).permute(1, 2, 0).contiguous()

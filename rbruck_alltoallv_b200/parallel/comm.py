@@ -123,7 +123,8 @@ class Communicator:
                 raise CommError("cudaIpcOpenMemHandle failed: " + self._lib.rbv_last_error().decode())
             dist.barrier(group=self._side)
         self.nvls = False
-        if self.nproc > 1 and os.environ.get("RBV_NVLS", "0") == "1":
+        self.nvls_owner = None
+        if self.nproc > 1 and os.environ.get("RBV_NVLS", "0") in ("1", "torch"):
             self._enable_nvls()
         info = (C.c_longlong * 8)()
         self._lib.rbv_ctx_info(self._ctx, info)
@@ -131,10 +132,75 @@ class Communicator:
         self.sm_count = int(info[7])
 
     def _enable_nvls(self) -> None:
-        """Moves the metadata tables into a buffer bound to an NVLink multicast object (allocated and bound by
-        torch's symmetric-memory allocator), so that the metadata phase publishes with ``multimem.st``: NVSwitch
-        replicates one store into the tables of all GPUs.  Opt-in (``RBV_NVLS=1``) and kept off in fault tests: a
-        process that dies while its memory is bound to a multicast object disturbs the other GPUs."""
+        """Moves the metadata tables into a buffer bound to an NVLink multicast object, so that the metadata phase
+        publishes with ``multimem.st`` (NVSwitch replicates one store into the tables of all GPUs) and the auxiliary
+        barriers arrive with one ``multimem.red``.  The object is the library's own: process 0 creates it with the
+        CUDA driver API and hands its file descriptor to the other processes over a Unix socket (``SCM_RIGHTS``);
+        every process adds its device, binds a buffer of its own and maps both views (``csrc/comm/comm.cu``,
+        ``Context::nvls_*``).  ``RBV_NVLS=torch`` borrows torch's symmetric-memory allocator for the object instead.
+        Opt-in (``RBV_NVLS=1``) and kept off in fault tests: a process that dies while its memory is bound to a
+        multicast object disturbs the other GPUs."""
+        if os.environ.get("RBV_NVLS") == "torch":
+            return self._enable_nvls_torch()
+        import socket
+        import tempfile
+        lib, dist = self._lib, self._dist
+        nbytes = max(int(lib.rbv_ctx_meta_bytes(self._ctx)), 4096)
+
+        def agree(ok: bool) -> bool:
+            flag = torch.tensor([1 if ok else 0], dtype=torch.int64)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self._side)
+            return bool(int(flag.item()))
+
+        # step 1: process 0 creates the object; the descriptor travels over a Unix socket
+        fd, size, ok, srv, path = C.c_int(-1), C.c_size_t(0), True, None, None
+        if self.proc == 0:
+            ok = lib.rbv_ctx_nvls_create(self._ctx, nbytes, C.byref(fd), C.byref(size)) == 0
+            if ok:
+                path = os.path.join(tempfile.mkdtemp(prefix="rbv_nvls_"), "fd.sock")
+                srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+                srv.bind(path)
+                srv.listen(self.nproc)
+        info = [(path, int(size.value)) if self.proc == 0 else None]
+        dist.broadcast_object_list(info, src=0, group=self._side)
+        path, obj_bytes = info[0]
+        if not agree(ok and path is not None):
+            if srv is not None:
+                srv.close()
+            lib.rbv_ctx_nvls_teardown(self._ctx)
+            return
+        if self.proc == 0:
+            for _ in range(self.nproc - 1):
+                conn, _ = srv.accept()
+                socket.send_fds(conn, [b"fd"], [fd.value])
+                conn.close()
+            srv.close()
+            os.close(fd.value)
+            try:
+                os.unlink(path)
+                os.rmdir(os.path.dirname(path))
+            except OSError:
+                pass
+        else:
+            cli = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+            cli.connect(path)
+            _, fds, _, _ = socket.recv_fds(cli, 16, 1)
+            cli.close()
+            ok = lib.rbv_ctx_nvls_import(self._ctx, fds[0], obj_bytes) == 0
+            os.close(fds[0])
+        # steps 2-4, each completed everywhere before the next starts
+        for step in (lib.rbv_ctx_nvls_add_device, lib.rbv_ctx_nvls_bind):
+            ok = agree(ok) and step(self._ctx) == 0
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self._side)
+        if not agree(ok):
+            lib.rbv_ctx_nvls_teardown(self._ctx)
+            return
+        self.nvls = True
+        self.nvls_owner = "library"
+
+    def _enable_nvls_torch(self) -> None:
+        """The same with a multicast object created and bound by torch's symmetric-memory allocator."""
         try:
             import torch.distributed._symmetric_memory as symm
             nbytes = max(int(self._lib.rbv_ctx_meta_bytes(self._ctx)), 4096)
@@ -157,6 +223,7 @@ class Communicator:
         self._dist.barrier(group=self._side)
         self._nvls_keep = (buf, hdl)
         self.nvls = True
+        self.nvls_owner = "torch"
 
     # ---- life cycle -------------------------------------------------------------------------
     def close(self):

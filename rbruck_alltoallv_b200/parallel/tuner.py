@@ -125,6 +125,21 @@ def _pow2_upto(limit: int) -> List[int]:
     return out
 
 
+def native_choose(P: int, nproc: int, mean_block_bytes: float, cv: float = 0.0, path=None) -> dict:
+    """The same lookup done by the native reader that serves the C API (``csrc/api/tuner_native.cpp``), on the table
+    file on disk (not on entries recorded in this process and not yet saved)."""
+    from .. import _native
+    from .plan import ALGOS
+    lib = _native.host_lib()
+    lib.rbv_tuner_set_table(str(path or _cache_path()).encode())
+    ch = _native.Choice()
+    lib.rbv_tuner_choose(P, nproc, float(mean_block_bytes), float(cv), ch)
+    out = {"algo": ALGOS[ch.algo], "protocol": "eager" if ch.eager else "rendezvous"}
+    for k in ("n", "r", "r2", "b", "b2"):
+        out[k] = int(getattr(ch, k))
+    return out
+
+
 def candidates(P: int, groups: Optional[List[int]] = None, full: bool = True) -> List[dict]:
     """The configurations a sweep tries, simplest first (single hop, then flat Bruck by decreasing radix, then the
     two-layer schedules).  Batch parameters run over 1, 2, 4, ... like the reference's drivers sweep them

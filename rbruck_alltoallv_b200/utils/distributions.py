@@ -88,6 +88,25 @@ def sparse_groups(P: int, n: int, ncores: int, transpose: bool = False) -> np.nd
     return Cm.T.copy() if transpose else Cm
 
 
+def leaders_only(P: int, n: int, ncores: int) -> np.ndarray:
+    """Only the first rank of every group of ``ncores`` talks, to the other groups' first ranks, ``n`` elements each:
+    the second pattern of the reference's gather driver (examples/gather_benchmark.cpp:120-125)."""
+    Cm = np.zeros((P, P), dtype=np.int64)
+    idx = np.arange(0, P, max(ncores, 1))
+    Cm[np.ix_(idx, idx)] = n
+    return Cm
+
+
+def merge_pattern(P: int, csize: int, lsize: int, ncores: int) -> np.ndarray:
+    """Small blocks of ``csize`` elements everywhere, large blocks of ``lsize`` between the first ranks of the groups
+    of ``ncores``: the setting the reference's merge_alltoallv is written for (local rank 0 carries the large
+    messages and stays out of the merge, benchmarks/merge_benchmark.cpp:155-332)."""
+    Cm = np.full((P, P), csize, dtype=np.int64)
+    idx = np.arange(0, P, max(ncores, 1))
+    Cm[np.ix_(idx, idx)] = lsize
+    return Cm
+
+
 def read_matrix(path: str | Path) -> np.ndarray:
     """A whitespace-separated P x P byte-count matrix; row r holds rank r's send counts."""
     vals = np.loadtxt(str(path), dtype=np.int64, ndmin=2)

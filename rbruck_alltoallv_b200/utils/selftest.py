@@ -22,6 +22,7 @@ from . import oracle
 from .timing import L2Flusher, RankAligner, time_steps
 
 CASES = [("linear", {}), ("spreadout", {}), ("scattered", dict(b=2)), ("pairwise", {}), ("xor", {}),
+         ("merge", dict(n=2)), ("simple_merge", dict(n=2)), ("split", {}),
          ("rbruck", dict(r=2)), ("rbruck", dict(r=3)), ("rbruck_om", dict(r=2)), ("tuna", dict(r=2, b=1)),
          ("tuna2", dict(r=2, b=0)), ("ttpl", dict(n=2, r=2)), ("ttpl_bt", dict(n=2, r=2)),
          ("ttpl_bt_s1", dict(n=2, r=2, b=2)), ("ttpl_bt_s2", dict(n=2, r=2)),
@@ -32,11 +33,11 @@ CASES = [("linear", {}), ("spreadout", {}), ("scattered", dict(b=2)), ("pairwise
 
 def check_all(comm: Communicator, ts: int = 4, seed: int = 3) -> int:
     P, mine = comm.P, comm.local_ranks
-    failures = 0
+    failures = ran = 0
     for ci, (algo, kw) in enumerate(CASES):
         if algo == "xor" and P & (P - 1):
             continue
-        if kw.get("n") and (P % kw["n"] or kw["n"] >= P):
+        if kw.get("n") and (P % kw["n"] or (kw["n"] >= P and algo not in ("merge", "simple_merge"))):
             continue
         counts = D.uniform(P, 3000, seed=seed + ci)
         counts[counts < 200] = 0
@@ -51,18 +52,40 @@ def check_all(comm: Communicator, ts: int = 4, seed: int = 3) -> int:
         comm.host_barrier()
         emax = comm.max_block_bytes(prob.counts[mine], ts)
         inplace_algo = algo == "ttpl_bt_s2"
-        for rep in range(4):   # back-to-back calls exercise both parities; even: rendezvous, odd: eager protocol
-            comm.alltoallv(send, recv, prob.counts[mine], prob.sdispls[mine], prob.recvcounts[mine], prob.rdispls[mine],
-                           algo=algo, type_size=ts, eager_max_bytes=(emax if rep % 2 and not inplace_algo else 0), **kw)
-        st = comm.status()
-        bad = oracle.first_mismatch([t.cpu().numpy() for t in recv], [want[r] for r in mine])
-        if st["code"] or bad is not None:
-            failures += 1
-            print(f"[proc {comm.proc}] FAIL {algo} {kw}: status={st['name']}@{st['site']} {st['detail']} mismatch={bad}",
-                  flush=True)
-            comm.reset()
+        wanted = [want[r] for r in mine]
+        args = (send, recv, prob.counts[mine], prob.sdispls[mine], prob.recvcounts[mine], prob.rdispls[mine])
+        # Every way a call can run, each checked on its own: one-shot rendezvous (metadata exchanged by the kernel),
+        # one-shot eager, a persistent call (static kernel: everything resolved on the host) launched twice, and
+        # eager again; back-to-back calls exercise both parities.
+        for rep, mode in enumerate(("rendezvous", "eager", "static", "eager")):
+            if mode == "eager" and (inplace_algo or algo == "split"):   # neither takes the eager protocol
+                continue
+            ran += 1
+            for t in recv:
+                t.fill_(oracle.CANARY)
+            if mode == "static":
+                call = comm.prepare(*args, algo=algo, type_size=ts, **kw)
+                call.launch()
+                call.launch()
+            else:
+                comm.alltoallv(*args, algo=algo, type_size=ts, eager_max_bytes=(emax if mode == "eager" else 0), **kw)
+            st = comm.status()
+            bad = oracle.first_mismatch([t.cpu().numpy() for t in recv], wanted)
+            if st["code"] or bad is not None:
+                failures += 1
+                print(f"[proc {comm.proc}] FAIL {algo} {kw} ({mode}): status={st['name']}@{st['site']} {st['detail']} "
+                      f"mismatch={bad}", flush=True)
+            # a failure on any process resets all of them together (reset is collective)
+            flag = torch.tensor([1 if (st["code"] or bad is not None) else 0], dtype=torch.int64)
+            if comm._side is not None:
+                comm._dist.all_reduce(flag, op=comm._dist.ReduceOp.MAX, group=comm._side)
+            if int(flag.item()):
+                comm.reset()
+            if mode == "static":
+                del call
         comm.host_barrier()
         del send, recv
+    check_all.cases = ran
     return failures
 
 

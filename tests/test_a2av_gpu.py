@@ -461,3 +461,34 @@ def test_ulysses_sequence_head_exchange_round_trip():
     comm.check()
     for r in range(P):
         assert torch.equal(back[r], x[r])
+
+
+def test_more_than_64_ranks_run_as_persistent_calls():
+    """Up to 1024 logical ranks (the size of the reference's largest recorded trace) run through the static kernel,
+    which keeps no per-rank tables; one-shot calls of such communicators are refused with a clear message."""
+    from rbruck_alltoallv_b200.parallel.comm import CommError, Communicator
+    for P, algos in ((200, [("spreadout", {}), ("pairwise", {})]), (128, [("rbruck", dict(r=2)), ("ttpl_bt_s1", dict(n=16, r=4))])):
+        comm = Communicator(nranks=P, heap_bytes=256 << 20, arena_bytes=1 << 20)
+        try:
+            counts = dist.uniform(P, 40, seed=P)
+            counts[counts < 8] = 0
+            prob = oracle.make_problem(counts, 4, P, packed=False)
+            send_h = oracle.fill_send(prob, P)
+            want = oracle.expected_recv(prob, send_h)
+            send = [torch.from_numpy(b).cuda() for b in send_h]
+            recv = [comm.symm_empty(len(w), torch.uint8) for w in want]
+            for algo, kw in algos:
+                for t in recv:
+                    t.fill_(oracle.CANARY)
+                call = comm.prepare(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo=algo,
+                                    type_size=4, **kw)
+                assert call.kind == "static"
+                call.launch()
+                call.launch()
+                comm.check()
+                assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None, (P, algo)
+            with pytest.raises(CommError, match="persistent"):
+                comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo="spreadout",
+                               type_size=4)
+        finally:
+            comm.close()

@@ -38,6 +38,29 @@ WORKER = textwrap.dedent("""
     t = torch.tensor([local_max], dtype=torch.int64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     assert int(t.item()) == int(counts.max()) * 4
+    # algo="auto": per-process totals that differ by far more than a size class must still give one choice
+    from types import SimpleNamespace
+    from rbruck_alltoallv_b200.ops import alltoallv as A
+    from rbruck_alltoallv_b200.parallel import tuner
+    tuner._TABLE = {}
+    tuner.record(8, 2, 300, {"algo": "linear", "protocol": "eager"}, 10.0)
+    tuner.record(8, 2, 40000, {"algo": "rbruck", "r": 2, "protocol": "rendezvous"}, 10.0)
+    tuner.record(8, 2, 700000, {"algo": "pairwise", "protocol": "rendezvous"}, 10.0)
+    side = dist.new_group(backend="gloo")
+    comm = SimpleNamespace(P=8, L=4, nproc=2, arena_bytes=64 << 20, _side=side, _dist=dist,
+                           max_block_bytes=lambda sc, ts: 4096)
+    sc = np.full((4, 8), 64 if rank == 0 else 20000, dtype=np.int32)      # 256 B blocks here, 80 KB blocks there
+    recv = [torch.empty(4, dtype=torch.float32)]
+    got = A._auto_choice(comm, recv, sc, {}, agree_on_max=True)
+    both = [None] * world
+    dist.all_gather_object(both, (got["algo"], got.get("r"), "eager_max_bytes" in got))
+    assert both[0] == both[1], both
+    assert got["algo"] == "rbruck", got                                    # the class of the global mean (40 KB)
+    # a one-shot call has no agreement step: without a hint that is the same everywhere it must not consult its own rows
+    one = A._auto_choice(comm, recv, sc, {}, agree_on_max=False)
+    assert one["algo"] == "spreadout" and "eager_max_bytes" not in one
+    hinted = A._auto_choice(comm, recv, sc, {"mean_block_bytes": 700000.0}, agree_on_max=False)
+    assert hinted["algo"] == "pairwise"
     dist.barrier()
     dist.destroy_process_group()
     print("worker", rank, "ok")

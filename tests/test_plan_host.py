@@ -166,3 +166,13 @@ def test_key_indices_follow_issue_order():
         keys = ops["key"].astype(np.int64)
         assert idx[0] == 0 and np.all(np.diff(idx) >= 0) and np.all(np.diff(idx) <= 1)
         assert np.array_equal(np.diff(idx) > 0, np.diff(keys) > 0), algo
+
+
+def test_large_communicators_compile_quickly():
+    # the reference's recorded traces go up to 1024 ranks (inputs/1024proc); direct schedules must stay cheap there
+    import time
+    t0 = time.time()
+    p = Plan("spreadout", 1024).check()
+    assert len(p.ops()) == 1024 * 1024 and p.ncells == 0
+    assert time.time() - t0 < 30
+    run(Plan("rbruck", 128, r=2).check(), 128, ts=1, seed=1, hi=3)

@@ -87,3 +87,30 @@ def test_noalloc_refuses_requests_beyond_its_limits():
     bufs = (C.c_void_p * P)(*[None] * P)
     assert lib.rbv_alltoallv_noalloc(P, 4, bufs, bufs, _ptr(big), _ptr(z64), _ptr(big), _ptr(z64), None) == -2
     assert lib.rbv_alltoallv_noalloc(0, 4, bufs, bufs, _ptr(big), _ptr(z64), _ptr(big), _ptr(z64), None) == -1
+
+
+def test_noalloc_status_names_the_failure():
+    """A block larger than the receiver's recvcount is refused by the kernel (nothing is written past the slot) and
+    the status query returns the recorded code (4 = truncation), not a blanket error; the next call works again."""
+    from rbruck_alltoallv_b200 import _native
+    lib = _native.cuda_lib()
+    P, ts = 4, 4
+    counts = dist.constant(P, 64)
+    prob = oracle.make_problem(counts, ts, 0, packed=True)
+    send_h = oracle.fill_send(prob, 1)
+    want = oracle.expected_recv(prob, send_h)
+    send = [torch.from_numpy(b).cuda() for b in send_h]
+    recv = [torch.full((len(w),), oracle.CANARY, dtype=torch.uint8, device="cuda") for w in want]
+    sp = (C.c_void_p * P)(*[t.data_ptr() for t in send])
+    rp = (C.c_void_p * P)(*[t.data_ptr() for t in recv])
+    sc = np.ascontiguousarray(prob.counts, dtype=np.int32)
+    rc = np.ascontiguousarray(prob.recvcounts, dtype=np.int32).copy()
+    rc[2, 1] = 10                      # rank 2 expects less from rank 1 than rank 1 sends
+    sd = np.ascontiguousarray(prob.sdispls, dtype=np.int64)
+    rd = np.ascontiguousarray(prob.rdispls, dtype=np.int64)
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.rbv_alltoallv_noalloc(P, ts, sp, rp, _ptr(sc), _ptr(sd), _ptr(rc), _ptr(rd), st) == 0
+    assert lib.rbv_noalloc_status(st) == 4
+    _run_noalloc(lib, prob, send, recv, ts)      # every call clears the control words: the entry point recovers
+    torch.cuda.synchronize()
+    assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None
