@@ -830,6 +830,7 @@ int Context::nvls_bind_and_map(void** self_ptr, void** mc_ptr, size_t* bytes_out
   ap.type = CU_MEM_ALLOCATION_TYPE_PINNED;
   ap.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
   ap.location.id = device_;
+  ap.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;   // the same kind as the multicast object's
   size_t gran = 0;
   RBV_CU(cuMemGetAllocationGranularity(&gran, &ap, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
   const size_t size = own_mc_bytes_;

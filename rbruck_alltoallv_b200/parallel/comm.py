@@ -148,6 +148,8 @@ class Communicator:
         nbytes = max(int(lib.rbv_ctx_meta_bytes(self._ctx)), 4096)
 
         def agree(ok: bool) -> bool:
+            if not ok and os.environ.get("RBV_VERBOSE"):
+                print(f"[rbv nvls, process {self.proc}] " + lib.rbv_last_error().decode(), flush=True)
             flag = torch.tensor([1 if ok else 0], dtype=torch.int64)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self._side)
             return bool(int(flag.item()))
