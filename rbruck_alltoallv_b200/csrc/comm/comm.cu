@@ -45,6 +45,7 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   if (const char* e = std::getenv("RBV_BULK")) bulk_mode_ = std::atoi(e);
   if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_mode_ = std::atoi(e) != 0 ? 1 : 0;
   if (const char* e = std::getenv("RBV_STATIC_OCC")) static_occ_ = std::atoi(e) >= 2 ? 2 : 1;
+  if (const char* e = std::getenv("RBV_SEQ_HINT")) seq_hints_ = std::atoi(e) != 0;
   int st_per_sm = 1;
   RBV_CUDA_THROW(a2av_static_configure(static_occ_, &st_per_sm));
   static_max_ctas_ = sm_count_ * std::max(1, std::min(st_per_sm, 2));
@@ -244,9 +245,27 @@ int Context::alltoallv(const AlgoSpec& spec, int ts, const CallArgs& ca, const C
 int Context::launch(const Prepared& pc, cudaStream_t stream) {
   // cooperative_mode_: 1 always cooperative, 0 never (in-place calls excepted), -1 only for calls that need it
   const bool coop = cooperative_mode_ > 0 || (cooperative_mode_ < 0 && pc.cooperative);
-  cudaError_t e = pc.is_static ? a2av_static_launch(pc.sa, pc.grid, static_occ_, coop, stream)
-                  : pc.eager   ? a2av_eager_launch(pc.ka, pc.grid, coop, stream)
-                               : a2av_launch(pc.ka, pc.grid, coop, stream);
+  // The host passes the call number along (one trip to device memory less before the first byte moves).  A launch
+  // that is being recorded into a CUDA graph must read the number on the device, and after the first such launch
+  // the host's count can no longer be trusted (replays advance the number unseen), so hints stay off from then on.
+  if (seq_hints_) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+      (void)cudaGetLastError();
+      seq_hints_ = false;
+    }
+  }
+  cudaError_t e;
+  if (pc.is_static) {
+    StaticArgs sa = pc.sa;
+    sa.seq_hint = host_seq_; sa.use_seq_hint = seq_hints_ ? 1u : 0u;
+    e = a2av_static_launch(sa, pc.grid, static_occ_, coop, stream);
+  } else {
+    KernelArgs ka = pc.ka;
+    ka.seq_hint = host_seq_; ka.use_seq_hint = seq_hints_ ? 1u : 0u;
+    e = pc.eager ? a2av_eager_launch(ka, pc.grid, coop, stream) : a2av_launch(ka, pc.grid, coop, stream);
+  }
+  if (e == cudaSuccess) host_seq_++;
   if (e != cudaSuccess) {
     last_error_ = std::string("kernel launch failed: ") + cudaGetErrorString(e);
     return RBV_ERR_BAD_ARG;
@@ -567,6 +586,7 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
         RBV_CUDA_THROW(cudaMemcpy(out->owned_items, tab.data(), tab.size() * sizeof(EagerItem), cudaMemcpyHostToDevice));
         ka.items = static_cast<const EagerItem*>(out->owned_items);
         ka.nitems = (unsigned)tab.size();
+        if (tab.size() <= (size_t)kInlineEagerItems) std::memcpy(ka.inl_items, tab.data(), tab.size() * sizeof(EagerItem));
         items = (double)tab.size();
       }
     }
@@ -892,6 +912,7 @@ cudaError_t Context::reset() {
     if (kv.second->d_done) cudaMemset(kv.second->d_done, 0, kv.second->nops * sizeof(unsigned));
   std::memset(host_status_, 0, sizeof(StatusBlock));
   std::memset(host_trace_, 0, sizeof(TraceBlock));
+  host_seq_ = 0;
   return cudaDeviceSynchronize();
 }
 

@@ -188,6 +188,8 @@ class Context {
   TraceBlock* host_trace_dev_ = nullptr;
   const DevPlan* last_plan_ = nullptr;
   double last_plan_build_s_ = 0;   // host time spent compiling the plan of the last prepare() (0: cached)
+  unsigned host_seq_ = 0;          // the call number as the host counts it (every launch advances it once)
+  bool seq_hints_ = true;          // off for good once a launch was recorded into a CUDA graph (or RBV_SEQ_HINT=0)
   int static_max_ctas_ = 1;
   int static_occ_ = 1;             // CTAs per SM the static kernel is built for (RBV_STATIC_OCC=2: the 64-register build)
   int prepare_static(const DevPlan* dp, int type_size, const CallArgs& args, const CallOptions& opt, Prepared* out);

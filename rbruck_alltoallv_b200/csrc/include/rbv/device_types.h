@@ -175,10 +175,18 @@ struct alignas(16) EagerItem {
 };
 static_assert(sizeof(EagerItem) == 32, "two 16-byte loads per item");
 
+constexpr int kInlineEagerItems = 32;   // work items of a small eager call travel in the kernel parameters
+
 struct KernelArgs {
   int P, L, nproc, proc;
   int type_size;
   unsigned flags;
+  // The call number as the host counts it (use_seq_hint != 0), which spares the kernel a trip to device memory
+  // before its first byte moves.  The host counts exactly: every launch advances the number once, whatever becomes
+  // of the call.  Launches recorded into a CUDA graph read the number from CtrlBlock::call_seq instead (their
+  // arguments are frozen), and a context that has seen such a launch stops passing hints for good, because replays
+  // advance the number behind the host's back.  The CTA that advances the number checks the hint against memory.
+  unsigned seq_hint, use_seq_hint;
   int nops;                // ops executed by this process
   int absent_rank;         // fault injection for tests: this local rank never publishes its metadata (-1: none)
   int ncells;
@@ -205,6 +213,7 @@ struct KernelArgs {
   StatusBlock* host_status;  // pinned, mapped: a copy of the final status
   TraceBlock* host_trace;    // pinned, mapped: per-key stamps of a traced call
   InlineMeta inl;
+  EagerItem inl_items[kInlineEagerItems];   // the item table itself when nitems <= kInlineEagerItems (items != null)
 };
 
 constexpr int kInlineItems = 48;   // items of a small static call travel in the kernel parameters
@@ -215,6 +224,7 @@ struct StaticArgs {
   int P, L, nproc, proc;
   unsigned flags;                       // CALL_TRACE
   unsigned nitems;
+  unsigned seq_hint, use_seq_hint;      // as in KernelArgs
   const StaticItem* items;              // issue order; item c is handled by warp c mod (warps in the grid)
   const unsigned long long* expect;     // [L] chunks that land in each local rank's receive buffer per call
   unsigned long long timeout_ns;

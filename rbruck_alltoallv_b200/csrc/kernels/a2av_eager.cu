@@ -125,12 +125,14 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   // next call: CTAs count when the work items are sized in the kernel (thread 0 reads the number for its CTA), warps
   // count when the call brings its item table (every warp reads the number itself).
   const bool pre = a.items != nullptr;
-  unsigned seq_early = 0;
+  const bool hinted = a.use_seq_hint != 0;   // the host passed the call number: nobody reads it from memory
+  unsigned seq_early = a.seq_hint;
+  unsigned cta_rank = 0;     // thread 0, without an item table: CTAs that had read the call number before this one
   if (tid == 0) {
-    seq_early = dev::read_call_seq(my);
+    if (!hinted) seq_early = dev::read_call_seq(my);
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
     if (a.flags & CALL_TRACE) atomicMax(&my->status.trace[5], dev::globaltimer());   // latest CTA start
-    if (!pre && atomicAdd(&my->start_count, 1u) == gridDim.x - 1) dev::advance_call_seq(my, seq_early);
+    if (!pre) cta_rank = atomicAdd(&my->start_count, 1u);   // looked at when the CTA is done
   }
   unsigned seq = 0;
   int parity = 0;
@@ -143,10 +145,10 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   if (pre) {
     unsigned sq = 0;
     if (lane == 0) {
-      sq = (tid == 0) ? seq_early : dev::read_call_seq(my);
+      sq = (tid == 0 || hinted) ? seq_early : dev::read_call_seq(my);
       start_rank = atomicAdd(&my->start_count, 1u);   // the result is looked at after the warp's items
     }
-    seq = __shfl_sync(0xffffffffu, sq, 0);
+    seq = hinted ? a.seq_hint : __shfl_sync(0xffffffffu, sq, 0);
     parity = seq & 1;
     ec.flag = seq + 1u;
     if (blockIdx.x == 0 && tid == 0) my->status.trace[1] = dev::globaltimer();
@@ -179,7 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
     }
     if (t0 == 0 && tid == 0) s_seq = seq_early;
     __syncthreads();
-    if (t0 == 0) { seq = s_seq; parity = seq & 1; ec.flag = seq + 1u; }
+    if (t0 == 0) { seq = hinted ? a.seq_hint : s_seq; parity = seq & 1; ec.flag = seq + 1u; }
     if (tid < 32) {
       unsigned carry = 0;
       if (tid == 0) s_prefix[0] = 0;
@@ -206,11 +208,16 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
       unsigned k;
       Op o;
       if (pre) {
-        // the item brings its op along: one 32-byte fetch, nothing that depends on it but the data itself
-        const uint4* ip = reinterpret_cast<const uint4*>(a.items + c);
+        // the item brings its op along: one 32-byte fetch (none when the table fits the kernel parameters),
+        // nothing that depends on it but the data itself
         union { uint4 q[2]; EagerItem it; } u;
-        u.q[0] = __ldg(ip);
-        u.q[1] = __ldg(ip + 1);
+        if (a.nitems <= (unsigned)kInlineEagerItems) {
+          u.it = a.inl_items[c];
+        } else {
+          const uint4* ip = reinterpret_cast<const uint4*>(a.items + c);
+          u.q[0] = __ldg(ip);
+          u.q[1] = __ldg(ip + 1);
+        }
         o = u.it.op;
         k = u.it.k;
         oi = (int)u.it.index;
@@ -353,11 +360,11 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   // No end-of-call pass.  With an item table the warp that completed the start count advances the call number now
   // (its own items are done, so the atomic's result has long arrived); it also reports a communicator that was
   // told to stop.  (The rendezvous protocol keeps no per-call counter targets here, so the protocols mix freely.)
-  if (pre && lane == 0 && start_rank == nwarps - 1) {
-    dev::advance_call_seq(my, seq);
+  if ((pre && lane == 0 && start_rank == nwarps - 1) || (!pre && tid == 0 && cta_rank == gridDim.x - 1)) {
+    if (!hinted) dev::advance_call_seq(my, seq);
+    else if (!dev::advance_call_seq_checked(my, seq)) eager_error(a, RBV_ERR_BAD_ARG, 0, (int)seq, -1);
     if (dev::ld_relaxed_sys(&my->abort_flag)) eager_error(a, RBV_ERR_ABORTED, 0, 0, 0);
   }
-  if (!pre && blockIdx.x == 0 && tid == 0 && dev::ld_relaxed_sys(&my->abort_flag)) eager_error(a, RBV_ERR_ABORTED, 0, 0, 0);
   if (trace) {
     __syncthreads();
     if (tid == 0) {

@@ -194,15 +194,15 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
   if (bulk) dev::bulk_pipe_init(bp, bulk_region, warp, (int)warps_per_cta, lane, a2av_bulk_stages(P));   // published by the barrier below
 
   if (tid < kMaxRanks) s_arrived[tid] = 0;
+  // The CTA that completes the start count advances the call number for the next call (checked at the end).
+  unsigned start_rank = 0;
   if (tid == 0) {
-    const unsigned sq = dev::read_call_seq(my);
-    s_seq = sq;
+    if (!a.use_seq_hint) s_seq = dev::read_call_seq(my);
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
-    // the last CTA to read the call number advances it for the next call
-    if (atomicAdd(&my->start_count, 1u) == gridDim.x - 1) dev::advance_call_seq(my, sq);
+    start_rank = atomicAdd(&my->start_count, 1u);
   }
   __syncthreads();
-  const unsigned seq = s_seq;
+  const unsigned seq = a.use_seq_hint ? a.seq_hint : s_seq;
   const int parity = seq & 1;
 
   // ---- in-place calls: move the send data out of recvbuf before anyone may write into it ----
@@ -430,6 +430,10 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_kernel(const __grid_constant
     if (blockIdx.x == 0 && tid == 0) my->status.trace[7] = dev::globaltimer();
   }
 
+  if (tid == 0 && start_rank == gridDim.x - 1) {
+    if (!a.use_seq_hint) dev::advance_call_seq(my, seq);
+    else if (!dev::advance_call_seq_checked(my, seq)) report_error(a, RBV_ERR_BAD_ARG, 0, (int)seq, -1);
+  }
   // ---- (3) completion ----
   if (blockIdx.x == 0) {
     if (tid == 0) my->status.trace[3] = dev::globaltimer();

@@ -69,16 +69,17 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
       for (unsigned off = lane * 128u; off < f.len; off += 32u * 128u)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(f.src + off));
   }
+  // The CTA that completes the start count advances the call number for the next call; the count's result is only
+  // looked at when the CTA is done, so the atomic's round trip is off the path of the data.
+  unsigned start_rank = 0;
   if (tid == 0) {
-    const unsigned sq = dev::read_call_seq(my);
-    s_seq = sq;
+    if (!a.use_seq_hint) s_seq = dev::read_call_seq(my);
     if (blockIdx.x == 0) my->status.trace[0] = dev::globaltimer();
-    // the last CTA to read the call number advances it for the next call
-    if (atomicAdd(&my->start_count, 1u) == gridDim.x - 1) dev::advance_call_seq(my, sq);
+    start_rank = atomicAdd(&my->start_count, 1u);
   }
   for (int i = tid; i < a.P; i += blockDim.x) s_arrived[i] = 0;
   __syncthreads();
-  const unsigned seq = s_seq;
+  const unsigned seq = a.use_seq_hint ? a.seq_hint : s_seq;
   const int parity = seq & 1;
   const unsigned flagv = seq + 1u;
   if (multi && blockIdx.x == 0 && tid < a.nproc && tid != a.proc)
@@ -137,6 +138,10 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   }
   __syncwarp();
   __syncthreads();
+  if (tid == 0 && start_rank == gridDim.x - 1) {
+    if (!a.use_seq_hint) dev::advance_call_seq(my, seq);
+    else if (!dev::advance_call_seq_checked(my, seq)) static_error(a, RBV_ERR_BAD_ARG, 0, (int)seq, -1);
+  }
   // report this CTA's deliveries: the barrier orders every warp's stores before the fence, which publishes them
   if (blockIdx.x == 0 && tid == 0) my->status.trace[5] = dev::globaltimer();
   for (int d = tid; d < a.P; d += blockDim.x) {

@@ -251,6 +251,13 @@ __device__ __forceinline__ void advance_call_seq(CtrlBlock* c, unsigned seq) {
   c->start_count = 0;
   c->call_seq = seq + 1u;
 }
+// The same when the call number came from the host: true if memory agrees with it (it must, unless launches that
+// the host did not count, such as graph replays, ran on this context).
+__device__ __forceinline__ bool advance_call_seq_checked(CtrlBlock* c, unsigned seq) {
+  const bool ok = __ldcg(&c->call_seq) == seq;
+  advance_call_seq(c, seq);
+  return ok;
+}
 
 // First failure of a call: kept in the control block (first one wins) and handed to the host at once, so that no
 // end-of-kernel pass is needed to publish it.  The abort flag makes every other wait on this process leave, and the

@@ -492,3 +492,51 @@ def test_more_than_64_ranks_run_as_persistent_calls():
                                type_size=4)
         finally:
             comm.close()
+
+
+def test_persistent_calls_replay_from_a_cuda_graph():
+    """The call number lives in device memory, so a recorded launch can be replayed.  Direct launches get the number
+    from the host as a shortcut; the first recorded launch switches that off for the context, because replays advance
+    the number without the host seeing them.  Direct launches, replays and direct launches again must all deliver."""
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    P, ts = 8, 4
+    comm = Communicator(nranks=P, heap_bytes=64 << 20, arena_bytes=2 << 20)
+    try:
+        counts = dist.uniform(P, 500, seed=12)
+        prob = oracle.make_problem(counts, ts, 12, packed=False)
+        send_h = oracle.fill_send(prob, 12)
+        want = oracle.expected_recv(prob, send_h)
+        send = [torch.from_numpy(b).cuda() for b in send_h]
+        recv = [comm.symm_empty(len(w), torch.uint8) for w in want]
+        args = (send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls)
+        calls = [comm.prepare(*args, algo="spreadout", type_size=ts),
+                 comm.prepare(*args, algo="spreadout", type_size=ts, eager_max_bytes=500 * ts)]
+        assert [c.kind for c in calls] == ["static", "eager"]
+
+        def verify(what):
+            comm.check()
+            assert oracle.first_mismatch([t.cpu().numpy() for t in recv], want) is None, what
+            for t in recv:
+                t.fill_(oracle.CANARY)
+
+        for t in recv:
+            t.fill_(oracle.CANARY)
+        for c in calls:                       # direct launches with the host's call number
+            c.launch()
+            verify("direct " + c.kind)
+        torch.cuda.synchronize()
+        graphs = []
+        for c in calls:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                c.launch()
+            graphs.append(g)
+        for rep in range(3):
+            for g, c in zip(graphs, calls):
+                g.replay()
+                verify(f"replay {rep} " + c.kind)
+        for c in calls:                       # and direct launches afterwards read the number on the device
+            c.launch()
+            verify("direct after replays " + c.kind)
+    finally:
+        comm.close()
