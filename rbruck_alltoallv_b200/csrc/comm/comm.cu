@@ -586,7 +586,7 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
         RBV_CUDA_THROW(cudaMemcpy(out->owned_items, tab.data(), tab.size() * sizeof(EagerItem), cudaMemcpyHostToDevice));
         ka.items = static_cast<const EagerItem*>(out->owned_items);
         ka.nitems = (unsigned)tab.size();
-        if (tab.size() <= (size_t)kInlineEagerItems) std::memcpy(ka.inl_items, tab.data(), tab.size() * sizeof(EagerItem));
+        std::memcpy(ka.inl_items, tab.data(), std::min(tab.size(), (size_t)kInlineEagerItems) * sizeof(EagerItem));
         items = (double)tab.size();
       }
     }
@@ -765,7 +765,7 @@ int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const
   for (int q = 0; q < nproc_; q++) sa.heap[q] = peer_[q];
   sa.host_status = host_status_dev_;
   sa.host_trace = host_trace_dev_;
-  if (items.size() <= (size_t)kInlineItems) std::memcpy(sa.inl, items.data(), items.size() * sizeof(StaticItem));
+  std::memcpy(sa.inl, items.data(), std::min(items.size(), (size_t)kInlineItems) * sizeof(StaticItem));
   const int warps_per_cta = kThreads / 32;
   int grid = opt.grid > 0 ? opt.grid : (int)((items.size() + warps_per_cta - 1) / warps_per_cta);
   out->grid = std::max(1, std::min(grid, static_max_ctas_));

@@ -175,7 +175,8 @@ struct alignas(16) EagerItem {
 };
 static_assert(sizeof(EagerItem) == 32, "two 16-byte loads per item");
 
-constexpr int kInlineEagerItems = 32;   // work items of a small eager call travel in the kernel parameters
+constexpr int kInlineEagerItems = 128;  // the first work items of an eager call with an item table travel in the
+                                        // kernel parameters (all of them for a small call)
 
 struct KernelArgs {
   int P, L, nproc, proc;
@@ -213,10 +214,10 @@ struct KernelArgs {
   StatusBlock* host_status;  // pinned, mapped: a copy of the final status
   TraceBlock* host_trace;    // pinned, mapped: per-key stamps of a traced call
   InlineMeta inl;
-  EagerItem inl_items[kInlineEagerItems];   // the item table itself when nitems <= kInlineEagerItems (items != null)
+  EagerItem inl_items[kInlineEagerItems];   // the first items of the table behind `items` (when there is one)
 };
 
-constexpr int kInlineItems = 48;   // items of a small static call travel in the kernel parameters
+constexpr int kInlineItems = 128;  // the first items of a static call travel in the kernel parameters
 
 // Arguments of the static rendezvous kernel (a2av_static.cu): a persistent call whose counts were all known on
 // the host.  Everything that depends on counts sits in the table behind `items`.
@@ -232,8 +233,8 @@ struct StaticArgs {
   char* heap[kMaxProcs];
   StatusBlock* host_status;
   TraceBlock* host_trace;               // pinned copy of the per-key stamps (written when CALL_TRACE is set)
-  // A call of at most kInlineItems items carries them here: the first fetch of a small call then costs no trip to
-  // device memory (after an L2 flush that trip is a DRAM access on the critical path).
+  // The first kInlineItems items of the table: a warp whose first item is among them starts without a trip to
+  // device memory (after an L2 flush that trip is a DRAM access on the critical path of a small call).
   StaticItem inl[kInlineItems];
 };
 

@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
         // the item brings its op along: one 32-byte fetch (none when the table fits the kernel parameters),
         // nothing that depends on it but the data itself
         union { uint4 q[2]; EagerItem it; } u;
-        if (a.nitems <= (unsigned)kInlineEagerItems) {
+        if (c < (unsigned)kInlineEagerItems) {
           u.it = a.inl_items[c];
         } else {
           const uint4* ip = reinterpret_cast<const uint4*>(a.items + c);

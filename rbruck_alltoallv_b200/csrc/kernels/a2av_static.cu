@@ -60,10 +60,9 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   TraceBlock* tb = reinterpret_cast<TraceBlock*>(a.heap[a.proc] + a.lay.trace_off);
   dev::WaitCfg wc{&my->abort_flag, a.timeout_ns};
 
-  // Small calls carry their items in the kernel parameters: the source of a warp's first item is requested from
-  // memory before the call number has even arrived (the two trips to DRAM overlap instead of following each other).
-  const bool inl = a.nitems <= (unsigned)kInlineItems;
-  if (inl && gwarp < a.nitems) {
+  // The first items travel in the kernel parameters: the source of such an item is requested from memory before
+  // anything else happens (with a call number that has to be read from memory, the two trips to DRAM overlap).
+  if (gwarp < a.nitems && gwarp < (unsigned)kInlineItems) {
     const StaticItem& f = a.inl[gwarp];
     if (!(f.flags & ITEM_SRC_STAGE))
       for (unsigned off = lane * 128u; off < f.len; off += 32u * 128u)
@@ -92,7 +91,7 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   unsigned ready = 1u << a.proc;   // processes known to have entered this call
   for (unsigned c = gwarp; c < a.nitems; c += nwarps) {
     union { uint4 q[2]; StaticItem it; } u;
-    if (inl) {
+    if (c < (unsigned)kInlineItems) {
       u.it = a.inl[c];
     } else {
       const uint4* ip = reinterpret_cast<const uint4*>(a.items + c);

@@ -2,7 +2,11 @@
 126 MB L2, at most a few GB on the device, a handful of launches).
 
     python -m rbruck_alltoallv_b200.utils.profile_case a2av        # spread-out alltoallv, 8 ranks on one GPU, 4 MB blocks
-    python -m rbruck_alltoallv_b200.utils.profile_case a2av_bruck  # radix-2 two-phase Bruck, same sizes
+                                                                   # (persistent call: the static kernel)
+    python -m rbruck_alltoallv_b200.utils.profile_case a2av_bruck  # radix-2 two-phase Bruck, same sizes (static kernel,
+                                                                   # chunk-granular forwarding)
+    python -m rbruck_alltoallv_b200.utils.profile_case a2av_dynamic  # the same spread-out exchange through the kernel
+                                                                   # that exchanges metadata itself
     python -m rbruck_alltoallv_b200.utils.profile_case a2av_small  # Zipf blocks <= 64 KB (latency regime)
     python -m rbruck_alltoallv_b200.utils.profile_case gemm1       # grouped SwiGLU GEMM, 2 experts x 2048 rows, 4096 -> 2 x 14336
     python -m rbruck_alltoallv_b200.utils.profile_case gemm2       # grouped down GEMM, 14336 -> 4096
@@ -104,6 +108,8 @@ def main() -> int:
         _a2av("spreadout")
     elif case == "a2av_bruck":
         _a2av("rbruck", r=2)
+    elif case == "a2av_dynamic":
+        _a2av("spreadout", static=False)
     elif case == "a2av_small":
         _a2av("rbruck", small=True, r=2)
     elif case == "gemm1":
