@@ -92,5 +92,8 @@ def declare_moe(lib):
     lib.rbv_quantize_rows_fp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_moe_route.argtypes = [vp, i, i, vp, vp, vp, vp]
     lib.rbv_moe_layout.argtypes = [vp, i, i, i, vp, vp, vp, vp, vp, vp]
+    lib.rbv_moe_layout_streamed.argtypes = [vp, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, i, vp, vp]
+    lib.rbv_moe_dispatch_streamed.argtypes = [vp, vp, i, i, vp, vp, vp, vp, vp, ull, ull, ll, i, vp, vp]
+    lib.rbv_grouped_gemm_bf16_gated.argtypes = [vp, ll, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp, vp, vp, C.c_double]
     lib.rbv_moe_dispatch.argtypes = [vp, vp, i, i, vp, vp, vp, vp, ull, ll, i, vp, vp]
     lib.rbv_moe_combine.argtypes = [vp, vp, i, i, vp, vp, vp, ull, i, vp, vp]

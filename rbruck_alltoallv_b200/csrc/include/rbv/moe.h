@@ -25,6 +25,14 @@ int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void* B, void* 
                           const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
                           int max_ctas, void* cuda_stream);
 
+/* The same with a gated start per group: the loader touches the rows of group g only once ready[g] >= ready_target[g]
+ * (device uint64 arrays; the counters are bumped by whoever delivers the rows, e.g. rbv_moe_dispatch_streamed running
+ * at the same time on this and on other GPUs).  The wait is bounded by timeout_ms (0: 2 s). */
+int rbv_grouped_gemm_bf16_gated(const void* A, long long a_rows, const void* B, void* C, const int* group_start,
+                                const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
+                                int max_ctas, void* cuda_stream, const unsigned long long* ready,
+                                const unsigned long long* ready_target, double timeout_ms);
+
 /* Block-scaled fp8 (e4m3) variant.  A: [a_rows, K] bytes with one fp32 scale per row and 128-wide K block, stored
  * transposed as a_scale_t [K / 128][a_rows]; B: [G, N, K] bytes with one scale per 128 x 128 block, b_scale
  * [G][N / 128][K / 128].  N % 128 == 0, K % 128 == 0.  Output bf16, epilogues as above. */
@@ -53,6 +61,20 @@ int rbv_moe_layout(const int* hist_all, int P, int E, int me, int* dst_base, int
 int rbv_moe_dispatch(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
                      int* cursor, int* slot, unsigned long long xrecv_off, long long recv_capacity_rows,
                      int E, int* error_flag, void* cuda_stream);
+
+/* Streamed dispatch (overlaps with the first expert GEMM).  rbv_moe_layout_streamed is rbv_moe_layout plus: loc_off [E]
+ * (where this rank's rows for expert e start in an expert-major ordering of its routed rows), order [2 T] (that
+ * ordering), and ready_target [E / P] += rows each local expert receives in this call (a running total kept across
+ * calls; zero it once).  rbv_moe_dispatch_streamed walks `order`, stores every row into its place on the owner and
+ * adds one to the owner's counter ready[e_local] (uint64 [E / P] at byte offset ready_off of every heap, zeroed once,
+ * never reset).  It does not wait for anybody: the consumer is rbv_grouped_gemm_bf16_gated(ready, ready_target). */
+int rbv_moe_layout_streamed(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start,
+                            int* group_rows, int* cursor, int* totals, int* loc_off, unsigned long long* ready_target,
+                            const int* topk_idx, int T, int* order, void* cuda_stream);
+int rbv_moe_dispatch_streamed(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                              const int* loc_off, const int* order, int* slot, unsigned long long xrecv_off,
+                              unsigned long long ready_off, long long recv_capacity_rows, int E, int* error_flag,
+                              void* cuda_stream);
 
 /* Combine: out[t] = sum_k w[t,k] * Y_owner(k)[slot[t,k]], rows pulled from the owners' `y_off` buffers over
  * NVLink after a bounded cross-GPU barrier ("all expert outputs are complete"). */

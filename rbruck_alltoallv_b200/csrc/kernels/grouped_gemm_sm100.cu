@@ -48,9 +48,36 @@ struct GemmParams {
   void* C;                  // bf16
   int* error;               // set to non-zero when a wait ran out
   int epilogue;             // 0: C = bf16(acc); 1: C[:, j] = bf16(silu(acc[:, 2j]) * acc[:, 2j+1])
+  // Gated start (null: none): the rows of group g may be loaded once ready[g] >= ready_target[g].  The counters are
+  // bumped by the kernels that deliver the rows, possibly from other GPUs, while this kernel is already running.
+  const unsigned long long* ready;
+  const unsigned long long* ready_target;
+  unsigned long long timeout_ns;
 };
 
 struct Tile { int g, m0, n0, rows_left; bool valid; };
+
+// Waits (bounded) until all rows of group g have been delivered.  The deliveries are generic-proxy stores made
+// visible by a fence and a relaxed reduction at system scope; the loads that follow go through the TMA unit, hence
+// the proxy fence after the acquire.
+__device__ bool wait_group_ready(const GemmParams& p, int g, volatile int* abort_flag) {
+  const unsigned long long target = p.ready_target[g];
+  unsigned long long t0 = 0;
+  for (unsigned it = 0;; it++) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p.ready + g) : "memory");
+    if (v >= target) break;
+    if ((it & 15u) == 15u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (!t0) t0 = now;
+      if (*abort_flag || now - t0 > p.timeout_ns) return false;
+      __nanosleep(64);
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
 
 // Tile t of the static schedule: groups in order; inside a group n-major, m fastest.
 __device__ __forceinline__ Tile tile_of(const GemmParams& p, int t, const int* s_rows, const int* s_start) {
@@ -109,9 +136,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       tma_prefetch_desc(&tma_b);
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      int ready_g = -1;   // groups up to this one are known to be complete
       for (int t = blockIdx.x; ok; t += gridDim.x) {
         const Tile tl = tile_of(p, t, s_rows, s_start);
         if (!tl.valid) break;
+        if (p.ready && tl.g > ready_g) {
+          if (!wait_group_ready(p, tl.g, abort_flag)) { ok = false; break; }
+          ready_g = tl.g;
+        }
         for (int kb = 0; kb < num_kb; kb++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = tiles + (size_t)stage * STAGE_BYTES;
@@ -254,9 +286,24 @@ bool make_map(CUtensorMap* m, const void* base, unsigned long long rows, unsigne
 }  // namespace
 }  // namespace rbv
 
+extern "C" int rbv_grouped_gemm_bf16_gated(const void* A, long long a_rows, const void* B, void* C,
+                                           const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
+                                           int epilogue, int* error_flag, int max_ctas, void* cuda_stream,
+                                           const unsigned long long* ready, const unsigned long long* ready_target,
+                                           double timeout_ms);
+
 extern "C" int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void* B, void* C, const int* group_start,
                                      const int* group_rows, int G, int N, int K, int ldc, int epilogue,
                                      int* error_flag, int max_ctas, void* cuda_stream) {
+  return rbv_grouped_gemm_bf16_gated(A, a_rows, B, C, group_start, group_rows, G, N, K, ldc, epilogue, error_flag,
+                                     max_ctas, cuda_stream, nullptr, nullptr, 0.0);
+}
+
+extern "C" int rbv_grouped_gemm_bf16_gated(const void* A, long long a_rows, const void* B, void* C,
+                                           const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
+                                           int epilogue, int* error_flag, int max_ctas, void* cuda_stream,
+                                           const unsigned long long* ready, const unsigned long long* ready_target,
+                                           double timeout_ms) {
   using namespace rbv;
   if (G < 1 || G > kMoeMaxGroups || N % BN || K % BK || a_rows < 1 || (ldc % 8)) return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
@@ -274,6 +321,8 @@ extern "C" int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void
   GemmParams p;
   p.group_start = group_start; p.group_rows = group_rows; p.G = G; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
   p.error = error_flag; p.epilogue = epilogue;
+  p.ready = ready; p.ready_target = ready ? ready_target : nullptr;
+  p.timeout_ns = (unsigned long long)((timeout_ms > 0 ? timeout_ms : 2000.0) * 1e6);
   int grid = max_ctas;
   if (grid <= 0) {
     int dev = 0;

@@ -78,8 +78,11 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 // Layout: one CTA.  Receive buffer of a rank = its local experts in order; inside an expert the
 // rows of source rank 0, then 1, ...
 // ---------------------------------------------------------------------------------------------
+// loc_off (optional): first index of this rank's rows for expert e in an expert-major ordering of its routed rows;
+// ready_target (optional): running totals of rows each local expert has been promised over all calls so far.
 __global__ void moe_layout_kernel(const int* __restrict__ hist_all, int P, int E, int me, int* dst_base,
-                                  int* group_start, int* group_rows, int* cursor, int* totals) {
+                                  int* group_start, int* group_rows, int* cursor, int* totals, int* loc_off,
+                                  unsigned long long* ready_target) {
   __shared__ int s_tot[kMoeMaxExperts];      // rows of expert e over all sources
   __shared__ int s_before[kMoeMaxExperts];   // rows of expert e from sources < me
   const int El = E / P;
@@ -99,7 +102,15 @@ __global__ void moe_layout_kernel(const int* __restrict__ hist_all, int P, int E
     int base = 0;
     for (int e2 = owner * El; e2 < e; e2++) base += s_tot[e2];
     dst_base[e] = base + s_before[e];
-    if (owner == me) { group_start[e - owner * El] = base; group_rows[e - owner * El] = s_tot[e]; }
+    if (owner == me) {
+      group_start[e - owner * El] = base; group_rows[e - owner * El] = s_tot[e];
+      if (ready_target) ready_target[e - owner * El] += (unsigned long long)s_tot[e];
+    }
+    if (loc_off) {
+      int off = 0;
+      for (int e2 = 0; e2 < e; e2++) off += hist_all[me * E + e2];
+      loc_off[e] = off;
+    }
   }
   if (threadIdx.x == 0) {
     int recv = 0, sent = 0;
@@ -264,6 +275,61 @@ __global__ void __launch_bounds__(kMoeThreads) moe_combine_kernel(const __grid_c
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streamed dispatch.  The routed rows are visited expert by expert (`order` lists them expert-major), every GPU
+// therefore fills expert 0 of every owner first, then expert 1, ...; each landed row bumps a counter of its expert
+// on the owner, and the grouped GEMM's loader starts an expert's tiles as soon as the counter says that all its
+// rows are there (rbv_grouped_gemm_bf16_gated).  The first expert is complete after about one El-th of the
+// dispatch, and the GEMM of an expert takes far longer than its dispatch, so all but the head of the dispatch
+// disappears behind the GEMM.  No barrier at the end: nothing but the counters says when data is usable.
+// ---------------------------------------------------------------------------------------------
+__global__ void moe_order_kernel(const int* __restrict__ topk_idx, int n_rows, const int* __restrict__ loc_off,
+                                 int* __restrict__ cursor, int* __restrict__ order) {
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += gridDim.x * blockDim.x) {
+    const int e = topk_idx[r];
+    order[loc_off[e] + atomicAdd(&cursor[e], 1)] = r;
+  }
+}
+
+struct StreamedArgs {
+  MoeComm comm;
+  const char* x;
+  int T, H, E, El;
+  const int* topk_idx;
+  const int* dst_base;
+  const int* loc_off;
+  const int* order;
+  int* slot;
+  unsigned long long xrecv_off, ready_off;
+  long long capacity_rows;
+};
+
+__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_streamed_kernel(const __grid_constant__ StreamedArgs a) {
+  const MoeComm& c = a.comm;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const size_t row_bytes = (size_t)a.H * 2;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < 2 * a.T; i += warps) {
+    const int r = a.order[i];
+    const int e = a.topk_idx[r];
+    const int pos = a.dst_base[e] + (i - a.loc_off[e]);
+    const int owner = e / a.El;
+    if (lane == 0) a.slot[r] = pos;
+    if (pos < a.capacity_rows)
+      dev::group_copy(c.heap[owner] + a.xrecv_off + (size_t)pos * row_bytes, a.x + (size_t)(r >> 1) * row_bytes, row_bytes,
+                      lane, 32);
+    else if (lane == 0) moe_fail(c, 4, e);
+    __syncwarp();
+    // the row counts as landed once its stores are visible on the owner (a row that did not fit is counted too,
+    // so that the consumer's target is met and the error flag, not a time-out, tells the story)
+    if (lane == 0) {
+      const bool far = owner != c.proc;
+      dev::fence_acq_rel(far);
+      dev::red_relaxed_add(reinterpret_cast<unsigned long long*>(c.heap[owner] + a.ready_off) + (e - owner * a.El), 1ull, far);
+    }
+  }
+}
+
 MoeComm make_comm(rbv_ctx_t ctx, int* error) {
   MoeComm m;
   const Context& c = *ctx->c;
@@ -300,7 +366,20 @@ int rbv_moe_layout(const int* hist_all, int P, int E, int me, int* dst_base, int
                    int* cursor, int* totals, void* stream) {
   if (E > kMoeMaxExperts || E % P) return (int)cudaErrorInvalidValue;
   moe_layout_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(hist_all, P, E, me, dst_base, group_start,
-                                                                        group_rows, cursor, totals);
+                                                                        group_rows, cursor, totals, nullptr, nullptr);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_layout_streamed(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start,
+                            int* group_rows, int* cursor, int* totals, int* loc_off, unsigned long long* ready_target,
+                            const int* topk_idx, int T, int* order, void* stream) {
+  if (E > kMoeMaxExperts || E % P) return (int)cudaErrorInvalidValue;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  moe_layout_kernel<<<1, 256, 0, st>>>(hist_all, P, E, me, dst_base, group_start, group_rows, cursor, totals, loc_off,
+                                       ready_target);
+  int grid = (2 * T + 255) / 256;
+  grid = grid < 1 ? 1 : (grid > 592 ? 592 : grid);
+  moe_order_kernel<<<grid, 256, 0, st>>>(topk_idx, 2 * T, loc_off, cursor, order);
   return (int)cudaGetLastError();
 }
 
@@ -324,6 +403,34 @@ int rbv_moe_dispatch(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk
   const int cap = c.sm_count() * 2;
   grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
   moe_dispatch_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_dispatch_streamed(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                              const int* loc_off, const int* order, int* slot, unsigned long long xrecv_off,
+                              unsigned long long ready_off, long long recv_capacity_rows, int E, int* error_flag,
+                              void* stream) {
+  const Context& c = *ctx->c;
+  if (c.L() != 1 || E % c.P() || (H % 8)) return (int)cudaErrorInvalidValue;
+  StreamedArgs a;
+  a.comm = make_comm(ctx, error_flag);
+  a.x = static_cast<const char*>(x);
+  a.T = T; a.H = H; a.E = E; a.El = E / c.P();
+  a.topk_idx = topk_idx; a.dst_base = dst_base; a.loc_off = loc_off; a.order = order; a.slot = slot;
+  a.xrecv_off = xrecv_off; a.ready_off = ready_off; a.capacity_rows = recv_capacity_rows;
+  // One CTA per SM: the grouped GEMM that consumes the rows runs at the same time and needs its share of every SM.
+  // That kernel configures its SMs for the largest shared memory; an SM takes CTAs of two kernels only under one
+  // configuration, so this kernel asks for the same one although it uses no shared memory itself.
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(moe_dispatch_streamed_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    configured = true;
+  }
+  const int warps_per_cta = kMoeThreads / 32;
+  int grid = (2 * T + warps_per_cta - 1) / warps_per_cta;
+  grid = grid < 1 ? 1 : (grid > c.sm_count() ? c.sm_count() : grid);
+  moe_dispatch_streamed_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return (int)cudaGetLastError();
 }
 

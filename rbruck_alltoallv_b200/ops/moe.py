@@ -8,6 +8,7 @@ all-to-all count matrices under ``inputs/``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import numpy as np
@@ -22,11 +23,14 @@ def _p(t: Optional[torch.Tensor]):
 
 def grouped_gemm(A: torch.Tensor, B: torch.Tensor, group_start: torch.Tensor, group_rows: torch.Tensor,
                  out: Optional[torch.Tensor] = None, swiglu: bool = False, error: Optional[torch.Tensor] = None,
-                 max_ctas: int = 0) -> torch.Tensor:
+                 max_ctas: int = 0, ready: Optional[torch.Tensor] = None, ready_target: Optional[torch.Tensor] = None,
+                 timeout_ms: float = 0.0) -> torch.Tensor:
     """``out[rows of g] = epi(A[rows of g] @ B[g].T)`` with bf16 operands and fp32 accumulation.
 
     ``A`` [M, K], ``B`` [G, N, K], ``group_start`` / ``group_rows`` int32 CUDA tensors [G].  With ``swiglu``
-    the rows of ``B[g]`` interleave gate and up projections and ``out`` is [M, N // 2]."""
+    the rows of ``B[g]`` interleave gate and up projections and ``out`` is [M, N // 2].  With ``ready`` /
+    ``ready_target`` (int64 CUDA tensors [G]) the rows of group g are loaded only once ``ready[g] >= ready_target[g]``:
+    the kernel may be launched while the rows are still being delivered."""
     lib = _native.cuda_lib()
     assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
     G, N, K = B.shape
@@ -38,8 +42,9 @@ def grouped_gemm(A: torch.Tensor, B: torch.Tensor, group_start: torch.Tensor, gr
     if error is None:
         error = torch.zeros(1, dtype=torch.int32, device=A.device)
     st = torch.cuda.current_stream(A.device).cuda_stream
-    rc = lib.rbv_grouped_gemm_bf16(_p(A), M, _p(B), _p(out), _p(group_start), _p(group_rows), G, N, K,
-                                   out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas), C.c_void_p(st))
+    rc = lib.rbv_grouped_gemm_bf16_gated(_p(A), M, _p(B), _p(out), _p(group_start), _p(group_rows), G, N, K,
+                                         out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas), C.c_void_p(st),
+                                         _p(ready), _p(ready_target), float(timeout_ms))
     if rc:
         raise RuntimeError(f"grouped GEMM launch failed (CUDA error {rc})")
     return out
@@ -117,7 +122,7 @@ class MoEExpertParallel:
     """One MoE FFN layer sharded by experts over the ranks of a communicator (one rank per GPU)."""
 
     def __init__(self, comm, num_experts: int, hidden: int, inter: int, tokens: int, capacity_factor: float = 2.0,
-                 seed: int = 0, init_std: float = 0.02, fp8: bool = False):
+                 seed: int = 0, init_std: float = 0.02, fp8: bool = False, overlap: Optional[bool] = None):
         if comm.L != 1:
             raise ValueError("the MoE path needs one rank per process")
         if num_experts % comm.P:
@@ -152,10 +157,25 @@ class MoEExpertParallel:
         self.group_rows = torch.zeros(self.El, dtype=i32, device=dev)
         self.totals = torch.zeros(2, dtype=i32, device=dev)
         self.error = torch.zeros(4, dtype=i32, device=dev)
+        # Streamed dispatch (bf16 path): rows travel expert by expert, every landed row bumps its expert's counter on
+        # the owner, and the first grouped GEMM, launched on a second stream next to the dispatch, starts an expert as
+        # soon as its rows are complete.  ``overlap=False`` (or RBV_MOE_OVERLAP=0) keeps dispatch and GEMM back to back.
+        if overlap is None:
+            overlap = os.environ.get("RBV_MOE_OVERLAP", "1") != "0"
+        self.overlap = bool(overlap) and not self.fp8
+        self.ready = comm.symm_zeros(max(self.El, 2), torch.int64)          # bumped by every GPU, never reset
+        self.ready_target = torch.zeros(max(self.El, 2), dtype=torch.int64, device=dev)
+        self.loc_off = torch.zeros(self.E, dtype=i32, device=dev)
+        self.order = torch.zeros(2 * tokens, dtype=i32, device=dev)
+        self._side = torch.cuda.Stream(device=dev)
+        self._ev_layout, self._ev_gemm1 = torch.cuda.Event(), torch.cuda.Event()
         heap0 = self.lib.rbv_ctx_heap(comm._ctx, comm.proc)
         self.xrecv_off = self.xrecv.data_ptr() - heap0
         self.y_off = self.y.data_ptr() - heap0
-        comm.require_same_offsets(self.xrecv_off, self.y_off)
+        self.ready_off = self.ready.data_ptr() - heap0
+        comm.require_same_offsets(self.xrecv_off, self.y_off, self.ready_off)
+        torch.cuda.synchronize(dev)
+        comm.host_barrier()          # every rank's counters are zero before anybody's first dispatch
         # the histogram all-gather: every rank sends the same E counters to every rank
         cnt = np.full((1, self.P), self.E, dtype=np.int32)
         self._gather = comm.prepare(self.hist, self.hist_all.view(-1), cnt, np.zeros((1, self.P), dtype=np.int64), cnt,
@@ -177,6 +197,8 @@ class MoEExpertParallel:
         self._check(lib.rbv_moe_route(_p(logits), T, self.E, _p(self.topk_idx), _p(self.topk_w), _p(self.hist), st),
                     "router")
         self._gather.launch()
+        if self.overlap:
+            return self._forward_streamed(x, out, st)
         self._check(lib.rbv_moe_layout(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
                                        _p(self.group_start), _p(self.group_rows), _p(self.cursor), _p(self.totals),
                                        st), "layout")
@@ -196,6 +218,31 @@ class MoEExpertParallel:
                          error=self.error[1:2])
             grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False,
                          error=self.error[2:3])
+        self._check(lib.rbv_moe_combine(ctx, _p(out), T, H, _p(self.topk_idx), _p(self.topk_w), _p(self.slot),
+                                        self.y_off, self.E, _p(self.error[3:4]), st), "combine")
+        return out
+
+    def _forward_streamed(self, x, out, st):
+        lib, ctx, T, H = self.lib, self.comm._ctx, self.T, self.H
+        main = torch.cuda.current_stream(self.dev)
+        self._check(lib.rbv_moe_layout_streamed(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
+                                                _p(self.group_start), _p(self.group_rows), _p(self.cursor),
+                                                _p(self.totals), _p(self.loc_off), _p(self.ready_target),
+                                                _p(self.topk_idx), T, _p(self.order), st), "layout")
+        self._ev_layout.record(main)
+        # The dispatch goes first, so that its CTAs are in place (or done) when the GEMM's arrive: a GEMM that filled
+        # the GPU before the dispatch got in would wait for rows that nobody is there to send.
+        self._check(lib.rbv_moe_dispatch_streamed(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base),
+                                                  _p(self.loc_off), _p(self.order), _p(self.slot), self.xrecv_off,
+                                                  self.ready_off, self.cap, self.E, _p(self.error[0:1]), st), "dispatch")
+        # the first GEMM runs next to it, on its own stream, and takes each expert when its counter is complete
+        with torch.cuda.stream(self._side):
+            self._side.wait_event(self._ev_layout)
+            grouped_gemm(self.xrecv, self.w13, self.group_start, self.group_rows, out=self.h, swiglu=True,
+                         error=self.error[1:2], ready=self.ready, ready_target=self.ready_target)
+            self._ev_gemm1.record(self._side)
+        main.wait_event(self._ev_gemm1)
+        grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False, error=self.error[2:3])
         self._check(lib.rbv_moe_combine(ctx, _p(out), T, H, _p(self.topk_idx), _p(self.topk_w), _p(self.slot),
                                         self.y_off, self.E, _p(self.error[3:4]), st), "combine")
         return out

@@ -149,3 +149,51 @@ def test_moe_layer_fp8_close_to_bf16():
         assert rel < 0.08, f"fp8 layer deviates {rel:.3f} from the bf16 reference"
     finally:
         comm.close()
+
+
+def test_gated_gemm_waits_for_its_rows_and_gives_up_after_the_deadline():
+    """The loader of the gated GEMM takes a group only when its delivery counter has reached the target.  Counters that
+    are already complete change nothing; a counter that nothing ever bumps makes the bounded wait run out: the kernel
+    sets its error flag, frees its TMEM and returns (no fault, the context stays usable)."""
+    from rbruck_alltoallv_b200.ops.moe import grouped_gemm
+    torch.manual_seed(4)
+    rows, N, K = [130, 70], 256, 128
+    M = sum(rows)
+    A = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    B = (torch.randn(2, N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    gs, gr = _groups(rows, "cuda")
+    want = grouped_gemm(A, B, gs, gr)
+    ready = torch.tensor([130, 70], dtype=torch.int64, device="cuda")
+    target = torch.tensor([130, 70], dtype=torch.int64, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = grouped_gemm(A, B, gs, gr, error=err, ready=ready, ready_target=target)
+    torch.cuda.synchronize()
+    assert err.item() == 0 and torch.equal(got, want)
+    target[1] = 71                                            # one row that never arrives
+    grouped_gemm(A, B, gs, gr, error=err, ready=ready, ready_target=target, timeout_ms=50.0)
+    torch.cuda.synchronize()
+    assert err.item() != 0
+    err.zero_()
+    assert torch.equal(grouped_gemm(A, B, gs, gr, error=err), want) and err.item() == 0
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_moe_layer_streamed_dispatch_matches_reference(overlap):
+    from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    comm = Communicator(nranks=1, heap_bytes=256 << 20, arena_bytes=1 << 20)
+    try:
+        T, H, I, E = 384, 256, 512, 8
+        layer = MoEExpertParallel(comm, E, H, I, T, seed=2, overlap=overlap)
+        assert layer.overlap == overlap
+        g = torch.Generator(device="cuda")
+        g.manual_seed(9)
+        for rep in range(3):                   # the delivery counters run on from call to call
+            x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+            logits = torch.randn(T, E, device="cuda", generator=g)
+            out = layer.forward(x, logits)
+            layer.check()
+            ref, _, _ = reference_forward(x, logits, layer.w13, layer.w2)
+            assert (out.float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3, (overlap, rep)
+    finally:
+        comm.close()
