@@ -40,7 +40,7 @@ def _a2av(algo, small=False, **kw):
     from ..parallel.comm import Communicator
     from . import distributions as D
     P = 8
-    comm = Communicator(nranks=P, heap_bytes=1 << 30, arena_bytes=24 << 20)
+    comm = Communicator(nranks=P, heap_bytes=1 << 30, arena_bytes=40 << 20)
     counts = D.zipf(P, 16384, seed=1) if small else D.normal(P, 1 << 20, 0.25, seed=1)   # fp32 elements
     sc, rc = counts.astype(np.int32), counts.T.astype(np.int32).copy()
     send = [torch.zeros(max(int(sc[i].sum()), 1), dtype=torch.float32, device="cuda") for i in range(P)]
