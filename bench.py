@@ -441,10 +441,11 @@ def run_ours(args):
         verify(key)
 
     # radix / protocol choice by measurement (part of warm-up); the simplest within 3 % of the best wins
+    from rbruck_alltoallv_b200.parallel.tuner import robust_us
     per_radix = {}
     for key in calls:
-        t = time_steps(lambda: step(key), steps=30, warmup=3, flush=flush, align=align)
-        per_radix[key] = float(np.median(t)) * 1e3
+        t = time_steps(lambda: step(key), steps=40, warmup=3, flush=flush, align=align)
+        per_radix[key] = robust_us(t)      # mean of the fastest 80 %: finer than the event timer's 1 us steps
     keys = list(calls)
     fastest = min(per_radix.values())
     best_i = min(range(len(keys)), key=lambda i: per_radix[keys[i]])

@@ -30,7 +30,8 @@ def _cache_path() -> Path:
     return Path(p) if p else Path(__file__).resolve().parent / "tuner_table.json"
 
 
-MARGIN = 0.03          # a candidate must beat the current winner by more than this fraction to replace it
+MARGIN = 0.03          # a candidate must beat the current winner by more than this fraction to replace it ...
+MIN_GAIN_US = 0.5      # ... and by more than this: CUDA event times on B200 come in steps of about one microsecond
 MIN_STEPS = 30         # timed steps per candidate in a sweep
 SKEW_CV = 0.5          # coefficient of variation of the block sizes from which an exchange counts as skewed
 
@@ -79,7 +80,7 @@ def record(P: int, nproc: int, mean_block_bytes: float, choice: dict, us: float,
     (``replace=True``: unconditionally, for a fresh sweep whose winner was chosen by the same rule)."""
     tab = load_table()
     k = _key(P, nproc, size_class(mean_block_bytes), skew_class(cv))
-    if replace or k not in tab or us < tab[k]["us"] * (1.0 - MARGIN):
+    if replace or k not in tab or (us < tab[k]["us"] * (1.0 - MARGIN) and tab[k]["us"] - us > MIN_GAIN_US):
         tab[k] = {"choice": choice, "us": us}
 
 
@@ -90,9 +91,19 @@ def pick_winner(timings) -> tuple:
     for choice, us in timings:
         if us is None:
             continue
-        if best is None or us < best[1] * (1.0 - MARGIN):
+        if best is None or (us < best[1] * (1.0 - MARGIN) and best[1] - us > MIN_GAIN_US):
             best = (choice, us)
     return best
+
+
+def robust_us(samples_ms) -> float:
+    """Microseconds of one candidate from its per-step times: the mean of the fastest 80 % of the steps.  A median
+    would sit on one of the timer's one-microsecond steps; the mean of many steps resolves finer differences, and
+    dropping the slowest fifth keeps stragglers out."""
+    import numpy as np
+    t = np.sort(np.asarray(samples_ms, dtype=np.float64))
+    keep = max(1, int(round(0.8 * len(t))))
+    return float(t[:keep].mean()) * 1e3
 
 
 def default_choice(P: int, nproc: int, mean_block_bytes: float) -> dict:
@@ -218,7 +229,7 @@ def sweep(comm, mean_block_bytes=(16, 256, 4096, 65536, 1 << 20, 4 << 20), type_
                     comm.reset()
                     row["us"][name] = None
                     continue
-                us = float(np.median(t)) * 1e3
+                us = robust_us(t)
                 row["us"][name] = round(us, 2)
                 timings.append((dict(cand, protocol="eager" if eager else "rendezvous"), us))
         win = pick_winner(timings)

@@ -78,8 +78,11 @@ def test_margin_keeps_the_simplest_candidate_within_three_percent():
     t = [({"algo": "spreadout"}, 22.50), ({"algo": "xor"}, 22.40), ({"algo": "ttpl_bt", "n": 4}, 22.10),
          ({"algo": "rbruck", "r": 2}, 30.0)]
     assert tuner.pick_winner(t)[0] == {"algo": "spreadout"}          # nobody is more than 3 % faster than the first
-    t.append(({"algo": "scattered", "b": 4}, 21.0))                      # 6.7 % faster: a real difference
+    t.append(({"algo": "scattered", "b": 4}, 21.0))                      # 6.7 % and 1.5 us faster: a real difference
     assert tuner.pick_winner(t)[0] == {"algo": "scattered", "b": 4}
+    # 4 % faster but less than half a microsecond: below what the event timer resolves
+    assert tuner.pick_winner([({"algo": "spreadout"}, 10.0), ({"algo": "xor"}, 9.6)])[0] == {"algo": "spreadout"}
+    assert abs(tuner.robust_us([0.010, 0.010, 0.011, 0.010, 0.050]) - 10.25) < 1e-6
     assert tuner.pick_winner([({"algo": "a"}, None)]) is None
 
 
