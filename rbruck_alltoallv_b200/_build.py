@@ -31,6 +31,7 @@ CUDA_SOURCES = [
     "kernels/a2av_static.cu",
     "kernels/moe_kernels.cu",
     "kernels/grouped_gemm_sm100.cu",
+    "kernels/grouped_gemm_pair_sm100.cu",
     "kernels/grouped_gemm_fp8_sm100.cu",
     "kernels/fft_transpose.cu",
     "kernels/noalloc.cu",
@@ -132,7 +133,7 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_verbose: bool =
         for j in jobs:
             j[4].write_text(j[5])
         tmp = lib.with_suffix(f".tmp{os.getpid()}.so")
-        _run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *map(str, objs), "-o", str(tmp), "-lcuda"],
+        _run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *map(str, objs), "-o", str(tmp)],
              verbose)
         os.replace(tmp, lib)
         lib.with_suffix(".stamp").write_text(digest)

@@ -88,6 +88,10 @@ def declare_cuda(lib):
 def declare_moe(lib):
     vp, i, ll, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_ulonglong
     lib.rbv_grouped_gemm_bf16.argtypes = [vp, ll, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    lib.rbv_grouped_gemm_bf16_pair.argtypes = [vp, ll, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    lib.rbv_grouped_gemm_set_pair.argtypes = [i]
+    lib.rbv_grouped_gemm_set_pair.restype = None
+    lib.rbv_grouped_gemm_pair_enabled.argtypes = []
     lib.rbv_grouped_gemm_fp8.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     lib.rbv_quantize_rows_fp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_moe_route.argtypes = [vp, i, i, vp, vp, vp, vp]

@@ -789,16 +789,63 @@ int Context::set_nvls_meta(void* self_ptr, void* mc_ptr, size_t bytes) {
 }
 
 // ---- NVLS: the library's own multicast object (CUDA driver API) ---------------------------------------------
+// The driver entry points are looked up at run time (cudaGetDriverEntryPoint), so the library loads on a machine
+// without a driver (a build host) and needs libcudart only.
 namespace {
+struct DriverApi {
+#define RBV_DRV(name) decltype(&::name) name = nullptr;
+  RBV_DRV(cuGetErrorName) RBV_DRV(cuDeviceGetAttribute) RBV_DRV(cuMulticastGetGranularity) RBV_DRV(cuMulticastCreate)
+  RBV_DRV(cuMemExportToShareableHandle) RBV_DRV(cuMemImportFromShareableHandle) RBV_DRV(cuMulticastAddDevice)
+  RBV_DRV(cuMemGetAllocationGranularity) RBV_DRV(cuMemCreate) RBV_DRV(cuMulticastBindMem)
+  RBV_DRV(cuMemAddressReserve) RBV_DRV(cuMemMap) RBV_DRV(cuMemSetAccess) RBV_DRV(cuMemUnmap)
+  RBV_DRV(cuMemAddressFree) RBV_DRV(cuMulticastUnbind) RBV_DRV(cuMemRelease)
+#undef RBV_DRV
+  bool ok = false;
+  std::string missing;
+};
+
+template <typename F>
+bool drv_lookup(const char* name, F* out) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+    cudaGetLastError();
+    return false;
+  }
+  *out = reinterpret_cast<F>(p);
+  return true;
+}
+
+const DriverApi& drv() {
+  static DriverApi d = [] {
+    DriverApi a;
+    bool ok = true;
+#define RBV_DRV(name) if (!drv_lookup(#name, &a.name)) { ok = false; a.missing += std::string(a.missing.empty() ? "" : ", ") + #name; }
+    RBV_DRV(cuGetErrorName) RBV_DRV(cuDeviceGetAttribute) RBV_DRV(cuMulticastGetGranularity) RBV_DRV(cuMulticastCreate)
+    RBV_DRV(cuMemExportToShareableHandle) RBV_DRV(cuMemImportFromShareableHandle) RBV_DRV(cuMulticastAddDevice)
+    RBV_DRV(cuMemGetAllocationGranularity) RBV_DRV(cuMemCreate) RBV_DRV(cuMulticastBindMem)
+    RBV_DRV(cuMemAddressReserve) RBV_DRV(cuMemMap) RBV_DRV(cuMemSetAccess) RBV_DRV(cuMemUnmap)
+    RBV_DRV(cuMemAddressFree) RBV_DRV(cuMulticastUnbind) RBV_DRV(cuMemRelease)
+#undef RBV_DRV
+    a.ok = ok;
+    return a;
+  }();
+  return d;
+}
+
 const char* cu_name(CUresult r) {
   const char* s = nullptr;
-  cuGetErrorName(r, &s);
+  if (drv().cuGetErrorName) drv().cuGetErrorName(r, &s);
   return s ? s : "unknown CUDA driver error";
 }
 }  // namespace
 #define RBV_CU(expr)                                                              \
   do {                                                                            \
-    CUresult r__ = (expr);                                                        \
+    if (!drv().ok) {                                                              \
+      last_error_ = "CUDA driver entry points not found: " + drv().missing;       \
+      return -1;                                                                  \
+    }                                                                             \
+    CUresult r__ = (drv().expr);                                                  \
     if (r__ != CUDA_SUCCESS) {                                                    \
       last_error_ = std::string(#expr) + " failed: " + cu_name(r__);              \
       return (int)r__;                                                            \
@@ -883,11 +930,12 @@ void Context::nvls_teardown() {
   cudaDeviceSynchronize();
   nvls_self_ = nvls_mc_ = nullptr;
   nvls_bytes_ = 0;
-  if (own_mc_va_) { cuMemUnmap(own_mc_va_, own_mc_bytes_); cuMemAddressFree(own_mc_va_, own_mc_bytes_); }
-  if (own_va_) { cuMemUnmap(own_va_, own_mc_bytes_); cuMemAddressFree(own_va_, own_mc_bytes_); }
-  if (own_mc_bound_) cuMulticastUnbind(own_mc_handle_, device_, 0, own_mc_bytes_);
-  if (own_mem_handle_) cuMemRelease(own_mem_handle_);
-  cuMemRelease(own_mc_handle_);
+  const DriverApi& d = drv();   // complete, or no object could have been made
+  if (own_mc_va_) { d.cuMemUnmap(own_mc_va_, own_mc_bytes_); d.cuMemAddressFree(own_mc_va_, own_mc_bytes_); }
+  if (own_va_) { d.cuMemUnmap(own_va_, own_mc_bytes_); d.cuMemAddressFree(own_va_, own_mc_bytes_); }
+  if (own_mc_bound_) d.cuMulticastUnbind(own_mc_handle_, device_, 0, own_mc_bytes_);
+  if (own_mem_handle_) d.cuMemRelease(own_mem_handle_);
+  d.cuMemRelease(own_mc_handle_);
   own_mc_handle_ = own_mem_handle_ = own_va_ = own_mc_va_ = 0;
   own_mc_bound_ = false;
 }

@@ -25,6 +25,15 @@ int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void* B, void* 
                           const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
                           int max_ctas, void* cuda_stream);
 
+/* The kernel behind rbv_grouped_gemm_bf16 when CTA pairs are enabled (the default; RBV_GEMM_PAIR=0 or
+ * rbv_grouped_gemm_set_pair(0) selects the one-CTA kernel): clusters of two CTAs share 256 x 256 tiles with
+ * tcgen05 cta_group::2 MMAs, each CTA fetching half of the operands.  Same arguments and limits. */
+int rbv_grouped_gemm_bf16_pair(const void* A, long long a_rows, const void* B, void* C, const int* group_start,
+                               const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
+                               int max_ctas, void* cuda_stream);
+void rbv_grouped_gemm_set_pair(int on);
+int rbv_grouped_gemm_pair_enabled(void);
+
 /* The same with a gated start per group: the loader touches the rows of group g only once ready[g] >= ready_target[g]
  * (device uint64 arrays; the counters are bumped by whoever delivers the rows, e.g. rbv_moe_dispatch_streamed running
  * at the same time on this and on other GPUs).  The wait is bounded by timeout_ms (0: 2 s). */

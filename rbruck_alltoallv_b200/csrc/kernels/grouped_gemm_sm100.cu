@@ -305,6 +305,10 @@ extern "C" int rbv_grouped_gemm_bf16_gated(const void* A, long long a_rows, cons
                                            const unsigned long long* ready, const unsigned long long* ready_target,
                                            double timeout_ms) {
   using namespace rbv;
+  // Without a gate the CTA-pair kernel (grouped_gemm_pair_sm100.cu) is the default; the gated start stays on this one.
+  if (!ready && rbv_grouped_gemm_pair_enabled())
+    return rbv_grouped_gemm_bf16_pair(A, a_rows, B, C, group_start, group_rows, G, N, K, ldc, epilogue, error_flag,
+                                      max_ctas, cuda_stream);
   if (G < 1 || G > kMoeMaxGroups || N % BN || K % BK || a_rows < 1 || (ldc % 8)) return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return (int)cudaErrorInvalidValue;

@@ -24,13 +24,15 @@ def _p(t: Optional[torch.Tensor]):
 def grouped_gemm(A: torch.Tensor, B: torch.Tensor, group_start: torch.Tensor, group_rows: torch.Tensor,
                  out: Optional[torch.Tensor] = None, swiglu: bool = False, error: Optional[torch.Tensor] = None,
                  max_ctas: int = 0, ready: Optional[torch.Tensor] = None, ready_target: Optional[torch.Tensor] = None,
-                 timeout_ms: float = 0.0) -> torch.Tensor:
+                 timeout_ms: float = 0.0, pair: Optional[bool] = None) -> torch.Tensor:
     """``out[rows of g] = epi(A[rows of g] @ B[g].T)`` with bf16 operands and fp32 accumulation.
 
     ``A`` [M, K], ``B`` [G, N, K], ``group_start`` / ``group_rows`` int32 CUDA tensors [G].  With ``swiglu``
     the rows of ``B[g]`` interleave gate and up projections and ``out`` is [M, N // 2].  With ``ready`` /
     ``ready_target`` (int64 CUDA tensors [G]) the rows of group g are loaded only once ``ready[g] >= ready_target[g]``:
-    the kernel may be launched while the rows are still being delivered."""
+    the kernel may be launched while the rows are still being delivered.  ``pair`` picks the kernel of an ungated
+    call: True = CTA pairs (``cta_group::2``, 256 x 256 tiles; the default unless ``RBV_GEMM_PAIR=0``), False = one CTA
+    per 128 x 256 tile."""
     lib = _native.cuda_lib()
     assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
     G, N, K = B.shape
@@ -42,9 +44,17 @@ def grouped_gemm(A: torch.Tensor, B: torch.Tensor, group_start: torch.Tensor, gr
     if error is None:
         error = torch.zeros(1, dtype=torch.int32, device=A.device)
     st = torch.cuda.current_stream(A.device).cuda_stream
-    rc = lib.rbv_grouped_gemm_bf16_gated(_p(A), M, _p(B), _p(out), _p(group_start), _p(group_rows), G, N, K,
-                                         out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas), C.c_void_p(st),
-                                         _p(ready), _p(ready_target), float(timeout_ms))
+    prev = None
+    if pair is not None and ready is None:
+        prev = lib.rbv_grouped_gemm_pair_enabled()
+        lib.rbv_grouped_gemm_set_pair(1 if pair else 0)
+    try:
+        rc = lib.rbv_grouped_gemm_bf16_gated(_p(A), M, _p(B), _p(out), _p(group_start), _p(group_rows), G, N, K,
+                                             out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas),
+                                             C.c_void_p(st), _p(ready), _p(ready_target), float(timeout_ms))
+    finally:
+        if prev is not None:
+            lib.rbv_grouped_gemm_set_pair(prev)
     if rc:
         raise RuntimeError(f"grouped GEMM launch failed (CUDA error {rc})")
     return out

@@ -11,9 +11,10 @@ def _groups(rows, device):
     return (torch.from_numpy(start).to(device), torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(device))
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("rows,N,K", [([128, 128], 256, 64), ([100, 37, 0, 300], 256, 128), ([513, 64, 1], 512, 256),
-                                      ([1000, 24], 1024, 512)])
-def test_grouped_gemm_matches_fp32(rows, N, K):
+                                      ([1000, 24], 1024, 512), ([2000, 129, 1500], 2048, 1024)])
+def test_grouped_gemm_matches_fp32(rows, N, K, pair):
     from rbruck_alltoallv_b200.ops.moe import grouped_gemm
     torch.manual_seed(0)
     G, M = len(rows), int(sum(rows))
@@ -22,7 +23,7 @@ def test_grouped_gemm_matches_fp32(rows, N, K):
     gs, gr = _groups(rows, "cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = torch.full((M + 5, N), 7.0, dtype=torch.bfloat16, device="cuda")
-    grouped_gemm(A, B, gs, gr, out=out, error=err)
+    grouped_gemm(A, B, gs, gr, out=out, error=err, pair=pair)
     torch.cuda.synchronize()
     assert err.item() == 0
     r0 = 0
@@ -35,7 +36,8 @@ def test_grouped_gemm_matches_fp32(rows, N, K):
     assert torch.all(out[M:] == 7.0), "rows beyond the last group must stay untouched"
 
 
-def test_grouped_gemm_swiglu():
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_swiglu(pair):
     from rbruck_alltoallv_b200.ops.moe import grouped_gemm, pack_gate_up
     torch.manual_seed(1)
     rows, I, K = [200, 56], 256, 128
@@ -44,7 +46,7 @@ def test_grouped_gemm_swiglu():
     gate = (torch.randn(2, I, K, device="cuda") * 0.1).to(torch.bfloat16)
     up = (torch.randn(2, I, K, device="cuda") * 0.1).to(torch.bfloat16)
     gs, gr = _groups(rows, "cuda")
-    out = grouped_gemm(A, pack_gate_up(gate, up), gs, gr, swiglu=True)
+    out = grouped_gemm(A, pack_gate_up(gate, up), gs, gr, swiglu=True, pair=pair)
     torch.cuda.synchronize()
     r0 = 0
     for g, n in enumerate(rows):
