@@ -48,6 +48,10 @@ int rbv_grouped_gemm_bf16_gated(const void* A, long long a_rows, const void* B, 
 int rbv_grouped_gemm_fp8(const void* A, const float* a_scale_t, long long a_rows, const void* B, const float* b_scale,
                          void* C, const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
                          int epilogue, int* error_flag, int max_ctas, void* cuda_stream);
+/* The kernel behind rbv_grouped_gemm_fp8 when CTA pairs are enabled: 256 x 128 tiles on clusters of two CTAs. */
+int rbv_grouped_gemm_fp8_pair(const void* A, const float* a_scale_t, long long a_rows, const void* B,
+                              const float* b_scale, void* C, const int* group_start, const int* group_rows, int G,
+                              int N, int K, int ldc, int epilogue, int* error_flag, int max_ctas, void* cuda_stream);
 /* bf16 [rows, K] (row stride ldx elements) -> e4m3 [rows, K] + scale_t [K / 128][rows], scale = amax / 448. */
 int rbv_quantize_rows_fp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, float* scale_t,
                           void* cuda_stream);

@@ -350,6 +350,10 @@ extern "C" int rbv_grouped_gemm_fp8(const void* A, const float* a_scale_t, long 
                                     int G, int N, int K, int ldc, int epilogue, int* error_flag, int max_ctas,
                                     void* cuda_stream) {
   using namespace rbv;
+  // CTA pairs (grouped_gemm_fp8_pair_sm100.cu) unless switched off (RBV_GEMM_PAIR=0 / rbv_grouped_gemm_set_pair(0))
+  if (rbv_grouped_gemm_pair_enabled())
+    return rbv_grouped_gemm_fp8_pair(A, a_scale_t, a_rows, B, b_scale, C, group_start, group_rows, G, N, K, ldc,
+                                     epilogue, error_flag, max_ctas, cuda_stream);
   if (G < 1 || G > kMoeMaxGroups || N % BN || K % BK || a_rows < 1 || (ldc % 8)) return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return (int)cudaErrorInvalidValue;

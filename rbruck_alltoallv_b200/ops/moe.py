@@ -98,8 +98,9 @@ def dequantize_weight_blocks_fp8(q: torch.Tensor, scale: torch.Tensor) -> torch.
 def grouped_gemm_fp8(Aq: torch.Tensor, a_scale_t: torch.Tensor, Bq: torch.Tensor, b_scale: torch.Tensor,
                      group_start: torch.Tensor, group_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
                      swiglu: bool = False, error: Optional[torch.Tensor] = None, max_ctas: int = 0,
-                     coarse: bool = False) -> torch.Tensor:
-    """Block-scaled e4m3 grouped GEMM (see ``csrc/kernels/grouped_gemm_fp8_sm100.cu``); bf16 output.
+                     coarse: bool = False, pair: Optional[bool] = None) -> torch.Tensor:
+    """Block-scaled e4m3 grouped GEMM (see ``csrc/kernels/grouped_gemm_fp8_sm100.cu`` and its CTA-pair version
+    ``grouped_gemm_fp8_pair_sm100.cu``, the default; ``pair=False`` or ``RBV_GEMM_PAIR=0`` for the former); bf16 output.
 
     ``coarse=True`` promises that the scales do not change along K (one per activation row, one per 128 weight
     rows): the kernel then accumulates a whole tile in TMEM and applies ``a_scale_t[0] * b_scale[..., 0]`` once."""
@@ -114,9 +115,18 @@ def grouped_gemm_fp8(Aq: torch.Tensor, a_scale_t: torch.Tensor, Bq: torch.Tensor
     if error is None:
         error = torch.zeros(1, dtype=torch.int32, device=Aq.device)
     st = torch.cuda.current_stream(Aq.device).cuda_stream
-    rc = lib.rbv_grouped_gemm_fp8(_p(Aq), _p(a_scale_t), M, _p(Bq), _p(b_scale), _p(out), _p(group_start),
-                                  _p(group_rows), G, N, K, out.stride(0), (1 if swiglu else 0) | (2 if coarse else 0), _p(error), int(max_ctas),
-                                  C.c_void_p(st))
+    prev = None
+    if pair is not None:
+        prev = lib.rbv_grouped_gemm_pair_enabled()
+        lib.rbv_grouped_gemm_set_pair(1 if pair else 0)
+    try:
+        rc = lib.rbv_grouped_gemm_fp8(_p(Aq), _p(a_scale_t), M, _p(Bq), _p(b_scale), _p(out), _p(group_start),
+                                      _p(group_rows), G, N, K, out.stride(0),
+                                      (1 if swiglu else 0) | (2 if coarse else 0), _p(error), int(max_ctas),
+                                      C.c_void_p(st))
+    finally:
+        if prev is not None:
+            lib.rbv_grouped_gemm_set_pair(prev)
     if rc:
         raise RuntimeError(f"fp8 grouped GEMM launch failed (CUDA error {rc})")
     return out

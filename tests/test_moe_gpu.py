@@ -81,8 +81,10 @@ def test_moe_layer_single_gpu():
     smoke_moe()
 
 
-@pytest.mark.parametrize("rows,N,K", [([128], 128, 128), ([100, 37, 0, 300], 256, 256), ([513, 64], 512, 1024)])
-def test_grouped_gemm_fp8_block_scaled(rows, N, K):
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("rows,N,K", [([128], 128, 128), ([100, 37, 0, 300], 256, 256), ([513, 64], 512, 1024),
+                                      ([1500, 129, 700], 2048, 2048)])
+def test_grouped_gemm_fp8_block_scaled(rows, N, K, pair):
     from rbruck_alltoallv_b200.ops import moe
     torch.manual_seed(3)
     G, M = len(rows), int(sum(rows))
@@ -94,7 +96,7 @@ def test_grouped_gemm_fp8_block_scaled(rows, N, K):
     assert (moe.dequantize_rows_fp8(Aq, As) - A.float()).abs().max().item() <= 0.07 * A.float().abs().max().item()
     gs, gr = _groups(rows, "cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err)
+    out = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err, pair=pair)
     torch.cuda.synchronize()
     assert err.item() == 0
     Ad, Bd = moe.dequantize_rows_fp8(Aq, As), moe.dequantize_weight_blocks_fp8(Bq, Bs)
@@ -107,7 +109,8 @@ def test_grouped_gemm_fp8_block_scaled(rows, N, K):
         r0 += n
 
 
-def test_grouped_gemm_fp8_coarse_scales():
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_fp8_coarse_scales(pair):
     """Scales that are constant along K: the whole tile is accumulated in TMEM and scaled once."""
     from rbruck_alltoallv_b200.ops import moe
     torch.manual_seed(5)
@@ -119,8 +122,8 @@ def test_grouped_gemm_fp8_coarse_scales():
     Bs = (torch.rand(G, N // 128, 1, device="cuda") * 0.1 + 0.01).expand(G, N // 128, K // 128).contiguous()
     gs, gr = _groups(rows, "cuda")
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    fine = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err)
-    coarse = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err, coarse=True)
+    fine = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err, pair=pair)
+    coarse = moe.grouped_gemm_fp8(Aq, As, Bq, Bs, gs, gr, error=err, coarse=True, pair=pair)
     torch.cuda.synchronize()
     assert err.item() == 0
     Ad, Bd = moe.dequantize_rows_fp8(Aq, As), moe.dequantize_weight_blocks_fp8(Bq, Bs)
