@@ -284,28 +284,55 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
 }
 
 // Row-wise 1 x 128 quantisation of bf16 activations to e4m3: out[row, k] = x[row, k] / scale, scale = amax / 448.
-// One warp per (row, 128-column block); scales are stored transposed, [K / 128][rows].
-__global__ void quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long rows, int K, int ldx,
-                                     uint8_t* __restrict__ out, float* __restrict__ scale_t) {
-  const int lane = threadIdx.x & 31;
-  const long long nblk = (long long)rows * (K / 128);
-  const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < nblk; w += warps) {
-    const long long row = w / (K / 128);
-    const int kb = (int)(w % (K / 128));
-    const __nv_bfloat16* src = x + row * ldx + kb * 128 + lane * 4;
-    const uint2 raw = *reinterpret_cast<const uint2*>(src);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-    float m = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+// Sixteen lanes per (row, 128-column block), eight bf16 (one 16-byte load) per lane, four blocks per half-warp in
+// flight before the first reduction; scales are stored transposed, [K / 128][rows].
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long rows, int K, int ldx, uint8_t* __restrict__ out,
+                     float* __restrict__ scale_t) {
+  constexpr int kUnroll = 4;
+  const int lane16 = threadIdx.x & 15;
+  const unsigned kblocks = (unsigned)(K / 128);
+  const unsigned nblk = (unsigned)(rows * kblocks);                       // < 2^31, checked by the caller
+  const unsigned groups = (gridDim.x * blockDim.x) >> 4;                  // half-warps in the grid
+  const unsigned g0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const unsigned which = g0 & 1u;   // the two half-warps of a warp take neighbouring blocks; the loop is warp-uniform
+  for (unsigned base = g0 - which; base < nblk; base += groups * kUnroll) {
+    uint4 raw[kUnroll];
+    unsigned row[kUnroll], kb[kUnroll];
     #pragma unroll
-    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float scale = m > 0.0f ? m / 448.0f : 1.0f;
-    const float inv = 1.0f / scale;
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv, a.y * inv), __NV_SATFINITE, __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv, b.y * inv), __NV_SATFINITE, __NV_E4M3);
-    *reinterpret_cast<uint32_t*>(out + row * K + kb * 128 + lane * 4) = lo | (hi << 16);
-    if (lane == 0) scale_t[(size_t)kb * rows + row] = scale;
+    for (int u = 0; u < kUnroll; u++) {
+      const unsigned w = base + which + (unsigned)u * groups;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      row[u] = w / kblocks;
+      kb[u] = w - row[u] * kblocks;
+      if (w < nblk)
+        raw[u] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)row[u] * ldx + kb[u] * 128 + lane16 * 8));
+    }
+    #pragma unroll
+    for (int u = 0; u < kUnroll; u++) {
+      const unsigned w = base + which + (unsigned)u * groups;
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+      float2 v[4];
+      float m = 0.0f;
+      #pragma unroll
+      for (int j = 0; j < 4; j++) {
+        v[j] = __bfloat1622float2(h[j]);
+        m = fmaxf(m, fmaxf(fabsf(v[j].x), fabsf(v[j].y)));
+      }
+      #pragma unroll
+      for (int o = 8; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));   // stays inside 16 lanes
+      if (w < nblk) {
+        const float scale = m > 0.0f ? m / 448.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        uint32_t q[4];
+        #pragma unroll
+        for (int j = 0; j < 4; j++)
+          q[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[j].x * inv, v[j].y * inv), __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint2*>(out + (size_t)row[u] * K + kb[u] * 128 + lane16 * 8) =
+            make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+        if (lane16 == 0) scale_t[(size_t)kb[u] * rows + row[u]] = scale;
+      }
+    }
   }
 }
 
@@ -383,10 +410,14 @@ extern "C" int rbv_grouped_gemm_fp8(const void* A, const float* a_scale_t, long 
 extern "C" int rbv_quantize_rows_fp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, float* scale_t,
                                      void* cuda_stream) {
   using namespace rbv;
-  if (K % 128 || rows < 1 || (ldx % 4)) return (int)cudaErrorInvalidValue;
+  if (K % 128 || rows < 1 || (ldx % 8) || (reinterpret_cast<uintptr_t>(x_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(out_fp8) & 7))
+    return (int)cudaErrorInvalidValue;
   const long long nblk = rows * (K / 128);
-  long long grid = (nblk + 7) / 8;
-  if (grid > 148 * 16) grid = 148 * 16;
+  if (nblk >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  long long grid = (nblk + 63) / 64;   // 16 half-warps per block, four blocks of columns each
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (grid < 1) grid = 1;
   quantize_rows_kernel<<<(int)grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const __nv_bfloat16*>(x_bf16), rows, K, ldx, static_cast<uint8_t*>(out_fp8), scale_t);
   return (int)cudaGetLastError();
