@@ -19,7 +19,8 @@
 //
 // Completion is the same as in the dynamic kernel (a2av_kernel.cu): chunks that land in a receive buffer are
 // tallied per CTA and added to the receiver's arrival counter behind one fence; the receiver's target for the
-// call was counted on the host.  All waits are bounded.
+// call was counted on the host.  When one process hosts every rank nothing is tallied or waited for: every delivery
+// is a store of this very launch, so the end of the kernel is the completion.  All waits are bounded.
 #include <cuda_runtime.h>
 
 #include "kernels/primitives.cuh"
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   if (multi && blockIdx.x == 0 && tid < a.nproc && tid != a.proc)
     dev::st_relaxed_sys(&ctrl_of(a, tid)->entered[a.proc], flagv);
   // the owner of a receive buffer adds the chunks this call brings to its running target
-  if (blockIdx.x == 0)
+  if (multi && blockIdx.x == 0)
     for (int i = tid; i < a.L; i += blockDim.x) my->recv_target[i] += a.expect[i];
 
   bool alive = true;
@@ -130,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
     }
     __syncwarp();
     if (lane == 0) {
-      if (it.signal_flag == kNoFlag) atomicAdd(&s_arrived[it.dst_rank], 1u);
+      if (it.signal_flag == kNoFlag) { if (multi) atomicAdd(&s_arrived[it.dst_rank], 1u); }
       else if (ok) dev::signal_store(flag_of(a, dproc, parity, it.signal_flag), flagv, remote);
       if (trace) atomicMax(&tb->kend[kidx], dev::globaltimer());
     }
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   }
   // report this CTA's deliveries: the barrier orders every warp's stores before the fence, which publishes them
   if (blockIdx.x == 0 && tid == 0) my->status.trace[5] = dev::globaltimer();
-  for (int d = tid; d < a.P; d += blockDim.x) {
+  for (int d = tid; multi && d < a.P; d += blockDim.x) {
     const unsigned n = s_arrived[d];
     const int dproc = d / a.L;
     const bool far = dproc != a.proc;
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   }
   if (blockIdx.x == 0) {
     if (tid == 0) my->status.trace[3] = my->status.trace[6] = dev::globaltimer();
-    for (int i = tid; i < a.L; i += blockDim.x) {
+    for (int i = tid; multi && i < a.L; i += blockDim.x) {
       const unsigned long long target = my->recv_target[i];
       int r = alive ? dev::wait_ge(&my->recv_arrivals[i], target, wc, multi) : (int)dev::WAIT_ABORTED;
       if (r == dev::WAIT_TIMEOUT)
