@@ -460,7 +460,7 @@ def run_ours(args):
         t = time_steps(lambda: step(best), steps=args.steps, warmup=warm, flush=flush, align=align)
         comm.check()
 
-        # End to end through the public API.  Three ways to move a step's inputs from pinned host memory to the GPUs
+        # End to end through the public API.  Ways to move a step's inputs from pinned host memory to the GPUs
         # and its result back, all timed (the fastest is reported, the others are listed):
         #  "copy":      cudaMemcpyAsync H2D of every send buffer, the collective, cudaMemcpyAsync D2H of every
         #               receive buffer;
@@ -487,6 +487,14 @@ def run_ours(args):
             ci_call.launch()
 
         e2e_paths = {"copy": e2e_copy, "zero_copy": zc_call.launch, "copy_in": e2e_copy_in}
+        # "zero_copy_static": a persistent call resolved on the host (static kernel) given the pinned host buffers
+        # themselves.  One process hosting every rank: each block goes from the pinned send buffer to the pinned
+        # receive buffer in one copy.  Several processes: the kernel reads the send blocks from pinned host memory,
+        # stores them into the destination GPU's receive buffer and, once everything has arrived, copies the
+        # received blocks on to the pinned receive buffer itself.
+        zs_call = comm.prepare(pin_send_l, pin_recv_l, sc, sd, rc, rd, algo="rbruck", r=8, type_size=TYPE_SIZE)
+        if zs_call.kind == "static":
+            e2e_paths["zero_copy_static"] = zs_call.launch
         e2e_us = {}
         for name, fn in e2e_paths.items():
             pin_recv.fill_(0)

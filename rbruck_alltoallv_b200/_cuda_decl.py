@@ -57,6 +57,8 @@ def declare_cuda(lib):
     lib.rbv_prepare_global.argtypes = lib.rbv_prepare.argtypes + [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.rbv_prepared_info.argtypes = [C.c_void_p, c_ll_p]
     lib.rbv_ctx_set_static.argtypes = [C.c_void_p, C.c_int]
+    lib.rbv_ctx_set_recv_mirror.argtypes = [C.c_void_p, C.c_void_p]
+    lib.rbv_ctx_set_recv_mirror.restype = None
     lib.rbv_ctx_last_trace.argtypes = [C.c_void_p, C.POINTER(C.c_uint), C.POINTER(C.c_ulonglong),
                                        C.POINTER(C.c_ulonglong), C.c_int]
     lib.rbv_iteration_count.argtypes = [C.c_void_p]

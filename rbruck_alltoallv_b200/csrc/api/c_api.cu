@@ -133,9 +133,13 @@ void* rbv_prepare_global(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, i
     ca.counts_on_device = counts_on_device != 0;
     ca.bytes_hint = bytes_hint;
     ca.g_counts = g_counts; ca.g_caps = g_caps; ca.g_rdispls = g_rdispls; ca.g_recvoff = g_recvoff;
+    std::vector<void*> mirror;
+    mirror.swap(ctx->recv_mirror);   // holds for this call only
+    if ((int)mirror.size() == ctx->c->L()) ca.recv_mirror = mirror.data();
     CallOptions opt;
     opt.grid = grid; opt.chunk_bytes = chunk_bytes; opt.flags = flags & CALL_INPLACE;
     opt.allow_static = ctx->allow_static && !(flags & 0x100u);
+    opt.recv_anywhere = (flags & 0x200u) != 0;
     opt.eager_max_bytes = ctx->eager;
     auto pc = std::make_unique<Prepared>();
     int rc = ctx->c->prepare(s, type_size, ca, opt, nullptr, true, pc.get());
@@ -210,6 +214,10 @@ void rbv_ctx_set_trace(rbv_ctx_t ctx, int on) { ctx->c->set_trace(on != 0); }
 void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode) { ctx->c->set_bulk(mode); }
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int mode) { ctx->c->set_cooperative(mode < 0 ? -1 : (mode ? 1 : 0)); }
 void rbv_ctx_set_static(rbv_ctx_t ctx, int on) { ctx->allow_static = on != 0; }
+void rbv_ctx_set_recv_mirror(rbv_ctx_t ctx, void* const* mirrors) {
+  ctx->recv_mirror.clear();
+  if (mirrors) ctx->recv_mirror.assign(mirrors, mirrors + ctx->c->L());
+}
 void rbv_ctx_set_auto_hint(rbv_ctx_t ctx, double mean_block_bytes, double cv) { ctx->hint_mean = mean_block_bytes; ctx->hint_cv = cv; }
 
 // Per-key time stamps of the most recent traced call: fills keys[i] (plan key: phase << 24 | step), start_ns[i],

@@ -21,6 +21,7 @@ struct rbv_ctx_s {
   size_t chunk = 0;
   unsigned long long eager = 0;   // cell payload bytes of the eager protocol for the following calls (0: off)
   bool allow_static = true;       // persistent calls with host-side counts may run the static kernel
+  std::vector<void*> recv_mirror; // for the next rbv_prepare*: where the received blocks are wanted in the end
   double plan_build_s = 0;        // host time spent compiling the schedule of the latest call (0: it was cached)
   // per-rank entry points: the resolved call of the previous collective, reused when the next one has the same
   // arguments (a loop over one collective then costs one kernel launch per iteration)

@@ -310,9 +310,15 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
   out->owned_items = nullptr;
   for (int q = 0; q < nproc_; q++)
     if (!peer_[q]) { last_error_ = "peer heaps are not connected"; return RBV_ERR_BAD_ARG; }
+  // A persistent call whose counts are all on the host (own ranks only when this process hosts every rank, or the
+  // gathered tables) is resolved into copy descriptors and runs the static kernel.
+  const bool will_be_static = persistent && opt.allow_static && !ca.counts_on_device && !eager && !inplace &&
+                              absent_rank_ < 0 && (nproc_ == 1 || (ca.g_counts && ca.g_rdispls && ca.g_recvoff));
   // With host-side counts the receive extents are known: a buffer that ends beyond the heap is refused here
-  // instead of letting peers store outside their mapping of it.
-  if (!ca.counts_on_device && !eager) {
+  // instead of letting peers store outside their mapping of it.  A static call of a single process addresses
+  // everything absolutely and has no peers: there any device-accessible memory will do (pinned host memory
+  // included) when the caller has checked the extents against its own knowledge of the buffers.
+  if (!ca.counts_on_device && !eager && !(will_be_static && nproc_ == 1 && opt.recv_anywhere)) {
     for (int lr = 0; lr < L_; lr++) {
       long long ext = 0;
       for (int s2 = 0; s2 < P_; s2++) {
@@ -328,11 +334,7 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
       }
     }
   }
-  // A persistent call whose counts are all on the host (own ranks only when this process hosts every rank, or the
-  // gathered tables) is resolved into copy descriptors here and runs the static kernel.
-  if (persistent && opt.allow_static && !ca.counts_on_device && !eager && !inplace && absent_rank_ < 0 &&
-      (nproc_ == 1 || (ca.g_counts && ca.g_rdispls && ca.g_recvoff)))
-    return prepare_static(dp, ts, ca, opt, out);
+  if (will_be_static) return prepare_static(dp, ts, ca, opt, out);
   if (P_ > kMaxRanks) {
     last_error_ = "communicators of more than 64 ranks take persistent calls with host-side counts only "
                   "(rendezvous protocol, not in place): prepare the call, then launch it";
@@ -647,7 +649,8 @@ int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const
           last_error_ = "block " + std::to_string(s) + " -> " + std::to_string(d) + " is larger than the receiver's recvcount";
           return RBV_ERR_TRUNCATE;
         }
-  for (int d = 0; d < P; d++) {
+  const bool anywhere = nproc_ == 1 && opt.recv_anywhere;   // no peers, extents checked by the caller
+  for (int d = 0; d < P && !anywhere; d++) {
     unsigned long long ext = 0;
     for (int s = 0; s < P; s++)
       ext = std::max(ext, (unsigned long long)(grd[(size_t)d * P + s] + gc[(size_t)s * P + d]) * ts);
@@ -744,12 +747,34 @@ int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const
   for (const Op& o : dp->plan.ops)
     if (o.dst_cell < 0 && o.dst / L == proc_) expect[o.dst - first] += nchunks(slice_bytes(o, nullptr));
 
-  // ---- device copy: [expect[L] | items] ----
+  // blocks to copy on to the caller's own buffers once everything has arrived (pieces of at most 64 KB, so that
+  // the warps of the copying CTA share a large block)
+  std::vector<DrainItem> drain;
+  if (ca.recv_mirror)
+    for (int lr = 0; lr < L; lr++) {
+      if (!ca.recv_mirror[lr] || ca.recv_mirror[lr] == ca.recvbufs[lr]) continue;
+      const int d = first + lr;
+      for (int s2 = 0; s2 < P; s2++) {
+        const unsigned long long len = (unsigned long long)std::max(gc[(size_t)s2 * P + d], 0) * ts;
+        const unsigned long long off = (unsigned long long)grd[(size_t)d * P + s2] * ts;
+        for (unsigned long long o2 = 0; o2 < len; o2 += 64u << 10) {
+          DrainItem di{};
+          di.src = reinterpret_cast<unsigned long long>(ca.recvbufs[lr]) + off + o2;
+          di.dst = reinterpret_cast<unsigned long long>(ca.recv_mirror[lr]) + off + o2;
+          di.len = (unsigned)std::min<unsigned long long>(64u << 10, len - o2);
+          drain.push_back(di);
+        }
+      }
+    }
+
+  // ---- device copy: [expect[L] | items | drain] ----
   const size_t head = align_up(sizeof(unsigned long long) * L, 32);
-  const size_t bytes = head + std::max<size_t>(items.size(), 1) * sizeof(StaticItem);
+  const size_t items_bytes = std::max<size_t>(items.size(), 1) * sizeof(StaticItem);
+  const size_t bytes = head + items_bytes + drain.size() * sizeof(DrainItem);
   std::vector<char> blob(bytes, 0);
   std::memcpy(blob.data(), expect.data(), sizeof(unsigned long long) * L);
   if (!items.empty()) std::memcpy(blob.data() + head, items.data(), items.size() * sizeof(StaticItem));
+  if (!drain.empty()) std::memcpy(blob.data() + head + items_bytes, drain.data(), drain.size() * sizeof(DrainItem));
   RBV_CUDA_THROW(cudaMalloc(&out->owned_items, bytes));
   RBV_CUDA_THROW(cudaMemcpy(out->owned_items, blob.data(), bytes, cudaMemcpyHostToDevice));
 
@@ -760,6 +785,8 @@ int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const
   sa.nitems = (unsigned)items.size();
   sa.expect = static_cast<const unsigned long long*>(out->owned_items);
   sa.items = reinterpret_cast<const StaticItem*>(static_cast<char*>(out->owned_items) + head);
+  sa.drain = reinterpret_cast<const DrainItem*>(static_cast<char*>(out->owned_items) + head + items_bytes);
+  sa.ndrain = (unsigned)drain.size();
   sa.timeout_ns = timeout_ns_;
   sa.lay = lay_;
   for (int q = 0; q < nproc_; q++) sa.heap[q] = peer_[q];

@@ -36,12 +36,16 @@ struct CallOptions {
   unsigned flags = 0;                 // CALL_INPLACE
   unsigned long long eager_max_bytes = 0;  // > 0: eager protocol with cells of this payload size (same on all ranks)
   bool allow_static = true;           // persistent calls with host-side counts may resolve everything on the host
+  bool recv_anywhere = false;         // the caller has checked the receive extents itself: a static call of a
+                                      // single process may then receive into any device-accessible memory
 };
 
 // Arguments of one collective call for all L local ranks.  Count arrays are [L][P].
 struct CallArgs {
   const void* const* sendbufs = nullptr;   // [L] device pointers (ignored for in-place calls)
   void* const* recvbufs = nullptr;         // [L] device pointers inside the symmetric heap
+  void* const* recv_mirror = nullptr;      // [L] or null: where the caller wants each rank's received blocks in the end
+                                           // (any device-accessible memory; static calls copy them there in the kernel)
   const int* sendcounts = nullptr;
   const int* recvcounts = nullptr;         // may be null
   const long long* sdispls = nullptr;

@@ -219,6 +219,14 @@ struct KernelArgs {
 
 constexpr int kInlineItems = 128;  // the first items of a static call travel in the kernel parameters
 
+// One received block (or a piece of it) that the static kernel copies on, once everything has arrived, from the
+// receive buffer in the symmetric heap to the caller's own buffer (any device-accessible memory, e.g. pinned host
+// memory).
+struct alignas(16) DrainItem {
+  unsigned long long src, dst;
+  unsigned len, pad0, pad1, pad2;
+};
+
 // Arguments of the static rendezvous kernel (a2av_static.cu): a persistent call whose counts were all known on
 // the host.  Everything that depends on counts sits in the table behind `items`.
 struct StaticArgs {
@@ -228,6 +236,8 @@ struct StaticArgs {
   unsigned seq_hint, use_seq_hint;      // as in KernelArgs
   const StaticItem* items;              // issue order; item c is handled by warp c mod (warps in the grid)
   const unsigned long long* expect;     // [L] chunks that land in each local rank's receive buffer per call
+  const DrainItem* drain;               // copies made after the last arrival (receive buffers mirrored elsewhere)
+  unsigned ndrain, pad;
   unsigned long long timeout_ns;
   HeapLayout lay;
   char* heap[kMaxProcs];

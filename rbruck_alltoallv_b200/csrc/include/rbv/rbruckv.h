@@ -90,7 +90,9 @@ void* rbv_prepare(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, 
  * g_rdispls[d * P + s], g_recvoff[d] (byte offset of rank d's receive buffer in its process's heap).  With them a
  * call with host-side counts is resolved completely on the host and runs without a metadata phase; every
  * process must then pass them.  A process that hosts all ranks gets this from rbv_prepare already.
- * flags: bit 0 in-place, bit 8 keep the dynamic kernel even where the static one is possible. */
+ * flags: bit 0 in-place, bit 8 keep the dynamic kernel even where the static one is possible, bit 9 the receive
+ * buffers of a single-process static call may lie outside the symmetric heap (any device-accessible memory, pinned
+ * host memory included); the caller then answers for displacement + count staying inside them. */
 void* rbv_prepare_global(rbv_ctx_t ctx, int algo, int n, int r, int r2, int b, int b2, int type_size,
                          const void* const* sendbufs, void* const* recvbufs, const int* sendcounts,
                          const int* recvcounts, const long long* sdispls, const long long* rdispls,
@@ -127,6 +129,11 @@ void rbv_ctx_set_trace(rbv_ctx_t ctx, int on);       /* report phase time stamps
 void rbv_ctx_set_bulk(rbv_ctx_t ctx, int mode);      /* bulk-copy engine for large chunks: 0 off (default), 1 on, -1 by size */
 void rbv_ctx_set_cooperative(rbv_ctx_t ctx, int mode); /* -1 where a call needs it (default), 0 never, 1 always */
 void rbv_ctx_set_static(rbv_ctx_t ctx, int on);      /* 0: persistent calls keep the dynamic kernel */
+/* For the next rbv_prepare* only: mirrors[L] (null entries: none) name where each local rank wants its received
+ * blocks in the end, e.g. pinned host memory.  A call that runs the static kernel copies them there from the receive
+ * buffers itself once everything has arrived, so the end of the launch is the end of the whole transfer; other calls
+ * ignore it.  The caller answers for displacement + count staying inside the mirrors. */
+void rbv_ctx_set_recv_mirror(rbv_ctx_t ctx, void* const* mirrors);
 /* Time stamps (device clock, ns) per key of the schedule (a round, a batch; key = phase << 24 | step) of the most
  * recent traced call: earliest start and latest end over all warps of this process.  Returns the number filled. */
 int rbv_ctx_last_trace(rbv_ctx_t ctx, unsigned* keys, unsigned long long* start_ns, unsigned long long* end_ns, int max);

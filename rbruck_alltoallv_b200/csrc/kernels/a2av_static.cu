@@ -160,10 +160,21 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
       int r = alive ? dev::wait_ge(&my->recv_arrivals[i], target, wc, multi) : (int)dev::WAIT_ABORTED;
       if (r == dev::WAIT_TIMEOUT)
         static_error(a, RBV_ERR_TIMEOUT, WAIT_RECV, i, (int)(target - my->recv_arrivals[i]));
+      if (r != dev::WAIT_OK) alive = false;
     }
     // a process that was told to stop (or runs on a communicator that failed earlier and was not reset) says so;
     // where fewer than all threads wait above, the load overlaps with that wait
     if (tid == (int)blockDim.x - 1 && dev::ld_relaxed_sys(&my->abort_flag)) static_error(a, RBV_ERR_ABORTED, 0, 0, 0);
+    // Everything has arrived: received blocks the caller wants elsewhere (pinned host memory, say) are copied on by
+    // this CTA, whose 16 warps outrun a PCIe link; the end of the kernel then is the end of the whole transfer.
+    if (a.ndrain) {
+      const int all_ok = __syncthreads_and(alive ? 1 : 0);
+      if (all_ok)
+        for (unsigned c = warp; c < a.ndrain; c += warps_per_cta) {
+          const DrainItem di = a.drain[c];
+          dev::group_copy(reinterpret_cast<char*>(di.dst), reinterpret_cast<const char*>(di.src), di.len, lane, 32);
+        }
+    }
     __syncthreads();
     if (tid == 0) my->status.trace[4] = my->status.trace[7] = dev::globaltimer();
   }

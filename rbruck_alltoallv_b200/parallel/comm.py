@@ -53,8 +53,9 @@ class PreparedCall:
 
     KINDS = {0: "rendezvous", 1: "eager", 2: "static"}
 
-    def __init__(self, comm: "Communicator", handle, keep):
+    def __init__(self, comm: "Communicator", handle, keep, mirrored=None):
         self._comm, self._h, self._keep = comm, C.c_void_p(handle), keep
+        self._mirrored = mirrored or []      # (caller's tensor, symmetric stand-in) pairs, see Communicator.prepare
         self._launch = comm._lib.rbv_launch
         self._ctx = comm._ctx
         self._dev = comm.device
@@ -69,6 +70,10 @@ class PreparedCall:
         rc = self._launch(self._ctx, self._h, C.c_void_p(st.cuda_stream))
         if rc:
             raise CommError("launch failed: " + self._comm._lib.rbv_last_error().decode())
+        if self._mirrored and self.kind != "static":     # the static kernel has copied them on itself
+            with torch.cuda.stream(st):
+                for t, bt in self._mirrored:
+                    t.reshape(-1).view(torch.uint8).copy_(bt, non_blocking=True)
 
     __call__ = launch
 
@@ -412,33 +417,80 @@ class Communicator:
         With host-side counts the rendezvous protocol is resolved completely on the host: the processes gather
         each other's counts, displacements and buffer offsets over the host side group here, once, and every launch
         runs the static kernel, which has no metadata phase (``static=False`` or ``RBV_STATIC=0`` keeps the
-        kernel that exchanges metadata itself).  Collective over the processes."""
+        kernel that exchanges metadata itself).  Collective over the processes.
+
+        ``recv`` tensors outside the symmetric heap (pinned host memory, say) are accepted when the counts are on the
+        host (their extents are checked against the tensors here).  When one process hosts every rank the call has no
+        peers and addresses everything absolutely: every block goes from the send buffer to the receive buffer in one
+        copy.  Otherwise the call receives into symmetric stand-ins and the static kernel copies the received blocks
+        on to the tensors itself once everything has arrived, so that the end of the launch is the end of the whole
+        transfer (all processes must pass such tensors in the same positions).  ``send`` may be any
+        device-accessible memory in every case."""
         ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep = self._marshal(
             send, recv, sendcounts, sdispls, recvcounts, rdispls, type_size)
         algo_id = ALGO_ID[algo] if isinstance(algo, str) else int(algo)
-        self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
-        self._lib.rbv_ctx_set_bulk(self._ctx, int(self._bulk if bulk is None else bulk))
         if static is None:
             static = os.environ.get("RBV_STATIC", "1") != "0"
         flags = (1 if inplace else 0) | (0 if static else 0x100)
+        mirrored, mirror_ptrs = [], None
+        if not on_dev and not eager_max_bytes and not inplace and self._recv_extents_fit(recv, keep, ts):
+            if self.nproc == 1 and static:
+                flags |= 0x200   # receive buffers may be any device-accessible memory; extents checked here
+            else:
+                # Peers cannot store into memory outside the symmetric heap: the call receives into symmetric
+                # stand-ins and the received blocks are copied on to the caller's tensors (by the static kernel
+                # itself once everything has arrived, by copies after the launch otherwise).  Collective: every
+                # process must pass such tensors in the same positions.
+                recv_l = keep[1]
+                stand = []
+                for t in recv_l:
+                    if self._lib.rbv_ctx_in_heap(self._ctx, C.c_void_p(t.data_ptr()), max(t.numel() * t.element_size(), 1)):
+                        stand.append(t)
+                    else:
+                        bt = self._bounce_for(t)
+                        stand.append(bt)
+                        mirrored.append((t, bt))
+                mirror_ptrs = (C.c_void_p * self.L)(*[(t.data_ptr() if bt is not t else None)
+                                                      for t, bt in zip(recv_l, stand)])
+                ts, on_dev, sp, rp, (p_sc, p_rc, p_sd, p_rd), keep2 = self._marshal(
+                    send, stand, sendcounts, sdispls, recvcounts, rdispls, ts)
+                keep = keep2 + [keep, mirror_ptrs]
+        self._lib.rbv_ctx_set_eager(self._ctx, int(eager_max_bytes))
+        self._lib.rbv_ctx_set_bulk(self._ctx, int(self._bulk if bulk is None else bulk))
         g = (None, None, None, None)
         if self.nproc > 1 and not eager_max_bytes and not inplace:
-            g = self._gather_global(keep, on_dev or not static)
+            g = self._gather_global(keep, rp, on_dev or not static)
+        self._lib.rbv_ctx_set_recv_mirror(self._ctx, mirror_ptrs)
         h = self._lib.rbv_prepare_global(self._ctx, algo_id, n, r, r2, b, b2, ts, sp, rp, p_sc, p_rc, p_sd, p_rd,
                                          1 if on_dev else 0, int(bytes_hint), flags, int(grid), int(chunk_bytes), *g)
         if not h:
             raise CommError(f"prepare({algo}) failed: {self._lib.rbv_last_error().decode()}")
-        return PreparedCall(self, h, keep)
+        return PreparedCall(self, h, keep, mirrored)
 
-    def _gather_global(self, keep, opt_out: bool):
+    def _recv_extents_fit(self, recv, keep, ts: int) -> bool:
+        """True when some receive tensor lies outside the symmetric heap and every block of every rank
+        (displacement + count, from the host-side arrays of ``keep``) ends inside its tensor.  Only then may a
+        single-process static call be told that its receive buffers can be anywhere."""
+        recv_l = [recv] if isinstance(recv, torch.Tensor) else list(recv)
+        if all(self._lib.rbv_ctx_in_heap(self._ctx, C.c_void_p(t.data_ptr()), max(t.numel() * t.element_size(), 1))
+               for t in recv_l):
+            return False
+        sc, rc, rd = keep[2], keep[3], keep[5]
+        if rd is None or (rc is None and self.L != self.P):
+            return False
+        cnt = np.asarray(rc if rc is not None else np.asarray(sc).T, dtype=np.int64).reshape(self.L, self.P)
+        ext = ((np.asarray(rd, dtype=np.int64).reshape(self.L, self.P) + np.maximum(cnt, 0)) * ts).max(axis=1)
+        return all(int(ext[i]) <= t.numel() * t.element_size() for i, t in enumerate(recv_l))
+
+    def _gather_global(self, keep, rp, opt_out: bool):
         """All processes' host-side arguments of one call, as the four tables ``rbv_prepare_global`` takes (or four
         ``None`` when some process cannot take part: device-resident counts, static resolution switched off).
-        ``keep`` is the list :meth:`_marshal` built: ... sc, rc, sd, rd, send pointers, receive pointers."""
+        ``keep`` is the list :meth:`_marshal` built (..., sc, rc, sd, rd, ...), ``rp`` its receive pointers."""
         sc, rc, sd, rd = keep[2:6] if not opt_out else (None, None, None, None)
         mine = None
         if not opt_out:
             base = int(self._lib.rbv_ctx_heap(self._ctx, self.proc))
-            off = np.array([int(p) - base for p in keep[-1]], dtype=np.uint64)
+            off = np.array([int(p) - base for p in rp], dtype=np.uint64)
             mine = (sc, rc, rd, off)
         allv = [None] * self.nproc
         self._dist.all_gather_object(allv, mine, group=self._side)

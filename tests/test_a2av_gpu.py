@@ -121,6 +121,34 @@ def test_static_kernel_refuses_what_the_host_can_see():
         comm.alltoallv(send, recv, prob.counts, prob.sdispls, prob.recvcounts, rd, algo="spreadout", type_size=ts)
 
 
+def test_static_call_of_one_process_takes_pinned_host_buffers():
+    """One process hosting every rank: a static call may send from and receive into pinned host memory directly."""
+    from rbruck_alltoallv_b200.parallel.comm import CommError
+    P, ts = 8, 4
+    comm = get_comm(P)
+    counts = dist.zipf(P, 4096, seed=9)
+    prob = oracle.make_problem(counts, ts, 1, packed=False)
+    send_h = oracle.fill_send(prob, 1)
+    want = oracle.expected_recv(prob, send_h)
+    send = [torch.from_numpy(b.copy()).pin_memory() for b in send_h]
+    recv = [torch.full((len(w),), oracle.CANARY, dtype=torch.uint8).pin_memory() for w in want]
+    for algo, kw in (("spreadout", {}), ("rbruck", dict(r=2)), ("ttpl_bt_s1", dict(n=4, r=2))):
+        for t in recv:
+            t.fill_(oracle.CANARY)
+        call = comm.prepare(send, recv, prob.counts, prob.sdispls, prob.recvcounts, prob.rdispls, algo=algo,
+                            type_size=ts, **kw)
+        assert call.kind == "static"
+        call.launch()
+        comm.check()
+        bad = oracle.first_mismatch([t.numpy() for t in recv], want)
+        assert bad is None, f"{algo}: first mismatch at rank/offset {bad}"
+    # a displacement that leaves the tensor is refused: the extent check of the heap is replaced by one against the tensor
+    rd = prob.rdispls.copy()
+    rd[3, 0] += 1 << 30
+    with pytest.raises(CommError, match="heap"):
+        comm.prepare(send, recv, prob.counts, prob.sdispls, prob.recvcounts, rd, algo="spreadout", type_size=ts)
+
+
 def test_eager_cells_never_show_flags_of_an_earlier_life():
     """Eager units are valid by the call number in their flag words.  The cells must therefore never hold flag
     words that did not come from the current numbering: not from rendezvous staging of user payload (which may
