@@ -34,6 +34,7 @@ CUDA_SOURCES = [
     "kernels/grouped_gemm_pair_sm100.cu",
     "kernels/grouped_gemm_fp8_sm100.cu",
     "kernels/grouped_gemm_fp8_pair_sm100.cu",
+    "kernels/grouped_gemm_mxfp8_sm100.cu",
     "kernels/fft_transpose.cu",
     "kernels/noalloc.cu",
     "api/c_api.cu",

@@ -96,9 +96,12 @@ def declare_moe(lib):
     lib.rbv_grouped_gemm_pair_enabled.argtypes = []
     lib.rbv_grouped_gemm_fp8.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     lib.rbv_grouped_gemm_fp8_pair.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    lib.rbv_grouped_gemm_mxfp8.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    lib.rbv_quantize_rows_mxfp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_quantize_rows_fp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_moe_route.argtypes = [vp, i, i, vp, vp, vp, vp]
     lib.rbv_moe_layout.argtypes = [vp, i, i, i, vp, vp, vp, vp, vp, vp]
+    lib.rbv_moe_layout_aligned.argtypes = [vp, i, i, i, vp, vp, vp, vp, vp, i, vp]
     lib.rbv_moe_layout_streamed.argtypes = [vp, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp, i, vp, vp]
     lib.rbv_moe_dispatch_streamed.argtypes = [vp, vp, i, i, vp, vp, vp, vp, vp, ull, ull, ll, i, vp, vp]
     lib.rbv_grouped_gemm_bf16_gated.argtypes = [vp, ll, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp, vp, vp, C.c_double]

@@ -52,6 +52,18 @@ int rbv_grouped_gemm_fp8(const void* A, const float* a_scale_t, long long a_rows
 int rbv_grouped_gemm_fp8_pair(const void* A, const float* a_scale_t, long long a_rows, const void* B,
                               const float* b_scale, void* C, const int* group_start, const int* group_rows, int G,
                               int N, int K, int ldc, int epilogue, int* error_flag, int max_ctas, void* cuda_stream);
+/* MXFP8 variant: e4m3 operands with one UE8M0 (power-of-two) scale per 32 elements along K on both operands, applied
+ * by the tensor core (tcgen05.mma.kind::mxf8f6f4.block_scale) on CTA pairs.  Scales are packed four to a uint32 (the
+ * four 32-blocks of one 128-wide K block, lowest byte first); the words of 128 consecutive rows form one 512-byte atom
+ * in which row r sits at word (r % 32) * 4 + (r % 128) / 32:  sfa [K / 128][ceil(a_rows / 128)][128],
+ * sfb [G][K / 128][N / 128][128].  Every group with rows must start at a multiple of 128 rows (error flag 5
+ * otherwise).  N % 128 == 0, K % 128 == 0.  Output bf16; epilogue 0 plain, 1 SwiGLU. */
+int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb, void* C,
+                           const int* group_start, const int* group_rows, int G, int N, int K, int ldc, int epilogue,
+                           int* error_flag, int max_ctas, void* cuda_stream);
+/* bf16 [rows, K] (row stride ldx elements) -> e4m3 [rows, K] + sf [K / 128][ceil(rows / 128)][128] as above. */
+int rbv_quantize_rows_mxfp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, void* sf,
+                            void* cuda_stream);
 /* bf16 [rows, K] (row stride ldx elements) -> e4m3 [rows, K] + scale_t [K / 128][rows], scale = amax / 448. */
 int rbv_quantize_rows_fp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, float* scale_t,
                           void* cuda_stream);
@@ -66,6 +78,10 @@ int rbv_moe_route(const float* logits, int T, int E, int* topk_idx, float* topk_
  *   totals [2]     rows received by this rank, rows sent by this rank. */
 int rbv_moe_layout(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start, int* group_rows,
                    int* cursor, int* totals, void* cuda_stream);
+/* The same with every expert's rows starting at a multiple of `align` rows of the owner's buffer (the MXFP8 GEMM wants
+ * 128); the buffer then needs up to (E / P - 1) * (align - 1) rows more than it receives. */
+int rbv_moe_layout_aligned(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start,
+                           int* group_rows, int* cursor, int* totals, int align, void* cuda_stream);
 
 /* Dispatch: every routed (token, k) row of x [T, H] bf16 is stored straight into its expert-sorted row of the
  * owner GPU's receive buffer (`xrecv_off` = byte offset of that buffer inside every process's heap).  slot [T, 2]

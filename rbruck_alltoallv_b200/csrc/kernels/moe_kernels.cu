@@ -80,9 +80,10 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 // ---------------------------------------------------------------------------------------------
 // loc_off (optional): first index of this rank's rows for expert e in an expert-major ordering of its routed rows;
 // ready_target (optional): running totals of rows each local expert has been promised over all calls so far.
+// align: every expert's rows start at a multiple of `align` rows in the owner's buffer (1: packed).
 __global__ void moe_layout_kernel(const int* __restrict__ hist_all, int P, int E, int me, int* dst_base,
                                   int* group_start, int* group_rows, int* cursor, int* totals, int* loc_off,
-                                  unsigned long long* ready_target) {
+                                  unsigned long long* ready_target, int align) {
   __shared__ int s_tot[kMoeMaxExperts];      // rows of expert e over all sources
   __shared__ int s_before[kMoeMaxExperts];   // rows of expert e from sources < me
   const int El = E / P;
@@ -100,7 +101,7 @@ __global__ void moe_layout_kernel(const int* __restrict__ hist_all, int P, int E
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int owner = e / El;
     int base = 0;
-    for (int e2 = owner * El; e2 < e; e2++) base += s_tot[e2];
+    for (int e2 = owner * El; e2 < e; e2++) base += (s_tot[e2] + align - 1) / align * align;
     dst_base[e] = base + s_before[e];
     if (owner == me) {
       group_start[e - owner * El] = base; group_rows[e - owner * El] = s_tot[e];
@@ -362,12 +363,18 @@ int rbv_moe_route(const float* logits, int T, int E, int* topk_idx, float* topk_
   return (int)cudaGetLastError();
 }
 
+int rbv_moe_layout_aligned(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start,
+                           int* group_rows, int* cursor, int* totals, int align, void* stream) {
+  if (E > kMoeMaxExperts || E % P || align < 1) return (int)cudaErrorInvalidValue;
+  moe_layout_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(hist_all, P, E, me, dst_base, group_start,
+                                                                        group_rows, cursor, totals, nullptr, nullptr,
+                                                                        align);
+  return (int)cudaGetLastError();
+}
+
 int rbv_moe_layout(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start, int* group_rows,
                    int* cursor, int* totals, void* stream) {
-  if (E > kMoeMaxExperts || E % P) return (int)cudaErrorInvalidValue;
-  moe_layout_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(hist_all, P, E, me, dst_base, group_start,
-                                                                        group_rows, cursor, totals, nullptr, nullptr);
-  return (int)cudaGetLastError();
+  return rbv_moe_layout_aligned(hist_all, P, E, me, dst_base, group_start, group_rows, cursor, totals, 1, stream);
 }
 
 int rbv_moe_layout_streamed(const int* hist_all, int P, int E, int me, int* dst_base, int* group_start,
@@ -376,7 +383,7 @@ int rbv_moe_layout_streamed(const int* hist_all, int P, int E, int me, int* dst_
   if (E > kMoeMaxExperts || E % P) return (int)cudaErrorInvalidValue;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   moe_layout_kernel<<<1, 256, 0, st>>>(hist_all, P, E, me, dst_base, group_start, group_rows, cursor, totals, loc_off,
-                                       ready_target);
+                                       ready_target, 1);
   int grid = (2 * T + 255) / 256;
   grid = grid < 1 ? 1 : (grid > 592 ? 592 : grid);
   moe_order_kernel<<<grid, 256, 0, st>>>(topk_idx, 2 * T, loc_off, cursor, order);

@@ -132,6 +132,110 @@ def grouped_gemm_fp8(Aq: torch.Tensor, a_scale_t: torch.Tensor, Bq: torch.Tensor
     return out
 
 
+# ---- MXFP8: e4m3 with one power-of-two scale per 32 elements along K on both operands, scaled by the tensor core ----
+def quantize_rows_mxfp8(x: torch.Tensor):
+    """bf16 [rows, K] -> (e4m3 bytes [rows, K], scale words [K // 128, ceil(rows / 128) * 128] int32 in atom order, see
+    :func:`mx_to_atoms`): per row and 32 columns one UE8M0 scale 2^(byte - 127) >= amax / 448; the four bytes of a
+    128-column block share a word, lowest byte first."""
+    lib = _native.cuda_lib()
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 128 == 0
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(K // 128, (rows + 127) // 128 * 128, dtype=torch.int32, device=x.device)
+    st = torch.cuda.current_stream(x.device).cuda_stream
+    rc = lib.rbv_quantize_rows_mxfp8(_p(x), rows, K, x.stride(0), _p(q), _p(sf), C.c_void_p(st))
+    if rc:
+        raise RuntimeError(f"MXFP8 quantisation launch failed (CUDA error {rc})")
+    return q, sf
+
+
+def _mx_atom_perm(n: int, device) -> torch.Tensor:
+    """Position of row r (r < n, n a multiple of 128) in the atom order of the GEMM's scale words:
+    (r // 128) * 128 + (r % 32) * 4 + (r % 128) // 32."""
+    r = torch.arange(n, device=device)
+    return (r // 128) * 128 + (r % 32) * 4 + (r % 128) // 32
+
+
+def mx_to_atoms(plain: torch.Tensor) -> torch.Tensor:
+    """Scale words with rows along the last dimension (padded to a multiple of 128 with the scale 1.0) -> atom order."""
+    n = plain.shape[-1]
+    npad = (n + 127) // 128 * 128
+    out = torch.full(plain.shape[:-1] + (npad,), 0x7f7f7f7f, dtype=torch.int32, device=plain.device)
+    out[..., _mx_atom_perm(npad, plain.device)[:n]] = plain.to(torch.int32)
+    return out.contiguous()
+
+
+def mx_from_atoms(atoms: torch.Tensor, n: int) -> torch.Tensor:
+    """Inverse of :func:`mx_to_atoms`: the words of rows 0..n-1 in row order."""
+    return atoms[..., _mx_atom_perm(atoms.shape[-1], atoms.device)[:n]].contiguous()
+
+
+def _mx_exponents(amax: torch.Tensor) -> torch.Tensor:
+    """ceil(log2(amax / 448)) as int32, 0 where amax == 0 (plain torch; used for weights and as the test oracle)."""
+    t = amax.float() / 448.0
+    m, e = torch.frexp(torch.where(t > 0, t, torch.ones_like(t)))       # t = m * 2^e, m in [0.5, 1)
+    e = torch.where(m == 0.5, e - 1, e)
+    return torch.where(t > 0, e, torch.zeros_like(e)).clamp(-127, 127).to(torch.int32)
+
+
+def quantize_weight_mxfp8(w: torch.Tensor):
+    """bf16 / fp32 [G, N, K] -> (e4m3 bytes [G, N, K], scale words [G, K // 128, N] int32 in atom order along N), one
+    scale per weight row and 32 columns."""
+    G, N, K = w.shape
+    blk = w.float().view(G, N, K // 32, 32)
+    e = _mx_exponents(blk.abs().amax(dim=3))                                # [G, N, K/32]
+    q = (blk * torch.exp2(-e.float())[..., None]).to(torch.float8_e4m3fn).view(G, N, K)
+    b = (e.to(torch.int64) + 127).view(G, N, K // 128, 4)
+    words = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16) | (b[..., 3] << 24)      # [G, N, K/128]
+    return q.view(torch.uint8).contiguous(), mx_to_atoms(words.permute(0, 2, 1).contiguous())
+
+
+def _mx_scales(words: torch.Tensor) -> torch.Tensor:
+    """int32 words [..., n] -> fp32 scales [..., n, 4] (byte j = 32-block j of the word's 128 columns)."""
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    b = torch.stack([(w >> (8 * j)) & 0xFF for j in range(4)], dim=-1)
+    return torch.exp2(b.float() - 127.0)
+
+
+def dequantize_rows_mxfp8(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    rows, K = q.shape
+    sc = _mx_scales(mx_from_atoms(sf, rows)).permute(1, 0, 2).reshape(rows, K // 32)             # [rows, K/32]
+    return (q.view(torch.float8_e4m3fn).float().view(rows, K // 32, 32) * sc[:, :, None]).view(rows, K)
+
+
+def dequantize_weight_mxfp8(q: torch.Tensor, sf: torch.Tensor) -> torch.Tensor:
+    G, N, K = q.shape
+    sc = _mx_scales(mx_from_atoms(sf, N)).permute(0, 2, 1, 3).reshape(G, N, K // 32)          # [G, N, K/32]
+    return (q.view(torch.float8_e4m3fn).float().view(G, N, K // 32, 32) * sc[..., None]).view(G, N, K)
+
+
+def grouped_gemm_mxfp8(Aq: torch.Tensor, sfa: torch.Tensor, Bq: torch.Tensor, sfb: torch.Tensor,
+                       group_start: torch.Tensor, group_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
+                       swiglu: bool = False, error: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
+    """MXFP8 grouped GEMM on CTA pairs with hardware block scaling (``csrc/kernels/grouped_gemm_mxfp8_sm100.cu``);
+    operands and scale words as the ``quantize_*_mxfp8`` functions make them; every group with rows must start at a
+    multiple of 128 rows; bf16 output."""
+    lib = _native.cuda_lib()
+    G, N, K = Bq.shape
+    M = Aq.shape[0]
+    assert Aq.dtype == torch.uint8 and Bq.dtype == torch.uint8 and Aq.is_contiguous() and Bq.is_contiguous()
+    assert sfa.shape == (K // 128, (M + 127) // 128 * 128) and sfb.shape == (G, K // 128, N)
+    assert sfa.is_contiguous() and sfb.is_contiguous()
+    assert sfa.dtype == torch.int32 and sfb.dtype == torch.int32
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(M, n_out, dtype=torch.bfloat16, device=Aq.device)
+    if error is None:
+        error = torch.zeros(1, dtype=torch.int32, device=Aq.device)
+    st = torch.cuda.current_stream(Aq.device).cuda_stream
+    rc = lib.rbv_grouped_gemm_mxfp8(_p(Aq), _p(sfa), M, _p(Bq), _p(sfb), _p(out), _p(group_start), _p(group_rows),
+                                    G, N, K, out.stride(0), 1 if swiglu else 0, _p(error), int(max_ctas),
+                                    C.c_void_p(st))
+    if rc:
+        raise RuntimeError(f"MXFP8 grouped GEMM launch failed (CUDA error {rc})")
+    return out
+
+
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Interleaves [G, I, H] gate and up weights into the [G, 2I, H] layout the SwiGLU epilogue expects."""
     G, I, H = gate.shape
@@ -157,11 +261,15 @@ class MoEExpertParallel:
         bf = torch.bfloat16
         self.w13 = (torch.randn(self.El, 2 * inter, hidden, device=dev, generator=g) * init_std).to(bf)
         self.w2 = (torch.randn(self.El, hidden, inter, device=dev, generator=g) * init_std).to(bf)
+        self.mx = fp8 == "mx"          # MXFP8: power-of-two scales per 32 elements, applied by the tensor core
         self.fp8 = bool(fp8)
-        if self.fp8:   # expert weights as e4m3 with one scale per 128 x 128 block
+        if self.mx:
+            self.w13_q, self.w13_s = quantize_weight_mxfp8(self.w13)
+            self.w2_q, self.w2_s = quantize_weight_mxfp8(self.w2)
+        elif self.fp8:   # expert weights as e4m3 with one scale per 128 x 128 block
             self.w13_q, self.w13_s = quantize_weight_blocks_fp8(self.w13)
             self.w2_q, self.w2_s = quantize_weight_blocks_fp8(self.w2)
-        self.cap = int(np.ceil(capacity_factor * 2 * tokens / 128.0)) * 128
+        self.cap = int(np.ceil(capacity_factor * 2 * tokens / 128.0)) * 128 + (128 * self.El if self.mx else 0)
         i32 = torch.int32
         self.xrecv = comm.symm_empty((self.cap, hidden), bf)
         self.y = comm.symm_empty((self.cap, hidden), bf)
@@ -222,13 +330,21 @@ class MoEExpertParallel:
         self._gather.launch()
         if self.overlap:
             return self._forward_streamed(x, out, st)
-        self._check(lib.rbv_moe_layout(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
-                                       _p(self.group_start), _p(self.group_rows), _p(self.cursor), _p(self.totals),
-                                       st), "layout")
+        # the MXFP8 GEMM wants every expert's rows to start at a multiple of 128 rows (its scale atoms)
+        self._check(lib.rbv_moe_layout_aligned(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
+                                               _p(self.group_start), _p(self.group_rows), _p(self.cursor),
+                                               _p(self.totals), 128 if self.mx else 1, st), "layout")
         self._check(lib.rbv_moe_dispatch(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base), _p(self.cursor),
                                          _p(self.slot), self.xrecv_off, self.cap, self.E, _p(self.error[0:1]), st),
                     "dispatch")
-        if self.fp8:
+        if self.mx:
+            xq, xs = quantize_rows_mxfp8(self.xrecv)
+            grouped_gemm_mxfp8(xq, xs, self.w13_q, self.w13_s, self.group_start, self.group_rows, out=self.h,
+                               swiglu=True, error=self.error[1:2])
+            hq, hs = quantize_rows_mxfp8(self.h)
+            grouped_gemm_mxfp8(hq, hs, self.w2_q, self.w2_s, self.group_start, self.group_rows, out=self.y,
+                               error=self.error[2:3])
+        elif self.fp8:
             # activations are quantised row-wise (1 x 128 blocks) right before each GEMM
             xq, xs = quantize_rows_fp8(self.xrecv)
             grouped_gemm_fp8(xq, xs, self.w13_q, self.w13_s, self.group_start, self.group_rows, out=self.h, swiglu=True,

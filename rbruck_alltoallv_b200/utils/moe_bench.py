@@ -58,6 +58,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--fp8", action="store_true", help="expert GEMMs in block-scaled e4m3 (1x128 / 128x128 scales)")
+    ap.add_argument("--mx", action="store_true",
+                    help="expert GEMMs in MXFP8 (e4m3, power-of-two scales per 32 elements, scaled by the tensor core)")
     ap.add_argument("--check", action="store_true", help="compare with the fp32 reference (small sizes only)")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
@@ -71,7 +73,7 @@ def main() -> int:
     heap = 2 * cap_rows * H * 2 + (64 << 20)
     comm = Communicator(nranks=world, heap_bytes=heap, arena_bytes=1 << 20)
     E = El * world
-    layer = MoEExpertParallel(comm, E, H, I, T, seed=3, fp8=a.fp8)
+    layer = MoEExpertParallel(comm, E, H, I, T, seed=3, fp8="mx" if a.mx else a.fp8)
     g = torch.Generator(device="cuda")
     g.manual_seed(100 + comm.proc)
     x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
@@ -80,7 +82,7 @@ def main() -> int:
     layer.forward(x, logits, out)
     layer.check()
     rows = int(layer.totals[0].item())
-    res = {"gpus": world, "expert_gemm_dtype": "fp8_e4m3_block_scaled" if a.fp8 else "bf16", "tokens_per_gpu": T, "hidden": H, "inter": I, "experts": E, "rows_received_rank0": rows}
+    res = {"gpus": world, "expert_gemm_dtype": "mxfp8" if a.mx else ("fp8_e4m3_block_scaled" if a.fp8 else "bf16"), "tokens_per_gpu": T, "hidden": H, "inter": I, "experts": E, "rows_received_rank0": rows}
     if a.check:
         if world > 1:
             w13 = [torch.empty_like(layer.w13) for _ in range(world)]
@@ -94,11 +96,21 @@ def main() -> int:
         err = (out.float() - ref).abs().max().item()
         res["max_abs_err"] = err
         res["ref_scale"] = ref.abs().max().item()
-        tol = 0.25 if a.fp8 else 0.02      # fp8 operands: compared against the unquantised bf16 weights
+        tol = 0.25 if (a.fp8 or a.mx) else 0.02      # fp8 operands: compared against the unquantised bf16 weights
         res["check"] = "ok" if err <= tol * res["ref_scale"] + 1e-3 else "FAILED"
     t_all = _time(lambda: layer.forward(x, logits, out), a.steps, a.warmup)
     layer.check()
-    if a.fp8:
+    if a.mx:
+        from ..ops.moe import grouped_gemm_mxfp8, quantize_rows_mxfp8
+        xq, xs = quantize_rows_mxfp8(layer.xrecv)
+        hq, hs = quantize_rows_mxfp8(layer.h)
+        t_q = _time(lambda: quantize_rows_mxfp8(layer.xrecv), a.steps, a.warmup)
+        res["ms_quantize_x"] = float(np.median(t_q))
+        t_g1 = _time(lambda: grouped_gemm_mxfp8(xq, xs, layer.w13_q, layer.w13_s, layer.group_start, layer.group_rows,
+                                                out=layer.h, swiglu=True, error=layer.error[1:2]), a.steps, a.warmup)
+        t_g2 = _time(lambda: grouped_gemm_mxfp8(hq, hs, layer.w2_q, layer.w2_s, layer.group_start, layer.group_rows,
+                                                out=layer.y, error=layer.error[2:3]), a.steps, a.warmup)
+    elif a.fp8:
         from ..ops.moe import grouped_gemm_fp8, quantize_rows_fp8
         xq, xs = quantize_rows_fp8(layer.xrecv)
         hq, hs = quantize_rows_fp8(layer.h)

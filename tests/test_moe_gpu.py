@@ -6,6 +6,17 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+def _groups_aligned(rows, device, align=128):
+    """Group starts at multiples of `align` rows; returns (start, rows, rows of the whole buffer)."""
+    start, at = [], 0
+    for n in rows:
+        start.append(at)
+        at += (n + align - 1) // align * align
+    total = start[-1] + rows[-1] if rows else 0
+    return (torch.tensor(start, dtype=torch.int32, device=device),
+            torch.tensor(rows, dtype=torch.int32, device=device), max(total, 1), start)
+
+
 def _groups(rows, device):
     start = np.concatenate([[0], np.cumsum(rows)[:-1]]).astype(np.int32)
     return (torch.from_numpy(start).to(device), torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(device))
@@ -134,6 +145,132 @@ def test_grouped_gemm_fp8_coarse_scales(pair):
             for got in (fine[r0:r0 + n].float(), coarse[r0:r0 + n].float()):
                 assert (got - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-3, f"group {g}"
         r0 += n
+
+
+def test_mxfp8_quantiser_matches_the_torch_recipe():
+    from rbruck_alltoallv_b200.ops import moe
+    torch.manual_seed(11)
+    x = (torch.randn(300, 256, device="cuda") * torch.rand(300, 1, device="cuda") * 5).to(torch.bfloat16)
+    x[7] = 0
+    x[9, :32] = 448.0          # amax / 448 an exact power of two
+    q, sf = moe.quantize_rows_mxfp8(x)
+    torch.cuda.synchronize()
+    e = moe._mx_exponents(x.float().view(300, 8, 32).abs().amax(dim=2))            # [rows, K/32]
+    want_bytes = (e.to(torch.int64) + 127).view(300, 2, 4)
+    want_words = (want_bytes[..., 0] | (want_bytes[..., 1] << 8) | (want_bytes[..., 2] << 16) | (want_bytes[..., 3] << 24))
+    assert torch.equal(moe.mx_from_atoms(sf, 300).t().contiguous(), want_words.to(torch.int32))
+    d = moe.dequantize_rows_mxfp8(q, sf)
+    assert (d - x.float()).abs().max().item() <= 0.07 * x.float().abs().max().item()
+    # per-block relative error of e4m3 with a scale that keeps amax in (224, 448]: at most 2^-4 of the block's amax
+    blk_err = (d - x.float()).view(300, 8, 32).abs().amax(dim=2)
+    blk_max = x.float().view(300, 8, 32).abs().amax(dim=2)
+    assert torch.all(blk_err <= blk_max / 16 + 1e-6)
+
+
+@pytest.mark.parametrize("scales", ["ones", "rows", "kblocks", "columns", "real"])
+def test_grouped_gemm_mxfp8_scale_paths(scales):
+    """Hardware block scaling, one source of scale variation at a time: no scaling at all, per activation row, per
+    32-block of K, per weight row, and the quantisers' own scales."""
+    from rbruck_alltoallv_b200.ops import moe
+    torch.manual_seed(21)
+    rows, N, K = [300, 0, 129, 700], 256, 512
+    G = len(rows)
+    gs, gr, M, starts = _groups_aligned(rows, "cuda")
+    if scales == "real":
+        A = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 3).to(torch.bfloat16)
+        B = (torch.randn(G, N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        Aq, sfa = moe.quantize_rows_mxfp8(A)
+        Bq, sfb = moe.quantize_weight_mxfp8(B)
+    else:
+        Aq = torch.randn(M, K, device="cuda").clamp(-3, 3).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+        Bq = torch.randn(G, N, K, device="cuda").clamp(-3, 3).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+        ea = torch.zeros(K // 32, M, dtype=torch.int32, device="cuda")          # exponents, [K/32][rows]
+        eb = torch.zeros(G, K // 32, N, dtype=torch.int32, device="cuda")
+        if scales == "rows":
+            ea += (torch.arange(M, device="cuda", dtype=torch.int32) % 7 - 3)[None, :]
+        elif scales == "kblocks":
+            ea += (torch.arange(K // 32, device="cuda", dtype=torch.int32) % 5 - 2)[:, None]
+            eb += (torch.arange(K // 32, device="cuda", dtype=torch.int32) % 3 - 1)[None, :, None]
+        elif scales == "columns":
+            eb += (torch.arange(N, device="cuda", dtype=torch.int32) % 9 - 4)[None, None, :]
+
+        def pack(e4):
+            b = e4.to(torch.int64) + 127
+            return b[..., 0, :] | (b[..., 1, :] << 8) | (b[..., 2, :] << 16) | (b[..., 3, :] << 24)
+        sfa = moe.mx_to_atoms(pack(ea.view(K // 128, 4, M)))
+        sfb = moe.mx_to_atoms(pack(eb.view(G, K // 128, 4, N)))
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    moe.grouped_gemm_mxfp8(Aq, sfa, Bq, sfb, gs, gr, out=out, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    Ad, Bd = moe.dequantize_rows_mxfp8(Aq, sfa), moe.dequantize_weight_mxfp8(Bq, sfb)
+    used = torch.zeros(M, dtype=torch.bool, device="cuda")
+    for g, n in enumerate(rows):
+        r0 = starts[g]
+        used[r0:r0 + n] = True
+        if n:
+            ref = Ad[r0:r0 + n] @ Bd[g].t()
+            got = out[r0:r0 + n].float()
+            assert (got - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 1e-3, f"group {g} ({scales})"
+    assert torch.all(out[~used] == 7.0), "rows between the groups must stay untouched"
+
+
+def test_grouped_gemm_mxfp8_refuses_unaligned_groups():
+    from rbruck_alltoallv_b200.ops import moe
+    rows, N, K = [100, 50], 128, 128
+    gs, gr = _groups(rows, "cuda")                      # the second group starts at row 100
+    Aq = torch.zeros(150, K, dtype=torch.uint8, device="cuda")
+    Bq = torch.zeros(2, N, K, dtype=torch.uint8, device="cuda")
+    sfa = moe.mx_to_atoms(torch.full((K // 128, 150), 0x7f7f7f7f, dtype=torch.int32, device="cuda"))
+    sfb = moe.mx_to_atoms(torch.full((2, K // 128, N), 0x7f7f7f7f, dtype=torch.int32, device="cuda"))
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    moe.grouped_gemm_mxfp8(Aq, sfa, Bq, sfb, gs, gr, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 5
+
+
+def test_grouped_gemm_mxfp8_many_tiles_and_swiglu():
+    from rbruck_alltoallv_b200.ops import moe
+    torch.manual_seed(22)
+    rows, I, K = [1500, 129, 700], 1024, 2048
+    G = len(rows)
+    gs, gr, M, starts = _groups_aligned(rows, "cuda")
+    A = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 2).to(torch.bfloat16)
+    gate = (torch.randn(G, I, K, device="cuda") * 0.03).to(torch.bfloat16)
+    up = (torch.randn(G, I, K, device="cuda") * 0.03).to(torch.bfloat16)
+    Aq, sfa = moe.quantize_rows_mxfp8(A)
+    Bq, sfb = moe.quantize_weight_mxfp8(moe.pack_gate_up(gate, up))
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = moe.grouped_gemm_mxfp8(Aq, sfa, Bq, sfb, gs, gr, swiglu=True, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    Ad, Bd = moe.dequantize_rows_mxfp8(Aq, sfa), moe.dequantize_weight_mxfp8(Bq, sfb)
+    for g, n in enumerate(rows):
+        r0 = starts[g]
+        a = Ad[r0:r0 + n]
+        ref = torch.nn.functional.silu(a @ Bd[g, 0::2].t()) * (a @ Bd[g, 1::2].t())
+        assert (out[r0:r0 + n].float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3, f"group {g}"
+
+
+def test_moe_layer_mxfp8_close_to_bf16():
+    from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    comm = Communicator(nranks=1, heap_bytes=256 << 20, arena_bytes=1 << 20)
+    try:
+        T, H, I, E = 512, 512, 1024, 4
+        layer = MoEExpertParallel(comm, E, H, I, T, seed=5, fp8="mx")
+        g = torch.Generator(device="cuda")
+        g.manual_seed(17)
+        x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda", generator=g)
+        out = layer.forward(x, logits)
+        layer.check()
+        ref, _, _ = reference_forward(x, logits, layer.w13, layer.w2)
+        rel = (out.float() - ref).norm().item() / ref.norm().item()
+        assert rel < 0.08, f"MXFP8 layer deviates {rel:.3f} from the bf16 reference"
+    finally:
+        comm.close()
 
 
 def test_moe_layer_fp8_close_to_bf16():
