@@ -97,6 +97,7 @@ def declare_moe(lib):
     lib.rbv_grouped_gemm_fp8.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     lib.rbv_grouped_gemm_fp8_pair.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
     lib.rbv_grouped_gemm_mxfp8.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, i, i, i, i, i, vp, i, vp]
+    lib.rbv_grouped_gemm_mxfp8_swiglu_q.argtypes = [vp, vp, ll, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, i, vp]
     lib.rbv_quantize_rows_mxfp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_quantize_rows_fp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_moe_route.argtypes = [vp, i, i, vp, vp, vp, vp]

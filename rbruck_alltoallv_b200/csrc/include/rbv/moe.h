@@ -61,6 +61,12 @@ int rbv_grouped_gemm_fp8_pair(const void* A, const float* a_scale_t, long long a
 int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb, void* C,
                            const int* group_start, const int* group_rows, int G, int N, int K, int ldc, int epilogue,
                            int* error_flag, int max_ctas, void* cuda_stream);
+/* The up/gate GEMM with the SwiGLU epilogue AND the quantiser of the next GEMM fused: Cq is e4m3 [*, N / 2] (row
+ * stride ldc_bytes) and sf_out its scale words, [N / 256][ceil(a_rows / 128)][128] in the atom order above, i.e. what
+ * rbv_quantize_rows_mxfp8 would make of the bf16 result.  N % 256 == 0. */
+int rbv_grouped_gemm_mxfp8_swiglu_q(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb,
+                                    void* Cq, void* sf_out, const int* group_start, const int* group_rows, int G,
+                                    int N, int K, int ldc_bytes, int* error_flag, int max_ctas, void* cuda_stream);
 /* bf16 [rows, K] (row stride ldx elements) -> e4m3 [rows, K] + sf [K / 128][ceil(rows / 128)][128] as above. */
 int rbv_quantize_rows_mxfp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, void* sf,
                             void* cuda_stream);

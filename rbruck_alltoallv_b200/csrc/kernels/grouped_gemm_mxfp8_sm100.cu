@@ -56,8 +56,10 @@ struct MxParams {
   int G, N, K, ldc;
   int a_row_blocks;            // ceil(a_rows / 128): scale atoms of A per K block
   void* C;
+  uint32_t* sf_out;            // epilogue 3: scale words of the quantised output, [N / 256][a_row_blocks][128]
   int* error;
-  int epilogue;                // 0: C = bf16(acc); 1: SwiGLU over interleaved gate / up columns
+  int epilogue;                // 0: C = bf16(acc); 1: SwiGLU over interleaved gate / up columns, bf16;
+                               // 3: SwiGLU, then MXFP8 again: C is e4m3 [*, N / 2] (ldc in bytes) with sf_out
 };
 
 struct XTile { int g, m0, n0, rows; bool valid; };
@@ -244,6 +246,54 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __gri
       const int my_m0 = tl.m0 + (int)rank * XHM;
       const bool live = row < tl.rows - (int)rank * XHM;
       __nv_bfloat16* crow = C + (size_t)(my_m0 + row) * p.ldc;
+      if (p.epilogue == 3) {
+        // SwiGLU, then the quantiser of the next GEMM's A operand, fused: the 64 outputs of this thread's row are two
+        // blocks of 32; each gets its power-of-two scale from the row's own values (no other thread is involved)
+        uint8_t* qrow = static_cast<uint8_t*>(p.C) + (size_t)(my_m0 + row) * p.ldc + tl.n0 / 2;
+        uint32_t sbytes = 0;
+        #pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+          float o[32];
+          #pragma unroll
+          for (int cc = 0; cc < 2; cc++) {
+            uint32_t r[32];
+            tmem_ld32(taddr + half * 64 + cc * 32, r);
+            tmem_ld_wait();
+            #pragma unroll
+            for (int j = 0; j < 16; j++)
+              o[cc * 16 + j] = silu_x(__uint_as_float(r[2 * j])) * __uint_as_float(r[2 * j + 1]);
+          }
+          float m = 0.0f;
+          #pragma unroll
+          for (int j = 0; j < 32; j++) m = fmaxf(m, fabsf(o[j]));
+          int e = 0;
+          if (m > 0.0f && m < 3.0e38f) {
+            int ex;
+            const float fr = frexpf(m * (1.0f / 448.0f), &ex);
+            e = (fr == 0.5f) ? ex - 1 : ex;
+            e = max(-127, min(127, e));
+          }
+          const float inv = exp2f((float)-e);
+          sbytes |= (uint32_t)(e + 127) << (8 * half);
+          uint32_t w[8];
+          #pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * j] * inv, o[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * j + 2] * inv, o[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+            w[j] = lo | (hi << 16);
+          }
+          if (live) {
+            uint4* dst = reinterpret_cast<uint4*>(qrow + half * 32);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        }
+        if (live) {
+          const unsigned R = (unsigned)(my_m0 + row);
+          uint32_t* word = p.sf_out + ((size_t)(tl.n0 / 256) * p.a_row_blocks + R / 128) * 128 + (R % 32) * 4 + (R % 128) / 32;
+          *reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(word) + ((tl.n0 / 64) & 3)) = (uint16_t)sbytes;
+        }
+      } else
       #pragma unroll 1
       for (int c = 0; c < XN; c += 32) {
         uint32_t r[32];
@@ -413,11 +463,13 @@ bool make_map_atoms(CUtensorMap* m, const void* base, unsigned long long atoms) 
 }  // namespace
 }  // namespace rbv
 
-extern "C" int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb,
-                                      void* C, const int* group_start, const int* group_rows, int G, int N, int K,
-                                      int ldc, int epilogue, int* error_flag, int max_ctas, void* cuda_stream) {
+static int launch_mxfp8(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb, void* C,
+                        void* sf_out, const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
+                        int epilogue, int* error_flag, int max_ctas, void* cuda_stream) {
   using namespace rbv;
   if (G < 1 || G > kMoeMaxGroups || N % XN || K % XK || a_rows < 1 || (ldc % 8)) return (int)cudaErrorInvalidValue;
+  if (epilogue == 3 && (!sf_out || N % 256 || ldc % 16 || (reinterpret_cast<uintptr_t>(sf_out) & 15)))
+    return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(sfa) | reinterpret_cast<uintptr_t>(sfb)) & 15) return (int)cudaErrorInvalidValue;
@@ -437,7 +489,7 @@ extern "C" int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long 
   MxParams p;
   p.group_start = group_start; p.group_rows = group_rows; p.G = G; p.N = N; p.K = K; p.ldc = ldc;
   p.a_row_blocks = (int)nrb;
-  p.C = C; p.error = error_flag; p.epilogue = epilogue;
+  p.C = C; p.sf_out = static_cast<uint32_t*>(sf_out); p.error = error_flag; p.epilogue = epilogue;
   int grid = max_ctas;
   if (grid <= 0) {
     int dev = 0;
@@ -448,6 +500,22 @@ extern "C" int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long 
   if (grid < 2) return (int)cudaErrorInvalidValue;
   grouped_gemm_mxfp8_kernel<<<grid, XTHREADS, XSMEM, static_cast<cudaStream_t>(cuda_stream)>>>(ma, mb, msa, msb, p);
   return (int)cudaGetLastError();
+}
+
+extern "C" int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb,
+                                      void* C, const int* group_start, const int* group_rows, int G, int N, int K,
+                                      int ldc, int epilogue, int* error_flag, int max_ctas, void* cuda_stream) {
+  if (epilogue != 0 && epilogue != 1) return (int)cudaErrorInvalidValue;
+  return launch_mxfp8(A, sfa, a_rows, B, sfb, C, nullptr, group_start, group_rows, G, N, K, ldc, epilogue, error_flag,
+                      max_ctas, cuda_stream);
+}
+
+extern "C" int rbv_grouped_gemm_mxfp8_swiglu_q(const void* A, const void* sfa, long long a_rows, const void* B,
+                                               const void* sfb, void* Cq, void* sf_out, const int* group_start,
+                                               const int* group_rows, int G, int N, int K, int ldc_bytes,
+                                               int* error_flag, int max_ctas, void* cuda_stream) {
+  return launch_mxfp8(A, sfa, a_rows, B, sfb, Cq, sf_out, group_start, group_rows, G, N, K, ldc_bytes, 3, error_flag,
+                      max_ctas, cuda_stream);
 }
 
 extern "C" int rbv_quantize_rows_mxfp8(const void* x_bf16, long long rows, int K, int ldx, void* out_fp8, void* sf,

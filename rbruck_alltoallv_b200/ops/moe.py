@@ -236,6 +236,35 @@ def grouped_gemm_mxfp8(Aq: torch.Tensor, sfa: torch.Tensor, Bq: torch.Tensor, sf
     return out
 
 
+def grouped_gemm_mxfp8_swiglu_q(Aq: torch.Tensor, sfa: torch.Tensor, Bq: torch.Tensor, sfb: torch.Tensor,
+                                group_start: torch.Tensor, group_rows: torch.Tensor,
+                                out_q: Optional[torch.Tensor] = None, out_sf: Optional[torch.Tensor] = None,
+                                error: Optional[torch.Tensor] = None, max_ctas: int = 0):
+    """The MXFP8 up/gate GEMM with SwiGLU and the quantiser of the next GEMM fused into its epilogue: returns
+    ``(hq, hs)``, e4m3 bytes [M, N // 2] and their scale words [N // 256, ceil(M / 128) * 128] in atom order, i.e. what
+    :func:`quantize_rows_mxfp8` would make of the bf16 result, without that result ever going to memory."""
+    lib = _native.cuda_lib()
+    G, N, K = Bq.shape
+    M = Aq.shape[0]
+    assert N % 256 == 0 and Aq.dtype == torch.uint8 and Bq.dtype == torch.uint8 and Aq.is_contiguous() and Bq.is_contiguous()
+    mp = (M + 127) // 128 * 128
+    assert sfa.shape == (K // 128, mp) and sfb.shape == (G, K // 128, N) and sfa.is_contiguous() and sfb.is_contiguous()
+    if out_q is None:
+        out_q = torch.empty(M, N // 2, dtype=torch.uint8, device=Aq.device)
+    if out_sf is None:
+        out_sf = torch.empty(N // 256, mp, dtype=torch.int32, device=Aq.device)
+    assert out_q.shape == (M, N // 2) and out_q.stride(1) == 1 and out_sf.shape == (N // 256, mp) and out_sf.is_contiguous()
+    if error is None:
+        error = torch.zeros(1, dtype=torch.int32, device=Aq.device)
+    st = torch.cuda.current_stream(Aq.device).cuda_stream
+    rc = lib.rbv_grouped_gemm_mxfp8_swiglu_q(_p(Aq), _p(sfa), M, _p(Bq), _p(sfb), _p(out_q), _p(out_sf),
+                                             _p(group_start), _p(group_rows), G, N, K, out_q.stride(0), _p(error),
+                                             int(max_ctas), C.c_void_p(st))
+    if rc:
+        raise RuntimeError(f"MXFP8 grouped GEMM launch failed (CUDA error {rc})")
+    return out_q, out_sf
+
+
 def pack_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """Interleaves [G, I, H] gate and up weights into the [G, 2I, H] layout the SwiGLU epilogue expects."""
     G, I, H = gate.shape
@@ -338,10 +367,20 @@ class MoEExpertParallel:
                                          _p(self.slot), self.xrecv_off, self.cap, self.E, _p(self.error[0:1]), st),
                     "dispatch")
         if self.mx:
+            # activations are quantised once; the first GEMM's epilogue (SwiGLU) hands the second GEMM its operand
+            # already quantised, so the bf16 intermediate never exists
             xq, xs = quantize_rows_mxfp8(self.xrecv)
-            grouped_gemm_mxfp8(xq, xs, self.w13_q, self.w13_s, self.group_start, self.group_rows, out=self.h,
-                               swiglu=True, error=self.error[1:2])
-            hq, hs = quantize_rows_mxfp8(self.h)
+            if self.I % 128 == 0:
+                if getattr(self, "_hq", None) is None:
+                    self._hq = torch.empty(self.cap, self.I, dtype=torch.uint8, device=self.dev)
+                    self._hs = torch.empty(self.I // 128, self.cap, dtype=torch.int32, device=self.dev)
+                hq, hs = grouped_gemm_mxfp8_swiglu_q(xq, xs, self.w13_q, self.w13_s, self.group_start,
+                                                     self.group_rows, out_q=self._hq, out_sf=self._hs,
+                                                     error=self.error[1:2])
+            else:
+                grouped_gemm_mxfp8(xq, xs, self.w13_q, self.w13_s, self.group_start, self.group_rows, out=self.h,
+                                   swiglu=True, error=self.error[1:2])
+                hq, hs = quantize_rows_mxfp8(self.h)
             grouped_gemm_mxfp8(hq, hs, self.w2_q, self.w2_s, self.group_start, self.group_rows, out=self.y,
                                error=self.error[2:3])
         elif self.fp8:

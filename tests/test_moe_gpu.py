@@ -253,6 +253,43 @@ def test_grouped_gemm_mxfp8_many_tiles_and_swiglu():
         assert (out[r0:r0 + n].float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 1e-3, f"group {g}"
 
 
+def test_grouped_gemm_mxfp8_fused_output_quantiser_matches_the_separate_one():
+    """SwiGLU + quantisation in the epilogue: the same bytes and scales as quantising the bf16 result would give,
+    up to the rounding of that intermediate to bf16."""
+    from rbruck_alltoallv_b200.ops import moe
+    torch.manual_seed(23)
+    rows, I, K = [700, 129, 300], 512, 1024
+    G = len(rows)
+    gs, gr, M, starts = _groups_aligned(rows, "cuda")
+    A = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 2).to(torch.bfloat16)
+    gate = (torch.randn(G, I, K, device="cuda") * 0.03).to(torch.bfloat16)
+    up = (torch.randn(G, I, K, device="cuda") * 0.03).to(torch.bfloat16)
+    Aq, sfa = moe.quantize_rows_mxfp8(A)
+    Bq, sfb = moe.quantize_weight_mxfp8(moe.pack_gate_up(gate, up))
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    hq = torch.zeros(M, I, dtype=torch.uint8, device="cuda")
+    hs = moe.mx_to_atoms(torch.full((I // 128, M), 0x7f7f7f7f, dtype=torch.int32, device="cuda"))
+    moe.grouped_gemm_mxfp8_swiglu_q(Aq, sfa, Bq, sfb, gs, gr, out_q=hq, out_sf=hs, error=err)
+    h_bf16 = moe.grouped_gemm_mxfp8(Aq, sfa, Bq, sfb, gs, gr, swiglu=True, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+    fused = moe.dequantize_rows_mxfp8(hq, hs)
+    for g, n in enumerate(rows):
+        r0 = starts[g]
+        ref = h_bf16[r0:r0 + n].float()
+        got = fused[r0:r0 + n]
+        # e4m3 keeps 3 mantissa bits: every value within 1/16 of its 32-block's largest magnitude
+        blk = ref.view(n, I // 32, 32).abs().amax(dim=2, keepdim=True).expand(n, I // 32, 32).reshape(n, I)
+        assert torch.all((got - ref).abs() <= blk / 16 + 1e-6), f"group {g}"
+        # and the scales are the smallest powers of two that keep the block inside e4m3 (a bf16 rounding of the
+        # largest value may move a block across a power of two: allow one step)
+        e_ref = moe._mx_exponents(ref.view(n, I // 32, 32).abs().amax(dim=2))
+        words = moe.mx_from_atoms(hs, M)[:, r0:r0 + n]                                  # [I/128, n]
+        e_got = torch.stack([((words.to(torch.int64) >> (8 * j)) & 0xFF) - 127 for j in range(4)], dim=-1)
+        e_got = e_got.permute(1, 0, 2).reshape(n, I // 32)
+        assert (e_got - e_ref).abs().max().item() <= 1
+
+
 def test_moe_layer_mxfp8_close_to_bf16():
     from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
     from rbruck_alltoallv_b200.parallel.comm import Communicator
