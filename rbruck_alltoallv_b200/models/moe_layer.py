@@ -44,5 +44,11 @@ def smoke_moe(comm=None):
         err = (out.float() - ref).abs().max().item()
         scale = ref.abs().max().item()
         assert err <= 0.02 * scale + 1e-3, f"MoE smoke mismatch: max err {err} vs scale {scale}"
+        # the same layer with MXFP8 expert GEMMs (hardware block scaling, fused SwiGLU + quantiser epilogue)
+        mx = MoELayer(own, E, H, I, T, seed=1, fp8="mx")
+        out = mx(x, logits)
+        mx.ep.check()
+        rel = (out.float() - ref).norm().item() / ref.norm().item()
+        assert rel < 0.08, f"MXFP8 MoE smoke deviates {rel:.3f} from the fp32 reference"
     finally:
         own.close()

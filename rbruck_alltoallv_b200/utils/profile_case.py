@@ -10,6 +10,7 @@
     python -m rbruck_alltoallv_b200.utils.profile_case a2av_small  # Zipf blocks <= 64 KB (latency regime)
     python -m rbruck_alltoallv_b200.utils.profile_case gemm1       # grouped SwiGLU GEMM, 2 experts x 2048 rows, 4096 -> 2 x 14336
     python -m rbruck_alltoallv_b200.utils.profile_case gemm2       # grouped down GEMM, 14336 -> 4096
+    python -m rbruck_alltoallv_b200.utils.profile_case gemm_mx     # MXFP8 up/gate GEMM, SwiGLU + quantiser epilogue
     python -m rbruck_alltoallv_b200.utils.profile_case transpose   # fused pencil transpose, 384^3 complex64
     python -m rbruck_alltoallv_b200.utils.profile_case eager       # eager protocol, Zipf blocks <= 64 KB, radix 2
     python -m rbruck_alltoallv_b200.utils.profile_case moe         # MoE layer, 8192 tokens x 4096, 8 experts, FFN 1024
@@ -89,6 +90,22 @@ def _gemm_fp8():
     assert err.item() == 0
 
 
+def _gemm_mx():
+    from ..ops.moe import grouped_gemm_mxfp8_swiglu_q, quantize_rows_mxfp8, quantize_weight_mxfp8
+    G, rows, H, I = 2, 2048, 4096, 14336
+    gs = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    gr = torch.tensor([rows, rows], dtype=torch.int32, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    Aq, sfa = quantize_rows_mxfp8(torch.randn(G * rows, H, device="cuda").to(torch.bfloat16))
+    Bq, sfb = quantize_weight_mxfp8((torch.randn(G, 2 * I, H, device="cuda") * 0.02).to(torch.bfloat16))
+    hq = torch.empty(G * rows, I, dtype=torch.uint8, device="cuda")
+    hs = torch.empty(I // 128, G * rows, dtype=torch.int32, device="cuda")
+    for _ in range(4):
+        grouped_gemm_mxfp8_swiglu_q(Aq, sfa, Bq, sfb, gs, gr, out_q=hq, out_sf=hs, error=err)
+    torch.cuda.synchronize()
+    assert err.item() == 0
+
+
 def _transpose():
     from ..ops.fft import PencilTranspose
     from ..parallel.comm import Communicator
@@ -118,6 +135,8 @@ def main() -> int:
         _gemm(2)
     elif case == "gemm_fp8":
         _gemm_fp8()
+    elif case == "gemm_mx":
+        _gemm_mx()
     elif case == "transpose":
         _transpose()
     elif case == "eager":
