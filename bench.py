@@ -309,12 +309,22 @@ def run_moe(world, deadline):
         # the same layer with the expert GEMMs in MXFP8 (e4m3, power-of-two scales per 32 elements applied by the
         # tensor core); extra information, the configured dtype above is bf16
         layer = MoEExpertParallel(comm, El * world, H, I, T, seed=3, fp8="mx")
-        layer.forward(x, logits, out)
-        layer.check()
-        tm = _time(lambda: layer.forward(x, logits, out), 10, 3)
-        layer.check()
-        msx = float(np.median(tm))
-        res["mxfp8_experts"] = {"ms_layer": round(msx, 3), "tflops": round(flops / msx / 1e9, 1)}
+        good, why = 1, ""
+        try:
+            layer.forward(x, logits, out)
+            layer.check()
+        except Exception as e:  # noqa: BLE001 - every rank must reach the agreement below
+            good, why = 0, f"{type(e).__name__}: {str(e)[:120]}"
+        flag = torch.tensor([good], device="cuda", dtype=torch.int32)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()):
+            tm = _time(lambda: layer.forward(x, logits, out), 10, 3)
+            layer.check()
+            msx = float(np.median(tm))
+            res["mxfp8_experts"] = {"ms_layer": round(msx, 3), "tflops": round(flops / msx / 1e9, 1)}
+        else:
+            res["mxfp8_experts"] = {"error": why or "failed on another rank"}
         del layer
     del x, logits, out
     comm.close()
