@@ -36,11 +36,12 @@ def test_four_processes():
 
 
 @pytest.mark.skipif(_ngpus() < 2, reason="needs 2 GPUs")
-def test_moe_two_processes_matches_reference():
+@pytest.mark.parametrize("extra", [[], ["--mx"]], ids=["bf16", "mxfp8"])
+def test_moe_two_processes_matches_reference(extra):
     env = dict(os.environ, PYTHONPATH=ROOT, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29651", "-m", "rbruck_alltoallv_b200.utils.moe_bench", "--tokens", "512",
-           "--hidden", "512", "--inter", "1024", "--experts-per-rank", "4", "--check", "--steps", "3"]
+           "--hidden", "512", "--inter", "1024", "--experts-per-rank", "4", "--check", "--steps", "3"] + extra
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert '"check": "ok"' in res.stdout
