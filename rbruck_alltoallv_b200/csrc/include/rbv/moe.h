@@ -116,6 +116,30 @@ int rbv_moe_dispatch_streamed(rbv_ctx_t ctx, const void* x, int T, int H, const 
 int rbv_moe_combine(rbv_ctx_t ctx, void* out, int T, int H, const int* topk_idx, const float* topk_w,
                     const int* slot, unsigned long long y_off, int E, int* error_flag, void* cuda_stream);
 
+/* Dispatch that also leaves, beside every row, where its result has to go: word `pos` of the table at heap offset
+ * ret_off on the row's owner becomes (sending process << 24) | (token * 2 + k).  2 T < 2^24. */
+int rbv_moe_dispatch_ret(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                         int* cursor, int* slot, unsigned long long xrecv_off, unsigned long long ret_off,
+                         long long recv_capacity_rows, int E, int* error_flag, void* cuda_stream);
+
+/* Down GEMM fused with the return all-to-all: the epilogue stores row `pos` of the result straight into row
+ * (token * 2 + k) of the [T, 2, N] bf16 buffer at heap offset y2_off of the process the row came from (`ret`, the
+ * table rbv_moe_dispatch_ret filled; `heaps[nheaps]` this process's mappings of every process's heap), so the
+ * transfer overlaps the GEMM tile by tile.  Epilogue: plain bf16.  Pair kernel (cta_group::2) in both precisions. */
+int rbv_grouped_gemm_bf16_push(const void* A, long long a_rows, const void* B, const int* group_start,
+                               const int* group_rows, int G, int N, int K, const unsigned* ret,
+                               const void* const* heaps, int nheaps, unsigned long long y2_off, int* error_flag,
+                               int max_ctas, void* cuda_stream);
+int rbv_grouped_gemm_mxfp8_push(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb,
+                                const int* group_start, const int* group_rows, int G, int N, int K,
+                                const unsigned* ret, const void* const* heaps, int nheaps, unsigned long long y2_off,
+                                int* error_flag, int max_ctas, void* cuda_stream);
+
+/* Combine after such a GEMM: cross-GPU barrier (every process's GEMM has finished), then
+ * out[t] = w[t][0] * y2[t][0] + w[t][1] * y2[t][1] from local memory. */
+int rbv_moe_combine_pushed(rbv_ctx_t ctx, void* out, int T, int H, const float* topk_w, const void* y2,
+                           int* error_flag, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,6 +60,11 @@ struct MxParams {
   int* error;
   int epilogue;                // 0: C = bf16(acc); 1: SwiGLU over interleaved gate / up columns, bf16;
                                // 3: SwiGLU, then MXFP8 again: C is e4m3 [*, N / 2] (ldc in bytes) with sf_out
+  // Push mode (ret != null, epilogue 0): row `pos` of the result goes to row (ret[pos] & 0xffffff) of the [*, N] bf16
+  // buffer at offset y2_off of the heap of process ret[pos] >> 24: the return all-to-all of the MoE layer.
+  const unsigned* ret;
+  unsigned long long y2_off;
+  char* heap[16];
 };
 
 struct XTile { int g, m0, n0, rows; bool valid; };
@@ -246,6 +251,10 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __gri
       const int my_m0 = tl.m0 + (int)rank * XHM;
       const bool live = row < tl.rows - (int)rank * XHM;
       __nv_bfloat16* crow = C + (size_t)(my_m0 + row) * p.ldc;
+      if (p.ret && live) {
+        const unsigned rv = __ldg(p.ret + my_m0 + row);
+        crow = reinterpret_cast<__nv_bfloat16*>(p.heap[rv >> 24] + p.y2_off) + (size_t)(rv & 0xffffffu) * p.ldc;
+      }
       if (p.epilogue == 3) {
         // SwiGLU, then the quantiser of the next GEMM's A operand, fused: the 64 outputs of this thread's row are two
         // blocks of 32; each gets its power-of-two scale from the row's own values (no other thread is involved)
@@ -465,8 +474,10 @@ bool make_map_atoms(CUtensorMap* m, const void* base, unsigned long long atoms) 
 
 static int launch_mxfp8(const void* A, const void* sfa, long long a_rows, const void* B, const void* sfb, void* C,
                         void* sf_out, const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
-                        int epilogue, int* error_flag, int max_ctas, void* cuda_stream) {
+                        int epilogue, int* error_flag, int max_ctas, void* cuda_stream, const unsigned* ret = nullptr,
+                        const void* const* heaps = nullptr, int nheaps = 0, unsigned long long y2_off = 0) {
   using namespace rbv;
+  if (ret && (epilogue != 0 || !heaps || nheaps < 1 || nheaps > 16 || (y2_off & 15))) return (int)cudaErrorInvalidValue;
   if (G < 1 || G > kMoeMaxGroups || N % XN || K % XK || a_rows < 1 || (ldc % 8)) return (int)cudaErrorInvalidValue;
   if (epilogue == 3 && (!sf_out || N % 256 || ldc % 16 || (reinterpret_cast<uintptr_t>(sf_out) & 15)))
     return (int)cudaErrorInvalidValue;
@@ -490,6 +501,8 @@ static int launch_mxfp8(const void* A, const void* sfa, long long a_rows, const 
   p.group_start = group_start; p.group_rows = group_rows; p.G = G; p.N = N; p.K = K; p.ldc = ldc;
   p.a_row_blocks = (int)nrb;
   p.C = C; p.sf_out = static_cast<uint32_t*>(sf_out); p.error = error_flag; p.epilogue = epilogue;
+  p.ret = ret; p.y2_off = y2_off;
+  for (int q = 0; q < 16; q++) p.heap[q] = (ret && q < nheaps) ? static_cast<char*>(const_cast<void*>(heaps[q])) : nullptr;
   int grid = max_ctas;
   if (grid <= 0) {
     int dev = 0;
@@ -508,6 +521,16 @@ extern "C" int rbv_grouped_gemm_mxfp8(const void* A, const void* sfa, long long 
   if (epilogue != 0 && epilogue != 1) return (int)cudaErrorInvalidValue;
   return launch_mxfp8(A, sfa, a_rows, B, sfb, C, nullptr, group_start, group_rows, G, N, K, ldc, epilogue, error_flag,
                       max_ctas, cuda_stream);
+}
+
+extern "C" int rbv_grouped_gemm_mxfp8_push(const void* A, const void* sfa, long long a_rows, const void* B,
+                                           const void* sfb, const int* group_start, const int* group_rows, int G,
+                                           int N, int K, const unsigned* ret, const void* const* heaps, int nheaps,
+                                           unsigned long long y2_off, int* error_flag, int max_ctas,
+                                           void* cuda_stream) {
+  if (!ret) return (int)cudaErrorInvalidValue;
+  return launch_mxfp8(A, sfa, a_rows, B, sfb, const_cast<void*>(heaps ? heaps[0] : nullptr), nullptr, group_start,
+                      group_rows, G, N, K, N, 0, error_flag, max_ctas, cuda_stream, ret, heaps, nheaps, y2_off);
 }
 
 extern "C" int rbv_grouped_gemm_mxfp8_swiglu_q(const void* A, const void* sfa, long long a_rows, const void* B,

@@ -51,6 +51,12 @@ struct PairParams {
   void* C;
   int* error;
   int epilogue;   // 0: C = bf16(acc); 1: C[:, j] = bf16(silu(acc[:, 2j]) * acc[:, 2j+1])
+  // Push mode (ret != null, epilogue 0): row `pos` of the result goes to row (ret[pos] & 0xffffff) of the [*, N] bf16
+  // buffer at offset y2_off of the heap of process ret[pos] >> 24 (a peer mapping over NVLink when that is another
+  // GPU): the return all-to-all of the MoE layer, done by the epilogue.
+  const unsigned* ret;
+  unsigned long long y2_off;
+  char* heap[16];
 };
 
 struct PairTile { int m0, n0, b_row, rows; bool valid; };
@@ -183,6 +189,10 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)b * PN;
       const bool live = row < tl.rows - (int)rank * HM;
       __nv_bfloat16* crow = C + (size_t)(tl.m0 + (int)rank * HM + row) * p.ldc;
+      if (p.ret && live) {
+        const unsigned rv = __ldg(p.ret + tl.m0 + (int)rank * HM + row);
+        crow = reinterpret_cast<__nv_bfloat16*>(p.heap[rv >> 24] + p.y2_off) + (size_t)(rv & 0xffffffu) * p.ldc;
+      }
       #pragma unroll 1
       for (int c = 0; c < PN; c += 32) {
         uint32_t r[32];
@@ -280,13 +290,15 @@ extern "C" int rbv_grouped_gemm_pair_enabled() {
   return rbv::g_pair_mode;
 }
 
-extern "C" int rbv_grouped_gemm_bf16_pair(const void* A, long long a_rows, const void* B, void* C,
-                                          const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
-                                          int epilogue, int* error_flag, int max_ctas, void* cuda_stream) {
+static int launch_bf16_pair(const void* A, long long a_rows, const void* B, void* C, const int* group_start,
+                            const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
+                            int max_ctas, void* cuda_stream, const unsigned* ret, const void* const* heaps, int nheaps,
+                            unsigned long long y2_off) {
   using namespace rbv;
   if (G < 1 || G > kMoeMaxGroups || N % PN || K % PK || a_rows < 1 || (ldc % 8)) return (int)cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return (int)cudaErrorInvalidValue;
+  if (ret && (epilogue != 0 || !heaps || nheaps < 1 || nheaps > 16 || (y2_off & 15))) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -300,6 +312,8 @@ extern "C" int rbv_grouped_gemm_bf16_pair(const void* A, long long a_rows, const
   PairParams p;
   p.group_start = group_start; p.group_rows = group_rows; p.G = G; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
   p.error = error_flag; p.epilogue = epilogue;
+  p.ret = ret; p.y2_off = y2_off;
+  for (int q = 0; q < 16; q++) p.heap[q] = (ret && q < nheaps) ? static_cast<char*>(const_cast<void*>(heaps[q])) : nullptr;
   int grid = max_ctas;
   if (grid <= 0) {
     int dev = 0;
@@ -310,4 +324,21 @@ extern "C" int rbv_grouped_gemm_bf16_pair(const void* A, long long a_rows, const
   if (grid < 2) return (int)cudaErrorInvalidValue;
   grouped_gemm_pair_kernel<<<grid, PAIR_THREADS, PAIR_SMEM, static_cast<cudaStream_t>(cuda_stream)>>>(ma, mb, p);
   return (int)cudaGetLastError();
+}
+
+extern "C" int rbv_grouped_gemm_bf16_pair(const void* A, long long a_rows, const void* B, void* C,
+                                          const int* group_start, const int* group_rows, int G, int N, int K, int ldc,
+                                          int epilogue, int* error_flag, int max_ctas, void* cuda_stream) {
+  return launch_bf16_pair(A, a_rows, B, C, group_start, group_rows, G, N, K, ldc, epilogue, error_flag, max_ctas,
+                          cuda_stream, nullptr, nullptr, 0, 0ull);
+}
+
+extern "C" int rbv_grouped_gemm_bf16_push(const void* A, long long a_rows, const void* B, const int* group_start,
+                                          const int* group_rows, int G, int N, int K, const unsigned* ret,
+                                          const void* const* heaps, int nheaps, unsigned long long y2_off,
+                                          int* error_flag, int max_ctas, void* cuda_stream) {
+  if (!ret) return (int)cudaErrorInvalidValue;
+  // C is only a base for rows that are not pushed (there are none): any aligned address of this process will do
+  return launch_bf16_pair(A, a_rows, B, const_cast<void*>(heaps ? heaps[0] : nullptr), group_start, group_rows, G, N, K,
+                          N, 0, error_flag, max_ctas, cuda_stream, ret, heaps, nheaps, y2_off);
 }

@@ -169,6 +169,8 @@ struct DispatchArgs {
   int* slot;                // [T, 2] out
   unsigned long long xrecv_off;
   long long capacity_rows;
+  unsigned long long ret_off;   // != 0: heap offset of the owner's table of return addresses, one word per row:
+                                // (sending process << 24) | (token * 2 + k), for GEMMs that push their result back
 };
 
 __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
@@ -185,6 +187,8 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
     if (pos >= a.capacity_rows) { if (lane == 0) moe_fail(c, 4, e); continue; }
     const int owner = e / a.El;
     char* dst = c.heap[owner] + a.xrecv_off + (size_t)pos * row_bytes;
+    if (a.ret_off && lane == 0)
+      reinterpret_cast<unsigned*>(c.heap[owner] + a.ret_off)[pos] = ((unsigned)c.proc << 24) | (unsigned)r;
     dev::group_copy(dst, a.x + (size_t)(r >> 1) * row_bytes, row_bytes, lane, 32);
   }
   // completion: the last CTA tells every process that this rank's rows are in place, then waits for all ranks
@@ -258,6 +262,64 @@ __global__ void __launch_bounds__(kMoeThreads) moe_combine_kernel(const __grid_c
       for (int i = lane; i < nvec; i += 32) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         bf16x8_fma(acc, dev::ld_cg_v4(r0 + i), w0);
+        bf16x8_fma(acc, dev::ld_cg_v4(r1 + i), w1);
+        uint4 v;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+        #pragma unroll
+        for (int j = 0; j < 4; j++) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o[i] = v;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(&my->aux_exit[1], 1u) == gridDim.x - 1) {
+      my->aux_exit[1] = 0;
+      my->aux_seq[1] = my->aux_seq[1] + 1u;
+    }
+  }
+}
+
+// Combine after a down GEMM that pushed every result row back to the GPU of its token (row (token, k) of a
+// [T, 2, H] buffer there): a cross-GPU barrier says that every GEMM has finished, then the gate-weighted sum reads
+// local memory only.
+struct CombinePushedArgs {
+  MoeComm comm;
+  char* out;                // [T, H] bf16
+  const char* y2;           // [T, 2, H] bf16, local
+  int T, H;
+  const float* topk_w;
+};
+
+__global__ void __launch_bounds__(kMoeThreads) moe_combine_pushed_kernel(const __grid_constant__ CombinePushedArgs a) {
+  const MoeComm& c = a.comm;
+  __shared__ int s_ok;
+  CtrlBlock* my = ctrl_of(c, c.proc);
+  if (threadIdx.x == 0) {
+    const unsigned seq = __ldcg(&my->aux_seq[1]);
+    if (blockIdx.x == 0) {
+      dev::fence_acq_rel(c.nproc > 1);
+      aux_arrive(c, 1);
+    }
+    dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
+    const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
+    int r = dev::wait_ge(aux_counter(c, 1), target, wc, c.nproc > 1);
+    if (r != dev::WAIT_OK) moe_fail(c, 2, 0);
+    s_ok = (r == dev::WAIT_OK);
+  }
+  __syncthreads();
+  if (s_ok) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int nvec = a.H / 8;
+    for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < a.T; t += warps) {
+      const float w0 = a.topk_w[2 * t], w1 = a.topk_w[2 * t + 1];
+      const uint4* r0 = reinterpret_cast<const uint4*>(a.y2 + (size_t)(2 * t) * a.H * 2);
+      const uint4* r1 = r0 + nvec;
+      uint4* o = reinterpret_cast<uint4*>(a.out + (size_t)t * a.H * 2);
+      for (int i = lane; i < nvec; i += 32) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        bf16x8_fma(acc, dev::ld_cg_v4(r0 + i), w0);   // the rows were written by other GPUs: not through L1
         bf16x8_fma(acc, dev::ld_cg_v4(r1 + i), w1);
         uint4 v;
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
@@ -397,14 +459,22 @@ extern "C" {
 int rbv_moe_dispatch(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
                      int* cursor, int* slot, unsigned long long xrecv_off, long long recv_capacity_rows,
                      int E, int* error_flag, void* stream) {
+  return rbv_moe_dispatch_ret(ctx, x, T, H, topk_idx, dst_base, cursor, slot, xrecv_off, 0ull, recv_capacity_rows, E,
+                              error_flag, stream);
+}
+
+int rbv_moe_dispatch_ret(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                         int* cursor, int* slot, unsigned long long xrecv_off, unsigned long long ret_off,
+                         long long recv_capacity_rows, int E, int* error_flag, void* stream) {
   const Context& c = *ctx->c;
+  if (2ll * T >= (1ll << 24)) return (int)cudaErrorInvalidValue;
   if (c.L() != 1 || E % c.P() || (H % 8)) return (int)cudaErrorInvalidValue;
   DispatchArgs a;
   a.comm = make_comm(ctx, error_flag);
   a.x = static_cast<const char*>(x);
   a.T = T; a.H = H; a.E = E; a.El = E / c.P();
   a.topk_idx = topk_idx; a.dst_base = dst_base; a.cursor = cursor; a.slot = slot;
-  a.xrecv_off = xrecv_off; a.capacity_rows = recv_capacity_rows;
+  a.xrecv_off = xrecv_off; a.capacity_rows = recv_capacity_rows; a.ret_off = ret_off;
   const int warps_per_cta = kMoeThreads / 32;
   int grid = (2 * T + warps_per_cta - 1) / warps_per_cta;
   const int cap = c.sm_count() * 2;
@@ -457,6 +527,23 @@ int rbv_moe_combine(rbv_ctx_t ctx, void* out, int T, int H, const int* topk_idx,
   const int cap = c.sm_count() * 2;
   grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
   moe_combine_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_combine_pushed(rbv_ctx_t ctx, void* out, int T, int H, const float* topk_w, const void* y2,
+                           int* error_flag, void* stream) {
+  const Context& c = *ctx->c;
+  if (c.L() != 1 || (H % 8)) return (int)cudaErrorInvalidValue;
+  CombinePushedArgs a;
+  a.comm = make_comm(ctx, error_flag);
+  a.out = static_cast<char*>(out);
+  a.y2 = static_cast<const char*>(y2);
+  a.T = T; a.H = H; a.topk_w = topk_w;
+  const int warps_per_cta = kMoeThreads / 32;
+  int grid = (T + warps_per_cta - 1) / warps_per_cta;
+  const int cap = c.sm_count() * 2;   // every CTA waits on the barrier and only CTA 0 signals: any grid size is safe
+  grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
+  moe_combine_pushed_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return (int)cudaGetLastError();
 }
 

@@ -275,7 +275,8 @@ class MoEExpertParallel:
     """One MoE FFN layer sharded by experts over the ranks of a communicator (one rank per GPU)."""
 
     def __init__(self, comm, num_experts: int, hidden: int, inter: int, tokens: int, capacity_factor: float = 2.0,
-                 seed: int = 0, init_std: float = 0.02, fp8: bool = False, overlap: Optional[bool] = None):
+                 seed: int = 0, init_std: float = 0.02, fp8: bool = False, overlap: Optional[bool] = None,
+                 push_combine: Optional[bool] = None):
         if comm.L != 1:
             raise ValueError("the MoE path needs one rank per process")
         if num_experts % comm.P:
@@ -301,7 +302,6 @@ class MoEExpertParallel:
         self.cap = int(np.ceil(capacity_factor * 2 * tokens / 128.0)) * 128 + (128 * self.El if self.mx else 0)
         i32 = torch.int32
         self.xrecv = comm.symm_empty((self.cap, hidden), bf)
-        self.y = comm.symm_empty((self.cap, hidden), bf)
         self.h = torch.empty(self.cap, inter, dtype=bf, device=dev)
         self.hist = torch.zeros(self.E, dtype=i32, device=dev)
         self.hist_all = comm.symm_zeros((self.P, self.E), i32)
@@ -329,11 +329,25 @@ class MoEExpertParallel:
         self.order = torch.zeros(2 * tokens, dtype=i32, device=dev)
         self._side = torch.cuda.Stream(device=dev)
         self._ev_layout, self._ev_gemm1 = torch.cuda.Event(), torch.cuda.Event()
+        # Down GEMM fused with the return all-to-all (bf16 and MXFP8 paths): the dispatch leaves beside every row where
+        # its result has to go, the down GEMM's epilogue stores each result row straight into the [T, 2, H] buffer of
+        # the token's GPU (over NVLink while the GEMM is still computing other tiles), and the combine only waits for
+        # all GEMMs and adds two local rows per token.  ``push_combine=False`` / RBV_MOE_PUSH=0 keeps the combine that
+        # pulls the rows after the GEMM.
+        if push_combine is None:
+            push_combine = os.environ.get("RBV_MOE_PUSH", "1") != "0"
+        self.push = bool(push_combine) and (self.mx or not self.fp8) and not self.overlap
+        self.ret = comm.symm_zeros(self.cap, i32)
+        self.y2 = comm.symm_empty((2 * tokens, hidden), bf) if self.push else None      # results, by (token, k)
+        self.y = None if self.push else comm.symm_empty((self.cap, hidden), bf)         # results, expert-sorted
         heap0 = self.lib.rbv_ctx_heap(comm._ctx, comm.proc)
         self.xrecv_off = self.xrecv.data_ptr() - heap0
-        self.y_off = self.y.data_ptr() - heap0
+        self.y_off = 0 if self.push else self.y.data_ptr() - heap0
         self.ready_off = self.ready.data_ptr() - heap0
-        comm.require_same_offsets(self.xrecv_off, self.y_off, self.ready_off)
+        self.ret_off = self.ret.data_ptr() - heap0
+        self.y2_off = (self.y2.data_ptr() - heap0) if self.push else 0
+        self._heaps = (C.c_void_p * self.P)(*[self.lib.rbv_ctx_heap(comm._ctx, q) for q in range(self.P)])
+        comm.require_same_offsets(self.xrecv_off, self.y_off, self.ready_off, self.ret_off, self.y2_off)
         torch.cuda.synchronize(dev)
         comm.host_barrier()          # every rank's counters are zero before anybody's first dispatch
         # the histogram all-gather: every rank sends the same E counters to every rank
@@ -363,9 +377,9 @@ class MoEExpertParallel:
         self._check(lib.rbv_moe_layout_aligned(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
                                                _p(self.group_start), _p(self.group_rows), _p(self.cursor),
                                                _p(self.totals), 128 if self.mx else 1, st), "layout")
-        self._check(lib.rbv_moe_dispatch(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base), _p(self.cursor),
-                                         _p(self.slot), self.xrecv_off, self.cap, self.E, _p(self.error[0:1]), st),
-                    "dispatch")
+        self._check(lib.rbv_moe_dispatch_ret(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base), _p(self.cursor),
+                                             _p(self.slot), self.xrecv_off, self.ret_off if self.push else 0,
+                                             self.cap, self.E, _p(self.error[0:1]), st), "dispatch")
         if self.mx:
             # activations are quantised once; the first GEMM's epilogue (SwiGLU) hands the second GEMM its operand
             # already quantised, so the bf16 intermediate never exists
@@ -381,8 +395,14 @@ class MoEExpertParallel:
                 grouped_gemm_mxfp8(xq, xs, self.w13_q, self.w13_s, self.group_start, self.group_rows, out=self.h,
                                    swiglu=True, error=self.error[1:2])
                 hq, hs = quantize_rows_mxfp8(self.h)
-            grouped_gemm_mxfp8(hq, hs, self.w2_q, self.w2_s, self.group_start, self.group_rows, out=self.y,
-                               error=self.error[2:3])
+            if self.push:
+                self._check(lib.rbv_grouped_gemm_mxfp8_push(
+                    _p(hq), _p(hs), self.cap, _p(self.w2_q), _p(self.w2_s), _p(self.group_start), _p(self.group_rows),
+                    self.El, H, self.I, _p(self.ret), self._heaps, self.P, self.y2_off, _p(self.error[2:3]), 0, st),
+                    "down GEMM")
+            else:
+                grouped_gemm_mxfp8(hq, hs, self.w2_q, self.w2_s, self.group_start, self.group_rows, out=self.y,
+                                   error=self.error[2:3])
         elif self.fp8:
             # activations are quantised row-wise (1 x 128 blocks) right before each GEMM
             xq, xs = quantize_rows_fp8(self.xrecv)
@@ -394,10 +414,19 @@ class MoEExpertParallel:
         else:
             grouped_gemm(self.xrecv, self.w13, self.group_start, self.group_rows, out=self.h, swiglu=True,
                          error=self.error[1:2])
-            grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False,
-                         error=self.error[2:3])
-        self._check(lib.rbv_moe_combine(ctx, _p(out), T, H, _p(self.topk_idx), _p(self.topk_w), _p(self.slot),
-                                        self.y_off, self.E, _p(self.error[3:4]), st), "combine")
+            if self.push:
+                self._check(lib.rbv_grouped_gemm_bf16_push(
+                    _p(self.h), self.cap, _p(self.w2), _p(self.group_start), _p(self.group_rows), self.El, H, self.I,
+                    _p(self.ret), self._heaps, self.P, self.y2_off, _p(self.error[2:3]), 0, st), "down GEMM")
+            else:
+                grouped_gemm(self.h, self.w2, self.group_start, self.group_rows, out=self.y, swiglu=False,
+                             error=self.error[2:3])
+        if self.push:
+            self._check(lib.rbv_moe_combine_pushed(ctx, _p(out), T, H, _p(self.topk_w), _p(self.y2),
+                                                   _p(self.error[3:4]), st), "combine")
+        else:
+            self._check(lib.rbv_moe_combine(ctx, _p(out), T, H, _p(self.topk_idx), _p(self.topk_w), _p(self.slot),
+                                            self.y_off, self.E, _p(self.error[3:4]), st), "combine")
         return out
 
     def _forward_streamed(self, x, out, st):

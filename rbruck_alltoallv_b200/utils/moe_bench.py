@@ -70,7 +70,7 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
     T, H, I, El = a.tokens, a.hidden, a.inter, a.experts_per_rank
     cap_rows = int(np.ceil(2.0 * 2 * T / 128.0)) * 128
-    heap = 2 * cap_rows * H * 2 + (64 << 20)
+    heap = 2 * (cap_rows + 128 * El) * H * 2 + (64 << 20)
     comm = Communicator(nranks=world, heap_bytes=heap, arena_bytes=1 << 20)
     E = El * world
     layer = MoEExpertParallel(comm, E, H, I, T, seed=3, fp8="mx" if a.mx else a.fp8)

@@ -310,6 +310,31 @@ def test_moe_layer_mxfp8_close_to_bf16():
         comm.close()
 
 
+@pytest.mark.parametrize("fp8", [False, "mx"], ids=["bf16", "mxfp8"])
+def test_moe_push_combine_equals_pull_combine(fp8):
+    """The down GEMM that stores its rows straight into the token owners' buffers gives the same layer output as the
+    combine that pulls them afterwards."""
+    from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    comm = Communicator(nranks=1, heap_bytes=256 << 20, arena_bytes=1 << 20)
+    try:
+        T, H, I, E = 700, 512, 1024, 4
+        g = torch.Generator(device="cuda")
+        g.manual_seed(31)
+        x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+        logits = torch.randn(T, E, device="cuda", generator=g)
+        outs = []
+        for push in (True, False):
+            layer = MoEExpertParallel(comm, E, H, I, T, seed=9, fp8=fp8, push_combine=push)
+            assert layer.push == push
+            outs.append(layer.forward(x, logits).clone())
+            layer.check()
+            del layer
+        assert torch.equal(outs[0], outs[1])
+    finally:
+        comm.close()
+
+
 def test_moe_layer_fp8_close_to_bf16():
     from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
     from rbruck_alltoallv_b200.parallel.comm import Communicator
