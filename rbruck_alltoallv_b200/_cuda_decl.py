@@ -101,6 +101,8 @@ def declare_moe(lib):
     lib.rbv_grouped_gemm_bf16_push.argtypes = [vp, ll, vp, vp, vp, i, i, i, vp, vp, i, ull, vp, i, vp]
     lib.rbv_grouped_gemm_mxfp8_push.argtypes = [vp, vp, ll, vp, vp, vp, vp, i, i, i, vp, vp, i, ull, vp, i, vp]
     lib.rbv_moe_dispatch_ret.argtypes = [vp, vp, i, i, vp, vp, vp, vp, ull, ull, ll, i, vp, vp]
+    lib.rbv_moe_dispatch_mx.argtypes = [vp, vp, i, i, vp, vp, vp, vp, ull, ull, ull, ll, i, vp, vp]
+    lib.rbv_moe_scale_atoms.argtypes = [vp, vp, i, i, vp]
     lib.rbv_moe_combine_pushed.argtypes = [vp, vp, i, i, vp, vp, vp, vp]
     lib.rbv_quantize_rows_mxfp8.argtypes = [vp, ll, i, i, vp, vp, vp]
     lib.rbv_quantize_rows_fp8.argtypes = [vp, ll, i, i, vp, vp, vp]

@@ -122,6 +122,16 @@ int rbv_moe_dispatch_ret(rbv_ctx_t ctx, const void* x, int T, int H, const int* 
                          int* cursor, int* slot, unsigned long long xrecv_off, unsigned long long ret_off,
                          long long recv_capacity_rows, int E, int* error_flag, void* cuda_stream);
 
+/* Dispatch for the MXFP8 path: rows are quantised where they are read (as rbv_quantize_rows_mxfp8 would) and travel
+ * as H bytes + H / 128 scale words: the owner's [capacity, H] e4m3 buffer at heap offset xq_off and its row-major
+ * scale words [capacity, H / 128] at sfrow_off; rbv_moe_scale_atoms then makes the GEMM's atom order of them
+ * ([H / 128][ceil(rows / 128)][128]).  ret_off as in rbv_moe_dispatch_ret (0: none).  H % 128 == 0. */
+int rbv_moe_dispatch_mx(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                        int* cursor, int* slot, unsigned long long xq_off, unsigned long long sfrow_off,
+                        unsigned long long ret_off, long long recv_capacity_rows, int E, int* error_flag,
+                        void* cuda_stream);
+int rbv_moe_scale_atoms(const void* sfrow, void* sfa, int rows, int nkb, void* cuda_stream);
+
 /* Down GEMM fused with the return all-to-all: the epilogue stores row `pos` of the result straight into row
  * (token * 2 + k) of the [T, 2, N] bf16 buffer at heap offset y2_off of the process the row came from (`ret`, the
  * table rbv_moe_dispatch_ret filled; `heaps[nheaps]` this process's mappings of every process's heap), so the

@@ -4,6 +4,7 @@
 // owners' output buffers).  The reference has no counterpart; the cross-GPU synchronisation follows the
 // same rules as the alltoallv kernel (monotonic counters, bounded waits, no reset between calls).
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -206,6 +207,118 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_kernel(const __grid_
       if (dev::wait_ge(aux_counter(c, 0), target, wc, c.nproc > 1) != dev::WAIT_OK) moe_fail(c, 1, 0);
       my->aux_seq[0] = seq + 1u;
     }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Dispatch for the MXFP8 expert GEMMs: the row is quantised where it is read (e4m3, one power-of-two scale per 32
+// columns, as rbv_quantize_rows_mxfp8 does) and travels as H bytes plus H / 128 scale words instead of 2 H bytes, so
+// half as much crosses NVLink and the owner needs no quantiser pass.  Scale words land row-major
+// ([capacity][H / 128], one coalesced store per row); moe_scale_atoms_kernel puts them into the GEMM's atom order.
+// ---------------------------------------------------------------------------------------------
+struct DispatchMxArgs {
+  MoeComm comm;
+  const char* x;            // [T, H] bf16
+  int T, H, E, El;
+  const int* topk_idx;
+  const int* dst_base;
+  int* cursor;
+  int* slot;
+  unsigned long long xq_off;      // heap offset of the owner's [capacity, H] e4m3 rows
+  unsigned long long sfrow_off;   // heap offset of the owner's [capacity, H / 128] scale words
+  unsigned long long ret_off;     // as in DispatchArgs
+  long long capacity_rows;
+};
+
+__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_mx_kernel(const __grid_constant__ DispatchMxArgs a) {
+  const MoeComm& c = a.comm;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int nkb = a.H / 128;                    // scale words per row (<= 32 handled per pass of the word exchange)
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < 2 * a.T; r += warps) {
+    const int e = a.topk_idx[r];
+    int pos = 0;
+    if (lane == 0) pos = a.dst_base[e] + atomicAdd(&a.cursor[e], 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (lane == 0) a.slot[r] = pos;
+    if (pos >= a.capacity_rows) { if (lane == 0) moe_fail(c, 4, e); continue; }
+    const int owner = e / a.El;
+    if (a.ret_off && lane == 0)
+      reinterpret_cast<unsigned*>(c.heap[owner] + a.ret_off)[pos] = ((unsigned)c.proc << 24) | (unsigned)r;
+    const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(r >> 1) * a.H * 2);
+    uint2* dst = reinterpret_cast<uint2*>(c.heap[owner] + a.xq_off + (size_t)pos * a.H);
+    unsigned* sfdst = reinterpret_cast<unsigned*>(c.heap[owner] + a.sfrow_off) + (size_t)pos * nkb;
+    // 256 columns per pass: lane l holds columns 8 l .. 8 l + 7, a 32-column block is 4 lanes, a 128-column block
+    // (one scale word) 16 lanes
+    for (int base = 0; base < nkb; base += 32) {
+      unsigned myword = 0;
+      const int passes = min(16, (nkb - base + 1) / 2);
+      for (int i = 0; i < passes; i++) {
+        const int vec = (base / 2 + i) * 32 + lane;             // 16-byte vector of the row
+        const bool in = vec * 8 < a.H;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (in) raw = __ldg(src + vec);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float2 v[4];
+        float m = 0.0f;
+        #pragma unroll
+        for (int j = 0; j < 4; j++) {
+          v[j] = __bfloat1622float2(h[j]);
+          m = fmaxf(m, fmaxf(fabsf(v[j].x), fabsf(v[j].y)));
+        }
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        int ex = 0;
+        if (m > 0.0f) {
+          int e2;
+          const float fr = frexpf(m * (1.0f / 448.0f), &e2);
+          ex = (fr == 0.5f) ? e2 - 1 : e2;
+          ex = max(-127, min(127, ex));
+        }
+        const float inv = exp2f((float)-ex);
+        unsigned word = (unsigned)(ex + 127) << (8 * ((lane & 15) >> 2));
+        word |= __shfl_xor_sync(0xffffffffu, word, 4);
+        word |= __shfl_xor_sync(0xffffffffu, word, 8);
+        // word of K block base + 2 i sits in lanes 0-15, of base + 2 i + 1 in lanes 16-31; lane j keeps word j
+        const unsigned w = __shfl_sync(0xffffffffu, word, (lane & 1) * 16);
+        if ((lane >> 1) == i) myword = w;
+        if (in) {
+          unsigned q[4];
+          #pragma unroll
+          for (int j = 0; j < 4; j++)
+            q[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[j].x * inv, v[j].y * inv), __NV_SATFINITE, __NV_E4M3);
+          dst[vec] = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+        }
+      }
+      if (base + lane < nkb) sfdst[base + lane] = myword;
+    }
+  }
+  // completion: as moe_dispatch_kernel
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    CtrlBlock* my = ctrl_of(c, c.proc);
+    dev::fence_acq_rel(c.nproc > 1);
+    if (atomicAdd(&my->aux_exit[0], 1u) == gridDim.x - 1) {
+      my->aux_exit[0] = 0;
+      const unsigned seq = my->aux_seq[0];
+      dev::fence_acq_rel(c.nproc > 1);
+      aux_arrive(c, 0);
+      dev::WaitCfg wc{&my->abort_flag, c.timeout_ns};
+      const unsigned long long target = ((unsigned long long)seq + 1ull) * (unsigned long long)c.nproc;
+      if (dev::wait_ge(aux_counter(c, 0), target, wc, c.nproc > 1) != dev::WAIT_OK) moe_fail(c, 1, 0);
+      my->aux_seq[0] = seq + 1u;
+    }
+  }
+}
+
+// Scale words [rows][nkb] (row-major) -> the atom order of the MXFP8 GEMM, [nkb][ceil(rows / 128)][128].
+__global__ void moe_scale_atoms_kernel(const unsigned* __restrict__ sfrow, unsigned* __restrict__ sfa, int rows, int nkb) {
+  const long long n = (long long)rows * nkb;
+  const int nrb = (rows + 127) / 128;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    // consecutive threads walk the rows of one K block: reads are strided by nkb words, writes fill whole atoms
+    const int kb = (int)(i / rows), r = (int)(i - (long long)kb * rows);
+    sfa[((size_t)kb * nrb + r / 128) * 128 + (r % 32) * 4 + (r % 128) / 32] = sfrow[(size_t)r * nkb + kb];
   }
 }
 
@@ -480,6 +593,35 @@ int rbv_moe_dispatch_ret(rbv_ctx_t ctx, const void* x, int T, int H, const int* 
   const int cap = c.sm_count() * 2;
   grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
   moe_dispatch_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_dispatch_mx(rbv_ctx_t ctx, const void* x, int T, int H, const int* topk_idx, const int* dst_base,
+                        int* cursor, int* slot, unsigned long long xq_off, unsigned long long sfrow_off,
+                        unsigned long long ret_off, long long recv_capacity_rows, int E, int* error_flag,
+                        void* stream) {
+  const Context& c = *ctx->c;
+  if (c.L() != 1 || E % c.P() || (H % 128) || 2ll * T >= (1ll << 24)) return (int)cudaErrorInvalidValue;
+  DispatchMxArgs a;
+  a.comm = make_comm(ctx, error_flag);
+  a.x = static_cast<const char*>(x);
+  a.T = T; a.H = H; a.E = E; a.El = E / c.P();
+  a.topk_idx = topk_idx; a.dst_base = dst_base; a.cursor = cursor; a.slot = slot;
+  a.xq_off = xq_off; a.sfrow_off = sfrow_off; a.ret_off = ret_off; a.capacity_rows = recv_capacity_rows;
+  const int warps_per_cta = kMoeThreads / 32;
+  int grid = (2 * T + warps_per_cta - 1) / warps_per_cta;
+  const int cap = c.sm_count() * 2;
+  grid = grid < 1 ? 1 : (grid > cap ? cap : grid);
+  moe_dispatch_mx_kernel<<<grid, kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int rbv_moe_scale_atoms(const void* sfrow, void* sfa, int rows, int nkb, void* stream) {
+  if (rows < 1 || nkb < 1) return (int)cudaErrorInvalidValue;
+  long long n = (long long)rows * nkb;
+  int grid = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+  moe_scale_atoms_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned*>(sfrow), static_cast<unsigned*>(sfa), rows, nkb);
   return (int)cudaGetLastError();
 }
 

@@ -301,7 +301,16 @@ class MoEExpertParallel:
             self.w2_q, self.w2_s = quantize_weight_blocks_fp8(self.w2)
         self.cap = int(np.ceil(capacity_factor * 2 * tokens / 128.0)) * 128 + (128 * self.El if self.mx else 0)
         i32 = torch.int32
-        self.xrecv = comm.symm_empty((self.cap, hidden), bf)
+        # MXFP8: rows are quantised by the dispatch itself and cross NVLink as e4m3 + scale words (half the bytes, no
+        # quantiser pass on the owner); RBV_MOE_QDISPATCH=0 dispatches bf16 rows and quantises them afterwards
+        self.qdispatch = self.mx and hidden % 128 == 0 and os.environ.get("RBV_MOE_QDISPATCH", "1") != "0"
+        if self.qdispatch:
+            self.xrecv = None
+            self.xq = comm.symm_empty((self.cap, hidden), torch.uint8)
+            self.sfrow = comm.symm_empty((self.cap, hidden // 128), i32)
+            self.xs = torch.full((hidden // 128, self.cap), 0x7f7f7f7f, dtype=i32, device=dev)   # atom order
+        else:
+            self.xrecv = comm.symm_empty((self.cap, hidden), bf)
         self.h = torch.empty(self.cap, inter, dtype=bf, device=dev)
         self.hist = torch.zeros(self.E, dtype=i32, device=dev)
         self.hist_all = comm.symm_zeros((self.P, self.E), i32)
@@ -341,13 +350,14 @@ class MoEExpertParallel:
         self.y2 = comm.symm_empty((2 * tokens, hidden), bf) if self.push else None      # results, by (token, k)
         self.y = None if self.push else comm.symm_empty((self.cap, hidden), bf)         # results, expert-sorted
         heap0 = self.lib.rbv_ctx_heap(comm._ctx, comm.proc)
-        self.xrecv_off = self.xrecv.data_ptr() - heap0
+        self.xrecv_off = (self.xq if self.qdispatch else self.xrecv).data_ptr() - heap0
+        self.sfrow_off = (self.sfrow.data_ptr() - heap0) if self.qdispatch else 0
         self.y_off = 0 if self.push else self.y.data_ptr() - heap0
         self.ready_off = self.ready.data_ptr() - heap0
         self.ret_off = self.ret.data_ptr() - heap0
         self.y2_off = (self.y2.data_ptr() - heap0) if self.push else 0
         self._heaps = (C.c_void_p * self.P)(*[self.lib.rbv_ctx_heap(comm._ctx, q) for q in range(self.P)])
-        comm.require_same_offsets(self.xrecv_off, self.y_off, self.ready_off, self.ret_off, self.y2_off)
+        comm.require_same_offsets(self.xrecv_off, self.y_off, self.ready_off, self.ret_off, self.y2_off, self.sfrow_off)
         torch.cuda.synchronize(dev)
         comm.host_barrier()          # every rank's counters are zero before anybody's first dispatch
         # the histogram all-gather: every rank sends the same E counters to every rank
@@ -377,13 +387,21 @@ class MoEExpertParallel:
         self._check(lib.rbv_moe_layout_aligned(_p(self.hist_all), self.P, self.E, self.me, _p(self.dst_base),
                                                _p(self.group_start), _p(self.group_rows), _p(self.cursor),
                                                _p(self.totals), 128 if self.mx else 1, st), "layout")
-        self._check(lib.rbv_moe_dispatch_ret(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base), _p(self.cursor),
-                                             _p(self.slot), self.xrecv_off, self.ret_off if self.push else 0,
-                                             self.cap, self.E, _p(self.error[0:1]), st), "dispatch")
+        if self.qdispatch:
+            self._check(lib.rbv_moe_dispatch_mx(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base),
+                                                _p(self.cursor), _p(self.slot), self.xrecv_off, self.sfrow_off,
+                                                self.ret_off if self.push else 0, self.cap, self.E,
+                                                _p(self.error[0:1]), st), "dispatch")
+            self._check(lib.rbv_moe_scale_atoms(_p(self.sfrow), _p(self.xs), self.cap, H // 128, st), "scale layout")
+        else:
+            self._check(lib.rbv_moe_dispatch_ret(ctx, _p(x), T, H, _p(self.topk_idx), _p(self.dst_base),
+                                                 _p(self.cursor), _p(self.slot), self.xrecv_off,
+                                                 self.ret_off if self.push else 0, self.cap, self.E,
+                                                 _p(self.error[0:1]), st), "dispatch")
         if self.mx:
-            # activations are quantised once; the first GEMM's epilogue (SwiGLU) hands the second GEMM its operand
-            # already quantised, so the bf16 intermediate never exists
-            xq, xs = quantize_rows_mxfp8(self.xrecv)
+            # activations are quantised once (by the dispatch, or here); the first GEMM's epilogue (SwiGLU) hands the
+            # second GEMM its operand already quantised, so the bf16 intermediate never exists
+            xq, xs = (self.xq, self.xs) if self.qdispatch else quantize_rows_mxfp8(self.xrecv)
             if self.I % 128 == 0:
                 if getattr(self, "_hq", None) is None:
                     self._hq = torch.empty(self.cap, self.I, dtype=torch.uint8, device=self.dev)

@@ -335,6 +335,32 @@ def test_moe_push_combine_equals_pull_combine(fp8):
         comm.close()
 
 
+def test_moe_mx_quantising_dispatch_equals_the_quantiser_pass(monkeypatch):
+    """Rows quantised by the dispatch itself (e4m3 + scale words over the wire) give the same layer output, bit for
+    bit, as bf16 rows quantised on arrival."""
+    from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel
+    from rbruck_alltoallv_b200.parallel.comm import Communicator
+    comm = Communicator(nranks=1, heap_bytes=256 << 20, arena_bytes=1 << 20)
+    try:
+        T, H, I, E = 700, 640, 1024, 4            # H / 128 = 5 scale words per row: an odd count
+        g = torch.Generator(device="cuda")
+        g.manual_seed(41)
+        x = (torch.randn(T, H, device="cuda", generator=g) * 3).to(torch.bfloat16)
+        x[5] = 0
+        logits = torch.randn(T, E, device="cuda", generator=g)
+        outs = []
+        for q in ("1", "0"):
+            monkeypatch.setenv("RBV_MOE_QDISPATCH", q)
+            layer = MoEExpertParallel(comm, E, H, I, T, seed=9, fp8="mx")
+            assert layer.qdispatch == (q == "1")
+            outs.append(layer.forward(x, logits).clone())
+            layer.check()
+            del layer
+        assert torch.equal(outs[0], outs[1])
+    finally:
+        comm.close()
+
+
 def test_moe_layer_fp8_close_to_bf16():
     from rbruck_alltoallv_b200.ops.moe import MoEExpertParallel, reference_forward
     from rbruck_alltoallv_b200.parallel.comm import Communicator
