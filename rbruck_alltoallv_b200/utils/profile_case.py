@@ -11,6 +11,7 @@
     python -m rbruck_alltoallv_b200.utils.profile_case gemm1       # grouped SwiGLU GEMM, 2 experts x 2048 rows, 4096 -> 2 x 14336
     python -m rbruck_alltoallv_b200.utils.profile_case gemm2       # grouped down GEMM, 14336 -> 4096
     python -m rbruck_alltoallv_b200.utils.profile_case gemm_mx     # MXFP8 up/gate GEMM, SwiGLU + quantiser epilogue
+    python -m rbruck_alltoallv_b200.utils.profile_case moe_mx      # MoE layer with MXFP8 experts (quantising dispatch, pushed combine)
     python -m rbruck_alltoallv_b200.utils.profile_case transpose   # fused pencil transpose, 384^3 complex64
     python -m rbruck_alltoallv_b200.utils.profile_case eager       # eager protocol, Zipf blocks <= 64 KB, radix 2
     python -m rbruck_alltoallv_b200.utils.profile_case moe         # MoE layer, 8192 tokens x 4096, 8 experts, FFN 1024
@@ -23,12 +24,12 @@ import numpy as np
 import torch
 
 
-def _moe():
+def _moe(fp8=False):
     from ..ops.moe import MoEExpertParallel
     from ..parallel.comm import Communicator
     T, H, I, E = 8192, 4096, 1024, 8
     comm = Communicator(nranks=1, heap_bytes=1 << 30, arena_bytes=1 << 20)
-    layer = MoEExpertParallel(comm, E, H, I, T, capacity_factor=1.0, seed=1)
+    layer = MoEExpertParallel(comm, E, H, I, T, capacity_factor=1.0, seed=1, fp8=fp8)
     x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
     logits = torch.randn(T, E, device="cuda")
     for _ in range(3):
@@ -143,6 +144,8 @@ def main() -> int:
         _a2av("rbruck", small=True, r=2, eager=True)
     elif case == "moe":
         _moe()
+    elif case == "moe_mx":
+        _moe(fp8="mx")
     else:
         raise SystemExit("unknown case")
     print("case", case, "done")
