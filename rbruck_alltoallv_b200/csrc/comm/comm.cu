@@ -45,6 +45,7 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   if (const char* e = std::getenv("RBV_BULK")) bulk_mode_ = std::atoi(e);
   if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_mode_ = std::atoi(e) != 0 ? 1 : 0;
   if (const char* e = std::getenv("RBV_STATIC_OCC")) static_occ_ = std::atoi(e) >= 2 ? 2 : 1;
+  if (const char* e = std::getenv("RBV_STATIC_SPREAD")) static_spread_ = std::atoi(e) != 0;
   if (const char* e = std::getenv("RBV_SEQ_HINT")) seq_hints_ = std::atoi(e) != 0;
   int st_per_sm = 1;
   RBV_CUDA_THROW(a2av_static_configure(static_occ_, &st_per_sm));
@@ -794,7 +795,10 @@ int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const
   sa.host_trace = host_trace_dev_;
   std::memcpy(sa.inl, items.data(), std::min(items.size(), (size_t)kInlineItems) * sizeof(StaticItem));
   const int warps_per_cta = kThreads / 32;
-  int grid = opt.grid > 0 ? opt.grid : (int)((items.size() + warps_per_cta - 1) / warps_per_cta);
+  // Item c goes to warp c / grid of CTA c % grid (a2av_static.cu), so with one CTA per item (up to the CTAs that are
+  // resident at once) a small call spreads over as many SMs as it has items instead of filling 16 warps of a few.
+  int grid = opt.grid > 0 ? opt.grid
+                          : (int)(static_spread_ ? items.size() : (items.size() + warps_per_cta - 1) / warps_per_cta);
   out->grid = std::max(1, std::min(grid, static_max_ctas_));
   out->is_static = true;
   out->eager = false;

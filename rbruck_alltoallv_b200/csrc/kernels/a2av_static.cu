@@ -54,7 +54,8 @@ __global__ void __launch_bounds__(kThreads, MINB) a2av_static_kernel(const __gri
   __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned warps_per_cta = blockDim.x >> 5;
-  const unsigned gwarp = blockIdx.x * warps_per_cta + warp, nwarps = gridDim.x * warps_per_cta;
+  // items are dealt CTA by CTA: item c to warp c / grid of CTA c % grid, so consecutive items run on different SMs
+  const unsigned gwarp = warp * gridDim.x + blockIdx.x, nwarps = gridDim.x * warps_per_cta;
   const bool multi = a.nproc > 1;
   const bool trace = (a.flags & CALL_TRACE) != 0;
   CtrlBlock* my = ctrl_of(a, a.proc);
