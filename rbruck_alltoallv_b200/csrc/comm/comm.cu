@@ -795,10 +795,12 @@ int Context::prepare_static(const DevPlan* dp, int ts, const CallArgs& ca, const
   sa.host_trace = host_trace_dev_;
   std::memcpy(sa.inl, items.data(), std::min(items.size(), (size_t)kInlineItems) * sizeof(StaticItem));
   const int warps_per_cta = kThreads / 32;
-  // Item c goes to warp c / grid of CTA c % grid (a2av_static.cu), so with one CTA per item (up to the CTAs that are
-  // resident at once) a small call spreads over as many SMs as it has items instead of filling 16 warps of a few.
+  // One process: item c goes to warp c / grid of CTA c % grid (a2av_static.cu), so with one CTA per item (up to the
+  // CTAs that are resident at once) a small call spreads over as many SMs as it has items instead of filling the 16
+  // warps of a few.  Several processes: 16 items per CTA (see the kernel).
+  const bool spread = static_spread_ && nproc_ == 1;
   int grid = opt.grid > 0 ? opt.grid
-                          : (int)(static_spread_ ? items.size() : (items.size() + warps_per_cta - 1) / warps_per_cta);
+                          : (int)(spread ? items.size() : (items.size() + warps_per_cta - 1) / warps_per_cta);
   out->grid = std::max(1, std::min(grid, static_max_ctas_));
   out->is_static = true;
   out->eager = false;
