@@ -253,11 +253,23 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_mx_kernel(const __gr
     for (int base = 0; base < nkb; base += 32) {
       unsigned myword = 0;
       const int passes = min(16, (nkb - base + 1) / 2);
-      for (int i = 0; i < passes; i++) {
+      // eight loads (2048 columns) in flight at a time: two trips to memory per row instead of one per 256 columns
+      #pragma unroll 1
+      for (int i0 = 0; i0 < passes; i0 += 8) {
+      uint4 rawv[8];
+      #pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int vec = (base / 2 + i0 + j) * 32 + lane;
+        rawv[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (i0 + j < passes && vec * 8 < a.H) rawv[j] = __ldg(src + vec);
+      }
+      #pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int i = i0 + j;
+        if (i >= passes) break;
         const int vec = (base / 2 + i) * 32 + lane;             // 16-byte vector of the row
         const bool in = vec * 8 < a.H;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (in) raw = __ldg(src + vec);
+        const uint4 raw = rawv[j];
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
         float2 v[4];
         float m = 0.0f;
@@ -289,6 +301,7 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_mx_kernel(const __gr
             q[j] = __nv_cvt_float2_to_fp8x2(make_float2(v[j].x * inv, v[j].y * inv), __NV_SATFINITE, __NV_E4M3);
           dst[vec] = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
         }
+      }
       }
       if (base + lane < nkb) sfdst[base + lane] = myword;
     }
