@@ -26,6 +26,7 @@
 
 #include <cstdint>
 
+#include "kernels/mx_quant.cuh"
 #include "kernels/sm100_ptx.cuh"
 #include "rbv/moe.h"
 
@@ -275,14 +276,8 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __gri
           float m = 0.0f;
           #pragma unroll
           for (int j = 0; j < 32; j++) m = fmaxf(m, fabsf(o[j]));
-          int e = 0;
-          if (m > 0.0f && m < 3.0e38f) {
-            int ex;
-            const float fr = frexpf(m * (1.0f / 448.0f), &ex);
-            e = (fr == 0.5f) ? ex - 1 : ex;
-            e = max(-127, min(127, e));
-          }
-          const float inv = exp2f((float)-e);
+          const int e = mx_exponent(m);
+          const float inv = mx_inv_scale(e);
           sbytes |= (uint32_t)(e + 127) << (8 * half);
           uint32_t w[8];
           #pragma unroll
@@ -393,16 +388,8 @@ quantize_rows_mx_kernel(const __nv_bfloat16* __restrict__ x, long long rows, int
       }
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));   // the 4 lanes of one 32-column block
       m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-      // smallest power of two 2^e with amax / 2^e <= 448: e = ceil(log2(amax / 448))
-      int e = 0;
-      if (m > 0.0f) {
-        const float t = m * (1.0f / 448.0f);
-        int ex;
-        const float fr = frexpf(t, &ex);          // t = fr * 2^ex, fr in [0.5, 1)
-        e = (fr == 0.5f) ? ex - 1 : ex;
-        e = max(-127, min(127, e));
-      }
-      const float inv = exp2f((float)-e);
+      const int e = mx_exponent(m);
+      const float inv = mx_inv_scale(e);
       const uint32_t byte = (uint32_t)(e + 127);
       // the four blocks of the 128 columns: lanes 0-3, 4-7, 8-11, 12-15 -> bytes 0..3
       uint32_t word = byte << (8 * (lane16 >> 2));

@@ -10,6 +10,7 @@
 #include <cstdint>
 
 #include "api/ctx_internal.h"
+#include "kernels/mx_quant.cuh"
 #include "kernels/primitives.cuh"
 #include "rbv/device_types.h"
 #include "rbv/moe.h"
@@ -230,7 +231,7 @@ struct DispatchMxArgs {
   long long capacity_rows;
 };
 
-__global__ void __launch_bounds__(kMoeThreads) moe_dispatch_mx_kernel(const __grid_constant__ DispatchMxArgs a) {
+__global__ void __launch_bounds__(kMoeThreads, 2) moe_dispatch_mx_kernel(const __grid_constant__ DispatchMxArgs a) {
   const MoeComm& c = a.comm;
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -253,18 +254,19 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_mx_kernel(const __gr
     for (int base = 0; base < nkb; base += 32) {
       unsigned myword = 0;
       const int passes = min(16, (nkb - base + 1) / 2);
-      // eight loads (2048 columns) in flight at a time: two trips to memory per row instead of one per 256 columns
+      // four loads (1024 columns) in flight per lane at a time, two CTAs per SM: a quarter of the trips to memory
+      // that one load per 256 columns would take
       #pragma unroll 1
-      for (int i0 = 0; i0 < passes; i0 += 8) {
-      uint4 rawv[8];
+      for (int i0 = 0; i0 < passes; i0 += 4) {
+      uint4 rawv[4];
       #pragma unroll
-      for (int j = 0; j < 8; j++) {
+      for (int j = 0; j < 4; j++) {
         const int vec = (base / 2 + i0 + j) * 32 + lane;
         rawv[j] = make_uint4(0u, 0u, 0u, 0u);
         if (i0 + j < passes && vec * 8 < a.H) rawv[j] = __ldg(src + vec);
       }
       #pragma unroll
-      for (int j = 0; j < 8; j++) {
+      for (int j = 0; j < 4; j++) {
         const int i = i0 + j;
         if (i >= passes) break;
         const int vec = (base / 2 + i) * 32 + lane;             // 16-byte vector of the row
@@ -280,14 +282,8 @@ __global__ void __launch_bounds__(kMoeThreads) moe_dispatch_mx_kernel(const __gr
         }
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
         m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-        int ex = 0;
-        if (m > 0.0f) {
-          int e2;
-          const float fr = frexpf(m * (1.0f / 448.0f), &e2);
-          ex = (fr == 0.5f) ? e2 - 1 : e2;
-          ex = max(-127, min(127, ex));
-        }
-        const float inv = exp2f((float)-ex);
+        const int ex = mx_exponent(m);
+        const float inv = mx_inv_scale(ex);
         unsigned word = (unsigned)(ex + 127) << (8 * ((lane & 15) >> 2));
         word |= __shfl_xor_sync(0xffffffffu, word, 4);
         word |= __shfl_xor_sync(0xffffffffu, word, 8);
