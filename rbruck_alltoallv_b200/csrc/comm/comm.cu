@@ -46,6 +46,7 @@ Context::Context(int P, int nproc, int proc, int device, size_t user_bytes, size
   if (const char* e = std::getenv("RBV_COOPERATIVE")) cooperative_mode_ = std::atoi(e) != 0 ? 1 : 0;
   if (const char* e = std::getenv("RBV_STATIC_OCC")) static_occ_ = std::atoi(e) >= 2 ? 2 : 1;
   if (const char* e = std::getenv("RBV_STATIC_SPREAD")) static_spread_ = std::atoi(e) != 0;
+  if (const char* e = std::getenv("RBV_EAGER_SPREAD")) eager_spread_ = std::atoi(e);
   if (const char* e = std::getenv("RBV_SEQ_HINT")) seq_hints_ = std::atoi(e) != 0;
   int st_per_sm = 1;
   RBV_CUDA_THROW(a2av_static_configure(static_occ_, &st_per_sm));
@@ -593,7 +594,10 @@ int Context::prepare(const AlgoSpec& spec_in, int ts, const CallArgs& ca, const 
         items = (double)tab.size();
       }
     }
-    int g = opt.grid > 0 ? opt.grid : (int)std::min<double>(max_ctas_, std::max(1.0, std::ceil(items / warps_per_cta)));
+    const bool spread = eager_spread_ != 0 && ka.items != nullptr && opt.grid <= 0;
+    if (spread) ka.flags |= CALL_SPREAD;
+    int g = opt.grid > 0 ? opt.grid
+                         : (int)std::min<double>(max_ctas_, std::max(1.0, spread ? items : std::ceil(items / warps_per_cta)));
     out->grid = std::max(1, std::min(g, max_ctas_));
     // Items wait for units that other items send.  A sender never waits, and items are listed senders first, so a
     // grid that covers all items in one round cannot block itself as long as CTAs start in index order; with one

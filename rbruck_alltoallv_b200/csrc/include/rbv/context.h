@@ -196,6 +196,8 @@ class Context {
   bool seq_hints_ = true;          // off for good once a launch was recorded into a CUDA graph (or RBV_SEQ_HINT=0)
   int static_max_ctas_ = 1;
   int static_occ_ = 1;             // CTAs per SM the static kernel is built for (RBV_STATIC_OCC=2: the 64-register build)
+  int eager_spread_ = 0;           // eager calls with a prepared item table: one CTA per item (RBV_EAGER_SPREAD=1);
+                                   // off: measured on 2 GPUs it cost 1-2 us per call (16.8 against 15.0 us)
   bool static_spread_ = true;      // few items: one per CTA over many SMs instead of 16 per CTA on few (RBV_STATIC_SPREAD=0)
   int prepare_static(const DevPlan* dp, int type_size, const CallArgs& args, const CallOptions& opt, Prepared* out);
   std::string last_error_;

@@ -140,6 +140,8 @@ enum CallFlags : unsigned {
   CALL_BULK = 8u,         // large aligned chunks go through the bulk-copy engine (shared-memory ring per warp)
   CALL_STATIC = 16u,      // every count of the call was known on the host: the kernel walks a table of resolved
                           // copy descriptors (StaticItem) and has no metadata phase
+  CALL_SPREAD = 32u,      // eager kernel: work items are dealt CTA by CTA (item c to warp c / grid of CTA c % grid)
+                          // over a grid of up to one CTA per item, instead of 16 consecutive items per CTA
 };
 
 // One resolved copy of the static rendezvous kernel: chunk k of one op with its addresses worked out on the host.

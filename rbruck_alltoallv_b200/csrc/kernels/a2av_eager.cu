@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(kThreads, 1) a2av_eager_kernel(const __grid_co
   const int P = a.P, L = a.L, ts = a.type_size;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned warps_per_cta = blockDim.x >> 5;
-  const unsigned gwarp = blockIdx.x * warps_per_cta + warp, nwarps = gridDim.x * warps_per_cta;
+  const unsigned nwarps = gridDim.x * warps_per_cta;
+  const unsigned gwarp = (a.flags & CALL_SPREAD) ? warp * gridDim.x + blockIdx.x : blockIdx.x * warps_per_cta + warp;
   CtrlBlock* my = ctrl_of(a, a.proc);
   const bool inl = (a.flags & CALL_META_INLINE) != 0;
   const int* sendcounts = inl ? a.inl.sendcounts : a.sendcounts;
