@@ -17,8 +17,12 @@
 // the scale atom of its A rows and the scale atom of the tile's 128 weight rows.  The rank-0 CTA copies the scales of
 // both CTAs from shared memory into TMEM (tcgen05.cp.32x128b.warpx4, 4 + 4 columns per stage) and issues four MMAs
 // (M 256, N 128, K 32), each naming its scale byte in the instruction descriptor.  TMEM: two 128-column accumulators
-// (the epilogue of tile i overlaps the MMAs of tile i + 1) and 8 columns of scales per pipeline stage.  All waits are
-// bounded; on expiry both CTAs are told, record an error, release their TMEM and return.
+// (the epilogue of tile i overlaps the MMAs of tile i + 1) and 8 columns of scales per pipeline stage.
+// Epilogues: bf16; SwiGLU to bf16; SwiGLU followed by the MXFP8 quantiser of the next GEMM's operand (each thread owns a
+// row of the tile, so the scale of a 32-block needs no other thread); and, for the down GEMM of the MoE layer, bf16 rows
+// stored straight into the buffers of the GPUs the tokens came from (the return all-to-all, overlapped with the MMAs
+// of the other tiles).  All waits are bounded; on expiry both CTAs are told, record an error, release their TMEM and
+// return.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
