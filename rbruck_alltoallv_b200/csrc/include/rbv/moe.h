@@ -31,8 +31,8 @@ int rbv_grouped_gemm_bf16(const void* A, long long a_rows, const void* B, void* 
 int rbv_grouped_gemm_bf16_pair(const void* A, long long a_rows, const void* B, void* C, const int* group_start,
                                const int* group_rows, int G, int N, int K, int ldc, int epilogue, int* error_flag,
                                int max_ctas, void* cuda_stream);
-void rbv_grouped_gemm_set_pair(int on);
-int rbv_grouped_gemm_pair_enabled(void);
+void rbv_grouped_gemm_set_pair(int on);      /* process-wide switch, not synchronised: set it before launching from */
+int rbv_grouped_gemm_pair_enabled(void);      /* several host threads, not while they launch                          */
 
 /* The same with a gated start per group: the loader touches the rows of group g only once ready[g] >= ready_target[g]
  * (device uint64 arrays; the counters are bumped by whoever delivers the rows, e.g. rbv_moe_dispatch_streamed running
